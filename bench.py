@@ -1,0 +1,454 @@
+"""Benchmark of the quantized-weight matmul hot path.
+
+Workload (BASELINE.json configs[4]): the Qwen3-8B-shaped decode matmul stack —
+hidden 4096, 36 layers x {q,k,v,o,gate,up,down}, lm_head 151936 — int8
+per-channel weights (f32 scales, w = q*s), f16 activations, f32 accumulate,
+random init, synthetic activations.  One "step" = one pass of the whole stack
+over a batch of `--batch` tokens (default 8): 253 quantized matmuls, 7.57 GB of
+int8 weight streamed from HBM per step (far larger than L2, so nothing is
+flushed between steps).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch M] [--tp-mode chained|gather]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+    python bench.py --impl reference ...      # the CPU arm (oracle port on the host cores)
+
+Prints ONE JSON line on rank 0.  `value` = tokens/s of the whole job, timed on
+the device with CUDA events on the library's stream (max over ranks); `e2e` =
+the same metric through the public API with the activations copied from pinned
+host memory and the logits read back every step; `roofline` = algorithmic bytes
+per GEMV launch / measured duration against the measured HBM peak.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "qwen3_8b_decode_matmul_stack_tokens_per_s"
+UNIT = "tok/s"
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            d = json.load(open(p))
+            return float(d["hbm_gbs"]), float(d.get("bf16_tflops", FALLBACK_BF16_TFLOPS)), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed
+    region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i",
+                 str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except (ValueError, IndexError):
+                continue
+            for name, cell in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[3:7]):
+                if cell.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference's CPU path, on the host cores
+# ---------------------------------------------------------------------------
+
+class CpuArm:
+    """The reference CPU arithmetic (dequantize once, untimed; then matmul +
+    epilogue with f64 accumulation) on a bounded sample of the stack: one layer's
+    seven projections plus `lm_rows` rows of lm_head, extrapolated to a step."""
+
+    def __init__(self, batch: int, lm_rows: int = 8192, threads: int = 0):
+        import numpy as np
+
+        from oracle import oracle as orc
+        from torchlette_b200.decode_stack import QWEN3_8B as cfg
+
+        self.orc, self.cfg, self.batch, self.lm_rows = orc, cfg, batch, lm_rows
+        self.threads = threads or orc.max_threads()
+        rng = np.random.Generator(np.random.PCG64(0))
+        self.items = []
+        shapes = [(name, k, n) for name, k, n, _ in cfg.projections()] + [("lm_head", cfg.hidden, lm_rows)]
+        for name, k, n in shapes:
+            q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+            s = rng.uniform(0.001, 0.01, size=(n, 1)).astype(np.float32)
+            w = orc.dequantize_direct_f32(q.view(np.uint32).reshape(n, k // 4), s, k, k)  # the reference holds f32
+            x = rng.standard_normal((batch, k)).astype(np.float16).astype(np.float32)
+            self.items.append((name, w, x))
+
+    def step_seconds(self) -> float:
+        t_layer = t_lm = 0.0
+        for name, w, x in self.items:
+            t0 = time.perf_counter()
+            y = self.orc.matmul_nt(x, w, self.threads)
+            if name == "gate":
+                self.orc.unary("silu", y)
+            dt = time.perf_counter() - t0
+            if name == "lm_head":
+                t_lm = dt * (self.cfg.vocab / self.lm_rows)
+            else:
+                t_layer += dt
+        return t_layer * self.cfg.layers + t_lm
+
+    def describe(self, value: float):
+        return {"value": value, "unit": UNIT, "cores": self.threads, "kind": "port",
+                "sample": f"1 of {self.cfg.layers} layers (7 projections) + {self.lm_rows} of {self.cfg.vocab} lm_head "
+                          f"rows, batch {self.batch}, extrapolated to a full step; f32 weights dequantized once, untimed"}
+
+
+def cpu_sample(batch: int):
+    arm = CpuArm(batch)
+    arm.step_seconds()
+    return arm.describe(batch / arm.step_seconds())
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    arm = CpuArm(args.batch)
+    for _ in range(args.warmup):
+        arm.step_seconds()
+    times = [arm.step_seconds() for _ in range(args.steps)]
+    step_s = statistics.mean(times)
+    val = args.batch / step_s
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 accumulate over f32 (CPU)", "data": "synthetic",
+        "config": {"workload": "qwen3-8b-decode-matmul-stack", "batch": args.batch, "layers": 36,
+                   "note": "the reference is TypeScript and no node runtime exists here; this arm is the C port of its "
+                           "CPU path (oracle/tl_oracle.c) on all host cores, each step a bounded sample extrapolated"},
+        "cpu_baseline": arm.describe(val),
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def single_matrix_extras(be, hbm_peak, tf_peak):
+    """The two single-kernel figures the path's targets are stated on: the int8
+    GEMV on 4096x14336 (rotating over enough weight copies to defeat L2) and the
+    prefill GEMM M=2048 (tensor roofline)."""
+    import torch
+
+    from torchlette_b200 import binding as B
+
+    lib, ctx = be._lib, be._ctx
+    dev = torch.device("cuda", be.device)
+    out = {}
+    k, n = 4096, 14336
+    copies = 6  # 6 x 58.7 MB = 352 MB > 2 x L2
+    w = torch.randint(-127, 128, (copies, n, k), dtype=torch.int8, device=dev)
+    s = torch.empty(copies, n, dtype=torch.float32, device=dev).uniform_(0.001, 0.01)
+    bias = torch.randn(n, device=dev) * 0.02
+    q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, k, B.TL_F32, B.TL_SCALE_DIRECT)
+    e = B.Epilogue()
+    e.n_ops, e.n_inputs = 2, 1
+    e.ops[0] = B.EpilogueOp(B.TL_EPI_BIAS, 0, 0, 0)
+    e.ops[1] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY["gelu"], 0, 0)
+    e.inputs[0] = bias.data_ptr()
+    ev0, ev1 = C.c_void_p(), C.c_void_p()
+    B.check(ctx, lib.tl_event_create(ctx, C.byref(ev0)))
+    B.check(ctx, lib.tl_event_create(ctx, C.byref(ev1)))
+    torch.cuda.synchronize(dev)
+    for m in (1, 16):
+        x = torch.randn(m, k, device=dev).to(torch.float16)
+        y = torch.empty(m, n, dtype=torch.float16, device=dev)
+        torch.cuda.synchronize(dev)
+
+        def sweep(reps):
+            for _ in range(reps):
+                for c in range(copies):
+                    B.check(ctx, lib.tl_qgemv_nt(ctx, x.data_ptr(), B.TL_F16, w[c].data_ptr(), s[c].data_ptr(),
+                                                 y.data_ptr(), B.TL_F16, m, n, k, C.byref(q), 1.0, C.byref(e)))
+        sweep(3)
+        be.sync()
+        reps = 20
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        sweep(reps)
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        us = ms.value * 1e3 / (reps * copies)
+        nbytes = n * k + n * 4 + n * 4 + m * k * 2 + m * n * 2
+        gbs = nbytes / us / 1e3
+        out[f"gemv_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": gbs,
+                                       "frac_of_hbm_peak": gbs / hbm_peak, "epilogue": "bias+gelu, f16 out",
+                                       "l2": f"rotating over {copies} weight copies (352 MB)"}
+    del w, s
+    # prefill GEMM, config 3
+    for (m, kk, nn) in ((2048, 4096, 14336), (2048, 14336, 4096)):
+        w = torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device=dev)
+        s = torch.empty(nn, dtype=torch.float32, device=dev).uniform_(0.001, 0.01)
+        x = torch.randn(m, kk, device=dev).to(torch.bfloat16)
+        y = torch.empty(m, nn, dtype=torch.bfloat16, device=dev)
+        q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, kk, B.TL_F32, B.TL_SCALE_DIRECT)
+        e2 = B.Epilogue()
+        e2.n_ops = 1
+        e2.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY["gelu"], 0, 0)
+        torch.cuda.synchronize(dev)
+
+        def run():
+            return lib.tl_qgemm_nt(ctx, x.data_ptr(), B.TL_BF16, w.data_ptr(), s.data_ptr(), y.data_ptr(), B.TL_BF16,
+                                   m, nn, kk, C.byref(q), 1.0, C.byref(e2))
+        rc = run()
+        if rc != 0:
+            out[f"qgemm_{m}x{kk}x{nn}"] = {"unavailable": lib.tl_last_error(ctx).decode()}
+            continue
+        for _ in range(3):
+            run()
+        be.sync()
+        reps = 10
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        for _ in range(reps):
+            run()
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        tf = 2.0 * m * nn * kk / (ms.value / reps * 1e-3) / 1e12
+        out[f"qgemm_{m}x{kk}x{nn}"] = {"ms": ms.value / reps, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak,
+                                       "epilogue": "gelu, bf16 out"}
+        del w, s, x, y
+    lib.tl_event_destroy(ctx, ev0)
+    lib.tl_event_destroy(ctx, ev1)
+    return out
+
+
+def run_gpu(args):
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    from torchlette_b200 import backend as tb
+    from torchlette_b200 import binding as B
+    from torchlette_b200.decode_stack import QWEN3_8B, DecodeStack, StackConfig
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run for N>1")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback on this path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        B.preload_nccl()
+    be = tb.CudaBackend(local_rank)
+    lib, ctx = be._lib, be._ctx
+    if world > 1:
+        ident = [None]
+        if rank == 0:
+            buf = (C.c_char * B.TL_COMM_ID_BYTES)()
+            B.check(None, lib.tl_comm_unique_id(buf))
+            ident[0] = bytes(buf)
+        dist.broadcast_object_list(ident, src=0)
+        idbuf = (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])
+        B.check(ctx, lib.tl_comm_init(ctx, rank, world, idbuf))
+
+    cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
+    stack = DecodeStack(be, cfg, rank, world, args.tp_mode)
+    if args.autotune:
+        shapes = sorted({(cfg.batch, p.n, p.k) for p in stack.layers[0]} | {(cfg.batch, stack.lm_head.n, stack.lm_head.k)})
+        for (m, n, k) in shapes:
+            be.pretuneMatmulShapes([(m, n, k)], cfg.act_dtype, cfg.act_dtype, tb.QuantPacking("int8-grouped", k, "f32", "direct"))
+    stack.capture()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        be.sync()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=torch.device("cuda", local_rank))
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ev0, ev1 = C.c_void_p(), C.c_void_p()
+    B.check(ctx, lib.tl_event_create(ctx, C.byref(ev0)))
+    B.check(ctx, lib.tl_event_create(ctx, C.byref(ev1)))
+
+    # ---- device-timed steps ------------------------------------------------
+    for _ in range(args.warmup):
+        stack.step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    launches0 = be.getKernelLaunchCount()
+    B.check(ctx, lib.tl_event_record(ctx, ev0))
+    for _ in range(args.steps):
+        stack.step()
+    B.check(ctx, lib.tl_event_record(ctx, ev1))
+    barrier()
+    ms = C.c_float()
+    B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+    launches = be.getKernelLaunchCount() - launches0
+    dev_ms = max_over_ranks(ms.value)
+    ms_per_step = dev_ms / args.steps
+    value = cfg.batch * args.steps / (dev_ms * 1e-3)
+
+    # ---- end to end: pinned host activations in, logits out, every step -----
+    act_np = np.random.default_rng(1).standard_normal((cfg.batch, cfg.hidden)).astype(np.float16)
+    hx = torch.from_numpy(act_np).pin_memory()
+    hlogits = torch.empty(cfg.batch, cfg.vocab, dtype=torch.float32).pin_memory()
+    h2d, d2h = hx.numel() * 2, hlogits.numel() * 4
+
+    def e2e_step():
+        B.check(ctx, lib.tl_upload(ctx, stack.x.data_ptr(), hx.data_ptr(), h2d))
+        stack.step()
+        B.check(ctx, lib.tl_download(ctx, hlogits.data_ptr(), stack.logits.data_ptr(), d2h))
+        be.sync()
+
+    for _ in range(max(1, args.warmup)):
+        e2e_step()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        e2e_step()
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    clocks = sampler.stop() if rank == 0 else None
+    e2e_value = cfg.batch * args.steps / e2e_s
+    finite = bool(torch.isfinite(hlogits).all().item()) and float(hlogits.abs().max()) > 0
+
+    hbm_peak, tf_peak, which = measured_peaks()
+    # Per rank: the algorithmic bytes of its own shard, summed over the 253 launches of a step.
+    m, a = cfg.batch, 2
+    alg = 0
+    for p in stack.layers[0]:
+        alg += p.n * p.k + p.n * 4 + m * p.k * a + m * p.n * a
+    alg *= cfg.layers
+    alg += stack.lm_head.n * stack.lm_head.k + stack.lm_head.n * 4 + m * stack.lm_head.k * a + m * stack.lm_head.n * 4
+    gemv_launches = stack.launches_per_step()
+    achieved = alg / (ms_per_step * 1e-3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
+                "traffic": None, "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
+                "kernel": "qgemv_mma_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
+                "avg_launch_us": ms_per_step * 1e3 / gemv_launches,
+                "note": "per rank; all 253 small-batch GEMV launches of one step, events on the launching stream"
+                        + ("" if world == 1 else "; at N>1 the step time also holds the NCCL collectives")}
+    tpath = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(tpath):
+        try:
+            roofline["traffic"] = json.load(open(tpath)).get("qgemv_stack_dram_bytes_per_launch")
+        except Exception:
+            pass
+
+    extras = {}
+    cpu = None
+    if rank == 0 and world == 1:
+        if not args.no_extras:
+            try:
+                extras = single_matrix_extras(be, hbm_peak, tf_peak)
+            except tb.TlError as ex:  # reported, never hidden
+                extras = {"error": str(ex)}
+        if not args.no_cpu:
+            cpu = cpu_sample(cfg.batch)
+
+    if rank == 0:
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int8 weights x f16 activations, f32 accumulate", "data": "synthetic",
+            "config": {"workload": "qwen3-8b-decode-matmul-stack", "batch": cfg.batch, "layers": cfg.layers,
+                       "hidden": cfg.hidden, "intermediate": cfg.inter, "vocab": cfg.vocab,
+                       "weights": "int8 per-channel, f32 scales, random init", "parallelism": f"tp{world}",
+                       "tp_mode": args.tp_mode if world > 1 else "none", "replay": "cuda graph",
+                       "l2": "inputs larger than L2: 7.57 GB of weights per step, no flush needed",
+                       "autotune": bool(args.autotune)},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_s / args.steps * 1e3, "logits_finite": finite},
+            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+            "weight_GB_per_step": cfg.weight_bytes_per_step() / 1e9,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        if extras:
+            line["kernels"] = extras
+        print(json.dumps(line))
+    stack.destroy()
+    if world > 1:
+        lib.tl_comm_destroy(ctx)
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tp-mode", default="chained", choices=["chained", "gather"])
+    ap.add_argument("--autotune", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-matrix GEMV / prefill GEMM figures")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,273 @@
+/*
+ * tlcuda.h — C ABI of the sm_100a quantized-weight matmul library
+ * (libtlcuda.so).  This is the boundary a torchlette `cuda` backend binds:
+ * plain pointers and sizes, no C++ or framework types.
+ *
+ * Conventions
+ *   - One opaque context per GPU.  A context owns one CUDA stream, its scratch
+ *     memory, the variant/tuning tables and the route counters.
+ *   - Every call returns an int32 status (0 = TL_OK, negative = error) and
+ *     stores a message readable with tl_last_error().  No call throws, aborts
+ *     or frees caller memory.  Argument errors are detected before anything is
+ *     launched.
+ *   - Compute entry points take raw device pointers (memory from tl_alloc or
+ *     from any other allocator on the same device) and only ENQUEUE work on
+ *     the context's stream; tl_sync() waits for it.
+ *   - A context is single-caller (thread-compatible, not thread-safe).
+ *   - Packed weight layout is fixed by the reference quantizer
+ *     (src/backend/quantize.ts:62-131): u32 [N, K/4], four signed int8 per
+ *     word, byte lane = k & 3, lowest k in bits 0-7; scales [N, K/G] row-major.
+ *
+ * Each declaration names the torchlette interface it replaces (paths relative
+ * to the torchlette repository root).
+ */
+#ifndef TLCUDA_H_
+#define TLCUDA_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define TL_API
+#else
+#define TL_API __attribute__((visibility("default")))
+#endif
+
+typedef struct tl_ctx tl_ctx;
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  TL_OK = 0,
+  TL_ERR_INVALID_ARG = -1,   /* the reference throws a JS Error for these */
+  TL_ERR_UNSUPPORTED = -2,
+  TL_ERR_CUDA = -3,
+  TL_ERR_NCCL = -4,
+  TL_ERR_TIMEOUT = -5,       /* a bounded device-side wait ran out */
+  TL_ERR_OOM = -6,
+  TL_ERR_UNIMPLEMENTED = -7
+};
+
+/* ---- element types (src/backend/types.ts:133 DType, plus bf16) --------- */
+enum { TL_F32 = 0, TL_F16 = 1, TL_BF16 = 2 };
+
+/* ---- operand storage format -------------------------------------------- */
+/* Mirrors StorageFormat.packing / QuantPacking (src/backend/types.ts:38-67),
+ * widened with the per-channel f32 "direct" convention:
+ *   scale_convention TL_SCALE_SNORM127: w = (q/127) * s   (quantize.ts:138-156)
+ *   scale_convention TL_SCALE_DIRECT  : w = q * s
+ * group_size divides K; group_size == K is per-output-channel. */
+enum { TL_SCHEME_INT8_GROUPED = 1 };
+enum { TL_SCALE_SNORM127 = 0, TL_SCALE_DIRECT = 1 };
+typedef struct tl_quant_desc {
+  int32_t scheme;
+  int32_t group_size;
+  int32_t scales_dtype; /* TL_F16 or TL_F32 */
+  int32_t scale_convention;
+} tl_quant_desc;
+
+/* ---- fused epilogue ------------------------------------------------------ */
+/* Mirrors EpilogueConfig + epilogueInputs (src/backend/webgpu/matmul/types.ts:
+ * 13-24; GEMV seam src/backend/webgpu/matmul/gemv.ts:135-192; tiled seam
+ * src/schedule/matmul-skeleton.ts:916-966).  The chain is evaluated in f32 in
+ * listed order on acc*alpha; the result is cast to out_dtype at the store.
+ *   bias   : v += inputs[input_index][col]            (f32 [N])
+ *   unary  : v = op(v)
+ *   binary : v = v (op) inputs[input_index][row*N+col] (f32 [M,N])
+ *   cast   : v = round-trip through to_dtype */
+enum { TL_EPI_NONE = 0, TL_EPI_BIAS = 1, TL_EPI_UNARY = 2, TL_EPI_BINARY = 3, TL_EPI_CAST = 4 };
+enum {
+  TL_UNARY_RELU = 1, TL_UNARY_SILU = 2, TL_UNARY_SIGMOID = 3, TL_UNARY_TANH = 4,
+  TL_UNARY_GELU_TANH = 5, /* the reference's op name "gelu" */
+  TL_UNARY_GELU_ERF = 6
+};
+enum { TL_BINARY_ADD = 1, TL_BINARY_SUB = 2, TL_BINARY_MUL = 3 };
+#define TL_EPI_MAX_OPS 8
+#define TL_EPI_MAX_INPUTS 4
+typedef struct tl_epilogue_op {
+  int32_t kind;
+  int32_t op;
+  int32_t input_index;
+  int32_t to_dtype;
+} tl_epilogue_op;
+typedef struct tl_epilogue {
+  int32_t n_ops;
+  tl_epilogue_op ops[TL_EPI_MAX_OPS];
+  int32_t n_inputs;
+  const void* inputs[TL_EPI_MAX_INPUTS];
+} tl_epilogue;
+
+/* ---- context -------------------------------------------------------------- */
+/* initWebGPU / destroyWebGPU / syncWebGPU / getWebGPUInitError /
+ * getGpuUncapturedErrorCount (src/backend/webgpu/index.ts:39-70,
+ * src/backend/webgpu/gpu-context.ts:386-405). */
+TL_API int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx);
+TL_API int32_t tl_ctx_destroy(tl_ctx* ctx);
+TL_API int32_t tl_sync(tl_ctx* ctx);
+TL_API int64_t tl_async_error_count(tl_ctx* ctx);
+/* Message of the last failing call on ctx (or of the last failing call without
+ * a context when ctx is NULL).  Valid until the next call on the same thread. */
+TL_API const char* tl_last_error(tl_ctx* ctx);
+/* The CUDA stream every enqueue goes to (a cudaStream_t), so a host framework
+ * can order its own work or record its own events on it. */
+TL_API int32_t tl_ctx_stream(tl_ctx* ctx, void** out_stream);
+TL_API int32_t tl_device_sm_count(tl_ctx* ctx, int32_t* out_sms);
+
+/* ---- memory: tensorFromArray / read / destroy (src/backend/types.ts:341-345,
+ * :666) ---------------------------------------------------------------------- */
+TL_API int32_t tl_alloc(tl_ctx* ctx, size_t bytes, void** out_dptr);
+TL_API int32_t tl_free(tl_ctx* ctx, void* dptr);
+TL_API int32_t tl_upload(tl_ctx* ctx, void* dst_dptr, const void* src_host, size_t bytes);
+TL_API int32_t tl_download(tl_ctx* ctx, void* dst_host, const void* src_dptr, size_t bytes);
+TL_API int32_t tl_host_alloc_pinned(tl_ctx* ctx, size_t bytes, void** out_hptr);
+TL_API int32_t tl_host_free_pinned(tl_ctx* ctx, void* hptr);
+TL_API int32_t tl_memset(tl_ctx* ctx, void* dptr, int32_t byte_value, size_t bytes);
+/* Strided device-to-device copy on the context's stream (height rows of
+ * width_bytes, pitches in bytes): the `contiguous` of a column slice. */
+TL_API int32_t tl_copy2d(tl_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
+                         size_t width_bytes, size_t height);
+
+/* ---- host quantizer: quantizeLinearWeight (src/backend/quantize.ts:77-131) --
+ * weight f32 [n,k] (host) -> packed u32 [n,k/4] + scales u16 [n,k/group] (f16
+ * bits of the group abs-max), both host buffers.  Multi-threaded over rows. */
+TL_API int32_t tl_quantize_linear_weight(const float* weight, int64_t n, int64_t k,
+                                         int32_t group_size, uint32_t* packed, uint16_t* scales);
+/* f32ToF16Bits / f16BitsToF32 (src/backend/quantize.ts:22-60). */
+TL_API uint32_t tl_f32_to_f16_bits(float value);
+TL_API float tl_f16_bits_to_f32(uint32_t bits);
+
+/* ---- the hot path ---------------------------------------------------------- */
+/* dispatchQuantizedGemvNT (src/backend/webgpu/matmul/dispatch.ts:875-931),
+ * widened to m in [1,16], f16/bf16/f32 activations and outputs, and the GEMV
+ * epilogue seam (gemv.ts:168-192):
+ *   out[r, c] = epilogue(alpha * sum_k a[r,k] * dequant(packed, scales)[c,k])
+ * a: [m,k] a_dtype row-major; out: [m,n] out_dtype row-major; f32 accumulate.
+ * Bumps the quant-GEMV counter.  epilogue may be NULL. */
+TL_API int32_t tl_qgemv_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                           const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n,
+                           int64_t k, const tl_quant_desc* qdesc, float alpha,
+                           const tl_epilogue* epilogue);
+
+/* Prefill GEMM with dequantization fused into the tile loads (tcgen05 / TMEM).
+ * Replaces the reference's dispatchDequantizeInt8Grouped + dispatchMatmul pair
+ * for m > 1 (src/backend/webgpu/ops/matmul-ops.ts:163-181).  a is f16 or bf16;
+ * the dequantized weight is rounded to a_dtype before the tensor-core product.
+ * Bumps the quant-GEMM counter. */
+TL_API int32_t tl_qgemm_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                           const void* scales, void* out, int32_t out_dtype, int64_t m, int64_t n,
+                           int64_t k, const tl_quant_desc* qdesc, float alpha,
+                           const tl_epilogue* epilogue);
+
+/* The backend matmul seam for a packed B operand: matmulQuantizedB
+ * (src/backend/webgpu/ops/matmul-ops.ts:113-182).  Routes m <= 16 to
+ * tl_qgemv_nt and larger m to tl_qgemm_nt. */
+TL_API int32_t tl_qmatmul_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                             const void* scales, void* out, int32_t out_dtype, int64_t m,
+                             int64_t n, int64_t k, const tl_quant_desc* qdesc, float alpha,
+                             const tl_epilogue* epilogue);
+
+/* dispatchDequantizeInt8Grouped (src/backend/webgpu/matmul/dispatch.ts:949-1037):
+ * out[n,k] = dequant(packed, scales).  With out_dtype TL_F32 the result is
+ * bit-identical to dequantizeToF32 (quantize.ts:138-156).  Bumps the dequant
+ * counter. */
+TL_API int32_t tl_dequant_int8(tl_ctx* ctx, const void* packed, const void* scales, void* out,
+                               int32_t out_dtype, int64_t n, int64_t k,
+                               const tl_quant_desc* qdesc);
+/* Debug op: the signed byte lanes as int8 [n,k] (integer half of the dequant). */
+TL_API int32_t tl_unpack_int8(tl_ctx* ctx, const void* packed, void* out_i8, int64_t n, int64_t k);
+
+/* ---- selection: planTiledMatmul / selectMatmulChoice / SelectionReceipt
+ * (src/backend/webgpu/matmul/dispatch.ts:171-192, 1130-1329;
+ *  src/backend/webgpu/matmul/variants.ts:54-260) ------------------------------ */
+enum { TL_FAMILY_QGEMV = 1, TL_FAMILY_QGEMM = 2 };
+typedef struct tl_variant {
+  int32_t family;   /* TL_FAMILY_* */
+  int32_t kernel;   /* family-specific kernel id (see tl_variant_name) */
+  int32_t p0, p1, p2, p3; /* family-specific parameters */
+} tl_variant;
+typedef struct tl_plan_receipt {
+  tl_variant choice;
+  int32_t grid[3];
+  int32_t block;
+  int32_t split_k;
+  int32_t from_tuning_cache; /* 1 when a per-shape tuned winner was used */
+  int32_t epilogue_engaged;
+} tl_plan_receipt;
+/* Pure function of geometry, dtypes and format: what tl_qmatmul_nt would run. */
+TL_API int32_t tl_plan_qmatmul(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                               int32_t out_dtype, const tl_quant_desc* qdesc,
+                               const tl_epilogue* epilogue, tl_plan_receipt* out_receipt);
+TL_API const char* tl_variant_name(const tl_variant* v);
+/* Force one variant for every following call (NULL clears).  A/B testing hook,
+ * the analogue of an explicit MatmulKernelConfig (variants.ts:214-236). */
+TL_API int32_t tl_force_variant(tl_ctx* ctx, const tl_variant* v);
+
+/* ---- route counters (src/backend/webgpu/matmul/dispatch.ts:833-864, 943-947) */
+enum {
+  TL_COUNTER_QGEMV = 0,         /* getQuantGemvDispatchCount */
+  TL_COUNTER_DEQUANT = 1,       /* getDequantI8DispatchCount */
+  TL_COUNTER_QGEMV_EPILOGUE = 2,/* getGemvEpilogueDispatchCount */
+  TL_COUNTER_QGEMM = 3,
+  TL_COUNTER_KERNEL_LAUNCHES = 4, /* every kernel this library launched */
+  TL_COUNTER_COUNT = 5
+};
+TL_API int64_t tl_counter_get(tl_ctx* ctx, int32_t which);
+TL_API int32_t tl_counters_reset(tl_ctx* ctx);
+
+/* ---- autotune (src/backend/webgpu/matmul/autotune.ts:97-329;
+ * src/backend/webgpu/matmul/dispatch.ts:79-141, 405-578) ---------------------- */
+typedef struct tl_shape { int64_t m, n, k; } tl_shape;
+TL_API int32_t tl_autotune_set_enabled(tl_ctx* ctx, int32_t enabled);
+TL_API int32_t tl_autotune_is_enabled(tl_ctx* ctx);
+/* pretuneMatmulShapes: time every applicable candidate for each shape on
+ * rotated buffers and cache the winner per exact (m,n,k,dtype,format). */
+TL_API int32_t tl_pretune(tl_ctx* ctx, const tl_shape* shapes, int32_t n_shapes, int32_t a_dtype,
+                          int32_t out_dtype, const tl_quant_desc* qdesc);
+TL_API int32_t tl_tune_seed(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                            const tl_quant_desc* qdesc, const tl_variant* choice);
+TL_API int32_t tl_tune_get(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                           const tl_quant_desc* qdesc, tl_variant* out_choice); /* 1 = found */
+TL_API int32_t tl_tune_clear(tl_ctx* ctx);
+TL_API int64_t tl_tune_run_count(tl_ctx* ctx);
+/* exportTuningCache / importTuningCache: JSON text.  Export writes at most cap
+ * bytes (NUL-terminated) and returns the full length needed in *out_len. */
+TL_API int32_t tl_tune_export_json(tl_ctx* ctx, char* buf, size_t cap, size_t* out_len);
+TL_API int32_t tl_tune_import_json(tl_ctx* ctx, const char* json);
+
+/* ---- replay: the analogue of the reference's CompiledPlan replay
+ * (src/executor/executor.ts:1249) is a captured CUDA graph of enqueued calls. */
+typedef struct tl_graph tl_graph;
+TL_API int32_t tl_graph_begin(tl_ctx* ctx);
+TL_API int32_t tl_graph_end(tl_ctx* ctx, tl_graph** out_graph);
+TL_API int32_t tl_graph_launch(tl_ctx* ctx, tl_graph* graph);
+TL_API int32_t tl_graph_destroy(tl_ctx* ctx, tl_graph* graph);
+
+/* ---- timing on the context's stream (CUDA events) -------------------------- */
+typedef struct tl_event tl_event;
+TL_API int32_t tl_event_create(tl_ctx* ctx, tl_event** out_event);
+TL_API int32_t tl_event_record(tl_ctx* ctx, tl_event* ev);
+TL_API int32_t tl_event_elapsed_ms(tl_ctx* ctx, tl_event* start, tl_event* stop, float* out_ms);
+TL_API int32_t tl_event_destroy(tl_ctx* ctx, tl_event* ev);
+
+/* ---- multi-GPU (no counterpart in the reference, whose only parallelism is
+ * DiLoCo over WebSocket, src/distributed/) ------------------------------------
+ * One context per process/GPU.  tl_comm_unique_id fills a 128-byte NCCL id on
+ * rank 0; the host distributes it and every rank calls tl_comm_init. */
+#define TL_COMM_ID_BYTES 128
+TL_API int32_t tl_comm_unique_id(void* out_id128);
+TL_API int32_t tl_comm_init(tl_ctx* ctx, int32_t rank, int32_t world, const void* id128);
+TL_API int32_t tl_comm_destroy(tl_ctx* ctx);
+/* Column-parallel gather: every rank contributes local [m, n_local]; out is
+ * [m, world*n_local] with rank r's columns at offset r*n_local. */
+TL_API int32_t tl_allgather_cols(tl_ctx* ctx, const void* local, void* out, int64_t m,
+                                 int64_t n_local, int32_t dtype);
+/* Row-parallel reduction: in-place sum over ranks of buf[count]. */
+TL_API int32_t tl_allreduce_sum(tl_ctx* ctx, void* buf, int64_t count, int32_t dtype);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TLCUDA_H_ */

@@ -1,0 +1,555 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU
+oracle on the same seeded inputs.
+
+Tolerances (stated by the path's specification): unpacked int8 and dequantized
+f32 weights bit-exact; f32-accumulated f32 outputs within 1e-3; f16/bf16 outputs
+within 1e-2; both measured with the reference probes' metric
+|x - ref| / max(1, |ref|) (examples/qwen3/probe-quant-gemv.ts:166-177).
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+import cases
+from oracle import oracle as orc
+from torchlette_b200 import backend as tb
+from torchlette_b200 import binding as B
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-3
+TOL_HALF = 1e-2
+
+GEMV_VARIANTS_F32 = [(1, 0, 8, 0, 1, 0), (1, 1, 8, 1, 1, 0), (1, 1, 8, 2, 1, 0), (1, 1, 4, 4, 1, 0)]
+GEMV_VARIANTS_HALF = GEMV_VARIANTS_F32 + [(1, 2, 8, 4, 1, 0), (1, 2, 4, 2, 1, 0), (1, 2, 16, 2, 1, 0)]
+
+
+def _out_to_f32(arr, dtype):
+    if dtype == "bf16":
+        return orc.bf16_bits_to_f32(arr)
+    return np.asarray(arr, dtype=np.float32)
+
+
+def _upload_act(be, cs, m, k, dtype):
+    if dtype == "f32":
+        return be.ops.tensorFromArray(cs["x"], [m, k], "f32")
+    return be.ops.tensorFromArray(cs["x_bits"], [m, k], dtype)
+
+
+def _run_direct(be, cs, m, n, k, act_dtype, out_dtype, variant=None, bias=False, act=None, alpha=1.0):
+    """Per-channel f32 'direct' case through linear(); returns (gpu f32, oracle f32)."""
+    fmt = tb.perChannelFormat(k)
+    w = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, fmt)
+    x = _upload_act(be, cs, m, k, act_dtype)
+    bt = be.ops.tensorFromArray(cs["bias"], [n], "f32") if bias else None
+    be.forceVariant(variant)
+    try:
+        y = be.linear(x, w, bt, act, out_dtype)
+    finally:
+        be.forceVariant(None)
+    got = _out_to_f32(be.ops.read(y), out_dtype)
+    wref = orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k)
+    ref = orc.linear_reference(cs["x"], wref, cs["bias"] if bias else None, act, alpha)
+    for t in (w.scales, w, x, y) + ((bt,) if bt else ()):
+        t.destroy()
+    return got, ref
+
+
+# ---------------------------------------------------------------------------
+# integer unpack + dequant: bit-exact
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k,group", [(128, 128, 64), (96, 384, 128), (33, 256, 32), (7, 64, 4)])
+def test_unpack_and_dequant_snorm_bit_exact(backend, n, k, group):
+    be = backend
+    w, _ = orc.lcg_fill(0x51A7EE ^ n, n * k)
+    packed, scales = be.quantizeLinearWeight(w.reshape(n, k), group)
+    op, os_ = orc.quantize_linear_weight(w.reshape(n, k), group)
+    assert np.array_equal(packed, op) and np.array_equal(scales, os_)
+    fmt = tb.StorageFormat("f16", tb.QuantPacking("int8-grouped", group, "f16"))
+    wt = be.createQuantizedWeight(packed, scales, n, k, fmt)
+    assert np.array_equal(be.unpackInt8(wt, n, k), orc.unpack_int8(packed, k))
+    before = be.getDequantI8DispatchCount()
+    out = be.ops.empty([n, k], "f32")
+    be.dispatchDequantizeInt8Grouped(wt, wt.scales, out, n, k, group)
+    assert be.getDequantI8DispatchCount() == before + 1
+    ref = orc.dequantize_to_f32(packed, scales, k, group)
+    assert np.array_equal(be.ops.read(out).view(np.uint32), ref.view(np.uint32))
+    for dt in ("f16", "bf16"):
+        o2 = be.ops.empty([n, k], dt)
+        be.dispatchDequantizeInt8Grouped(wt, wt.scales, o2, n, k, group)
+        got = be.ops.read(o2)
+        if dt == "f16":
+            assert np.array_equal(got.view(np.uint16), ref.astype(np.float16).view(np.uint16))
+        else:
+            assert np.array_equal(got, orc.bf16_bits_rne(ref))
+        o2.destroy()
+    for t in (out, wt.scales, wt):
+        t.destroy()
+
+
+def test_unpack_every_byte_value_every_lane(backend):
+    be = backend
+    q = np.zeros((4, 1024), dtype=np.int8)
+    for lane in range(4):
+        q[lane, lane::4] = np.arange(-128, 128, dtype=np.int8)
+    packed = cases.pack_int8(q)
+    s = np.full((4, 1), 0.5, dtype=np.float32)
+    wt = be.createQuantizedWeight(packed, s, 4, 1024, tb.perChannelFormat(1024))
+    assert np.array_equal(be.unpackInt8(wt, 4, 1024), q)
+    out = be.ops.empty([4, 1024], "f32")
+    be.dispatchDequantizeInt8Grouped(wt, wt.scales, out, 4, 1024, 1024, packing=wt.format.packing)
+    assert np.array_equal(be.ops.read(out), q.astype(np.float32) * 0.5)  # -128 is not clamped
+    for t in (out, wt.scales, wt):
+        t.destroy()
+
+
+def test_dequant_direct_bit_exact_config0(backend):
+    be = backend
+    cs = cases.per_channel_case(2048, 2048, 1, seed=0)
+    wt = be.createQuantizedWeight(cs["packed"], cs["scales"], 2048, 2048, tb.perChannelFormat(2048))
+    out = be.ops.empty([2048, 2048], "f32")
+    be.dispatchDequantizeInt8Grouped(wt, wt.scales, out, 2048, 2048, 2048, packing=wt.format.packing)
+    ref = orc.dequantize_direct_f32(cs["packed"], cs["scales"], 2048, 2048)
+    assert np.array_equal(be.ops.read(out).view(np.uint32), ref.view(np.uint32))
+    for t in (out, wt.scales, wt):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# config 0: f32 activations, per-channel scales, every applicable variant
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("variant", [None] + GEMV_VARIANTS_F32)
+def test_config0_gemv_f32(backend, variant):
+    cs = cases.per_channel_case(2048, 2048, 1, seed=0)
+    got, ref = _run_direct(backend, cs, 1, 2048, 2048, "f32", "f32", variant)
+    assert cases.rel_err(got, ref) <= TOL_F32
+
+
+def test_config0_matches_committed_golden_rows(backend):
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "config0_rows0_63.npz"))
+    cs = cases.per_channel_case(2048, 2048, 1, seed=0)
+    got, _ = _run_direct(backend, cs, 1, 2048, 2048, "f32", "f32")
+    assert cases.rel_err(got[:, :64], g["y"]) <= TOL_F32
+
+
+def test_config0_reference_native_format_g64(backend):
+    """The same int8 values in the reference's own layout: f16 group scales
+    holding 127*s (so that (q/127)*scale = q*s up to the f16 rounding)."""
+    be = backend
+    cs = cases.per_channel_case(512, 2048, 1, seed=0)
+    s16 = np.repeat((cs["scales"] * 127.0).astype(np.float16), 2048 // 64, axis=1)
+    wt = be.createQuantizedWeight(cs["packed"], s16.view(np.uint16), 512, 2048, tb.resolveWeightFormat("int8-64"))
+    x = be.ops.tensorFromArray(cs["x"], [1, 2048], "f32")
+    y = be.linear(x, wt)
+    wref = orc.dequantize_to_f32(cs["packed"], s16.view(np.uint16), 2048, 64)
+    assert cases.rel_err(be.ops.read(y), orc.matmul_nt(cs["x"], wref)) <= TOL_F32
+    for t in (x, y, wt.scales, wt):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# the reference probes' gate shapes (probe-quant-gemv.ts:34-42, 166-187)
+# ---------------------------------------------------------------------------
+
+def _probe_gemv_case(be, n, k, group, state, act_dtype="f32"):
+    w, state = orc.lcg_fill(state, n * k)
+    a, state = orc.lcg_fill(state, k)
+    packed, scales = be.quantizeLinearWeight(w.reshape(n, k), group)
+    del w
+    fmt = tb.resolveWeightFormat("int8-64" if group == 64 else "int8-128")
+    wt = be.createQuantizedWeight(packed, scales, n, k, fmt)
+    if act_dtype == "f16":
+        a = a.astype(np.float16).astype(np.float32)
+        xt = be.ops.tensorFromArray(a.astype(np.float16), [1, k], "f16")
+    else:
+        xt = be.ops.tensorFromArray(a, [1, k], "f32")
+    out = be.ops.empty([1, n], "f32")
+    q0 = be.getQuantGemvDispatchCount()
+    be.dispatchQuantizedGemvNT(xt, wt, wt.scales, out, n, k, group)
+    assert be.getQuantGemvDispatchCount() == q0 + 1  # qHits === 1 (:188)
+    got = be.ops.read(out)[0]
+    deq = orc.dequantize_to_f32(packed, scales, k, group)
+    control = orc.matmul_nt(a.reshape(1, k), deq)[0]
+    ref64 = deq.astype(np.float64) @ a.astype(np.float64)
+    for t in (out, xt, wt.scales, wt):
+        t.destroy()
+    return got, control, ref64, state
+
+
+@pytest.mark.parametrize("act_dtype", ["f32", "f16"])
+def test_probe_quant_gemv_shapes(backend, act_dtype):
+    state = 0x51A7EE
+    for group in (64, 128):
+        for n, k in [(128, 128), (512, 1024), (1024, 2048), (2048, 6144)]:
+            got, control, ref64, state = _probe_gemv_case(backend, n, k, group, state, act_dtype)
+            assert cases.rel_err(got, control) <= 5e-4, (n, k, group)
+            assert cases.rel_err(got, ref64) <= 5e-4, (n, k, group)
+    assert backend.getGpuUncapturedErrorCount() == 0
+
+
+def test_probe_quant_gemv_lm_head_scale(backend):
+    """N = 151936 (the probe's 2-D-grid case), one group size to bound host time."""
+    got, control, ref64, _ = _probe_gemv_case(backend, 151936, 2048, 64, 0x51A7EE)
+    assert cases.rel_err(got, control) <= 5e-4
+    assert cases.rel_err(got, ref64) <= 5e-4
+
+
+@pytest.mark.parametrize("m", [1, 4])
+def test_probe_quant_operand(backend, m):
+    """probe-quant-operand.ts: linear(x, qWeight) vs the f32 control, drift <= 5e-3,
+    and the route: no explicit dequant on any M (the reference dequantizes for M=4)."""
+    be = backend
+    for n, k in [(128, 128), (512, 1024), (2048, 6144)]:
+        for group in (64, 128):
+            st = (0x51 ^ n ^ (k << 3) ^ (group << 7)) & 0xFFFFFFFF
+            w, st = orc.lcg_fill(st, n * k, 0.1)
+            x, st = orc.lcg_fill(st, m * k)
+            packed, scales = be.quantizeLinearWeight(w.reshape(n, k), group)
+            wt = be.createQuantizedWeight(packed, scales, n, k, tb.resolveWeightFormat(f"int8-{group}"))
+            xt = be.ops.tensorFromArray(x, [m, k], "f32")
+            q0, d0 = be.getQuantGemvDispatchCount(), be.getDequantI8DispatchCount()
+            y = be.linear(xt, wt)
+            assert be.getQuantGemvDispatchCount() == q0 + 1 and be.getDequantI8DispatchCount() == d0
+            ref = orc.matmul_nt(x.reshape(m, k), orc.dequantize_to_f32(packed, scales, k, group))
+            assert cases.drift(be.ops.read(y), ref) <= 5e-3, (n, k, group)
+            assert cases.rel_err(be.ops.read(y), ref) <= TOL_F32
+            for t in (y, xt, wt.scales, wt):
+                t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# config 1: Qwen3-0.6B decode projections, f16 activations, M = 1
+# ---------------------------------------------------------------------------
+
+CONFIG1 = [(1024, 2048), (1024, 1024), (1024, 1024), (1024, 3072), (1024, 3072), (2048, 1024), (3072, 1024)]
+
+
+@pytest.mark.parametrize("variant", [None] + GEMV_VARIANTS_HALF[1:])
+def test_config1_projections_f16(backend, variant):
+    for seed, (k, n) in enumerate(CONFIG1):
+        cs = cases.per_channel_case(n, k, 1, seed=seed, act_dtype="f16")
+        got, ref = _run_direct(backend, cs, 1, n, k, "f16", "f32", variant)
+        assert cases.rel_err(got, ref) <= TOL_F32, (k, n)
+        got16, _ = _run_direct(backend, cs, 1, n, k, "f16", "f16", variant)
+        assert cases.rel_err(got16, ref) <= TOL_HALF, (k, n)
+
+
+# ---------------------------------------------------------------------------
+# config 2: small batch with fused bias + activation, f16 in / f16 out
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m", [1, 4, 8, 16])
+def test_config2_fused_epilogue_small_batch(backend, m):
+    n, k = 14336, 4096
+    cs = cases.per_channel_case(n, k, m, seed=100 + m, act_dtype="f16", bias=True)
+    for act in (None, "relu", "gelu", "silu"):
+        got, ref = _run_direct(backend, cs, m, n, k, "f16", "f16", None, bias=True, act=act)
+        assert cases.rel_err(got, ref) <= TOL_HALF, (m, act)
+    got32, ref = _run_direct(backend, cs, m, n, k, "f16", "f32", None, bias=True, act="gelu")
+    assert cases.rel_err(got32, ref) <= TOL_F32
+
+
+@pytest.mark.parametrize("m", [2, 3, 5, 9, 13, 16])
+@pytest.mark.parametrize("act_dtype", ["f16", "bf16", "f32"])
+def test_small_batch_every_variant_and_dtype(backend, m, act_dtype):
+    n, k = 272, 512  # n is not a multiple of 16*warps; exercises tail tiles
+    cs = cases.per_channel_case(n, k, m, seed=m, act_dtype=act_dtype, bias=True)
+    variants = GEMV_VARIANTS_F32 if act_dtype == "f32" else GEMV_VARIANTS_HALF
+    for v in [None] + variants:
+        got, ref = _run_direct(backend, cs, m, n, k, act_dtype, "f32", v, bias=True, act="silu")
+        assert cases.rel_err(got, ref) <= TOL_F32, (v, m, act_dtype)
+
+
+def test_bf16_output_and_activations(backend):
+    cs = cases.per_channel_case(1024, 1024, 8, seed=77, act_dtype="bf16", bias=True)
+    got, ref = _run_direct(backend, cs, 8, 1024, 1024, "bf16", "bf16", None, bias=True, act="gelu")
+    assert cases.rel_err(got, ref) <= TOL_HALF
+
+
+# ---------------------------------------------------------------------------
+# grouped scales on the fast kernels, odd shapes, fallbacks
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("n,k,group,m", [
+    (130, 1024, 64, 1), (130, 1024, 128, 3), (1, 64, 64, 1), (17, 192, 64, 16), (33, 128, 32, 2),
+    (50, 80, 16, 1), (9, 68, 4, 1), (9, 68, 68, 5), (5, 8, 2, 1), (300, 4096, 4096, 7),
+])
+@pytest.mark.parametrize("act_dtype", ["f32", "f16"])
+def test_grouped_and_ragged_shapes(backend, n, k, group, m, act_dtype):
+    be = backend
+    rng = np.random.default_rng(n * 1000 + k + group)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    if act_dtype == "f16":
+        x = x.astype(np.float16).astype(np.float32)
+    packed, scales = be.quantizeLinearWeight(w, group)
+    fmt = tb.StorageFormat("f16", tb.QuantPacking("int8-grouped", group, "f16"))
+    wt = be.createQuantizedWeight(packed, scales, n, k, fmt)
+    xt = be.ops.tensorFromArray(x.astype(np.float16) if act_dtype == "f16" else x, [m, k], act_dtype)
+    y = be.linear(xt, wt)
+    ref = orc.matmul_nt(x, orc.dequantize_to_f32(packed, scales, k, group))
+    assert cases.rel_err(be.ops.read(y), ref) <= TOL_F32
+    plan = be.planQuantizedMatmul(m, n, k, act_dtype, "f32", fmt.packing)
+    if k % 16 or group % 16:
+        assert ".scalar" in plan["variant"]
+    elif act_dtype == "f32" or k % 64 or group % 64:
+        assert ".simt" in plan["variant"]
+    else:
+        assert ".mma" in plan["variant"]
+    for t in (y, xt, wt.scales, wt):
+        t.destroy()
+
+
+def test_f32_scales_grouped_direct(backend):
+    be = backend
+    n, k, group, m = 96, 512, 128, 4
+    rng = np.random.default_rng(11)
+    q = rng.integers(-127, 128, size=(n, k), dtype=np.int8)
+    s = rng.uniform(0.001, 0.01, size=(n, k // group)).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    fmt = tb.StorageFormat("f16", tb.QuantPacking("int8-grouped", group, "f32", "direct"))
+    wt = be.createQuantizedWeight(cases.pack_int8(q), s, n, k, fmt)
+    xt = be.ops.tensorFromArray(x, [m, k], "f16")
+    y = be.linear(xt, wt)
+    ref = orc.matmul_nt(x.astype(np.float32), orc.dequantize_direct_f32(cases.pack_int8(q), s, k, group))
+    assert cases.rel_err(be.ops.read(y), ref) <= TOL_F32
+    for t in (y, xt, wt.scales, wt):
+        t.destroy()
+
+
+def test_empty_shapes_launch_nothing(backend):
+    be = backend
+    lib, ctx = be._lib, be._ctx
+    q = B.QuantDesc(1, 64, B.TL_F16, 0)
+    buf = be._alloc(1024)
+    launches = be.getKernelLaunchCount()
+    for m, n in [(0, 64), (1, 0)]:
+        rc = lib.tl_qmatmul_nt(ctx, buf, B.TL_F32, buf, buf, buf, B.TL_F32, m, n, 64, C.byref(q), 1.0, None)
+        assert rc == B.TL_OK
+    assert be.getKernelLaunchCount() == launches
+    be._free(buf)
+
+
+# ---------------------------------------------------------------------------
+# epilogue battery (examples/qwen3/probe-gemv.ts:170-235; matmul-epilogue.spec.ts)
+# ---------------------------------------------------------------------------
+
+def _epilogue_case(be, ops, m=3, n=70, k=64, out_dtype="f32", act_dtype="f32"):
+    rng = np.random.default_rng(len(ops) * 7 + m)
+    cs = cases.per_channel_case(n, k, m, seed=5, act_dtype=act_dtype, bias=True)
+    extra = rng.standard_normal((m, n)).astype(np.float32)
+    wt = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, tb.perChannelFormat(k))
+    xt = _upload_act(be, cs, m, k, act_dtype)
+    bias_t = be.ops.tensorFromArray(cs["bias"], [n], "f32")
+    extra_t = be.ops.tensorFromArray(extra, [m, n], "f32")
+    chain, ref = [], orc.matmul_nt(cs["x"], orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k))
+    for op in ops:
+        if op == "bias":
+            chain.append(("add", bias_t))
+            ref = orc.add_bias(ref, cs["bias"])
+        elif op in ("add2d", "sub2d", "mul2d"):
+            chain.append((op[:3], extra_t))
+            r64 = ref.astype(np.float64)
+            e64 = extra.astype(np.float64)
+            ref = {"add": r64 + e64, "sub": r64 - e64, "mul": r64 * e64}[op[:3]].astype(np.float32)
+        elif op.startswith("cast:"):
+            chain.append(("cast", op[5:]))
+            ref = ref.astype(np.float16).astype(np.float32) if op[5:] == "f16" else orc.bf16_bits_to_f32(orc.bf16_bits_rne(ref))
+        else:
+            chain.append((op, None))
+            ref = orc.unary(op, ref)
+    cfg, inputs, consumed = tb.detectMatmulEpilogue(chain)
+    assert consumed == len(ops)
+    cfg.outputDtype = out_dtype
+    e0 = be.getGemvEpilogueDispatchCount()
+    y = be.ops.matmul(xt, be.ops.transpose(wt), {"epilogue": cfg, "epilogueInputs": inputs})
+    assert be.getGemvEpilogueDispatchCount() == e0 + 1
+    got = _out_to_f32(be.ops.read(y), out_dtype)
+    for t in (y, xt, bias_t, extra_t, wt.scales, wt):
+        t.destroy()
+    return got, ref
+
+
+@pytest.mark.parametrize("ops", [
+    ["bias"], ["relu"], ["gelu"], ["silu"], ["sigmoid"], ["tanh"], ["gelu_erf"], ["bias", "relu"], ["bias", "gelu"],
+    ["bias", "silu"], ["add2d"], ["bias", "mul2d", "relu"], ["sub2d", "tanh"], ["cast:f16", "bias"],
+    ["bias", "gelu", "cast:f16", "add2d"],
+])
+def test_epilogue_battery(backend, ops):
+    got, ref = _epilogue_case(backend, ops)
+    tol = 1e-2 if any(o.startswith("gelu") for o in ops) else 1e-3  # the reference's own tolerances
+    assert np.allclose(got, ref, rtol=tol, atol=tol), ops
+    assert cases.rel_err(got, ref) <= TOL_F32
+
+
+def test_epilogue_f16_output_mma_path(backend):
+    got, ref = _epilogue_case(backend, ["bias", "gelu"], m=8, n=200, k=256, out_dtype="f16", act_dtype="f16")
+    assert cases.rel_err(got, ref) <= TOL_HALF
+
+
+def test_alpha_scales_before_epilogue(backend):
+    be = backend
+    cs = cases.per_channel_case(64, 128, 2, seed=4, act_dtype="f16", bias=True)
+    wt = be.createQuantizedWeight(cs["packed"], cs["scales"], 64, 128, tb.perChannelFormat(128))
+    xt = be.ops.tensorFromArray(cs["x_bits"], [2, 128], "f16")
+    bt = be.ops.tensorFromArray(cs["bias"], [64], "f32")
+    cfg, inputs, _ = tb.detectMatmulEpilogue([("add", bt), ("relu", None)])
+    y = be.ops.matmul(xt, be.ops.transpose(wt), {"epilogue": cfg, "epilogueInputs": inputs, "alpha": 0.25})
+    ref = orc.linear_reference(cs["x"], orc.dequantize_direct_f32(cs["packed"], cs["scales"], 128, 128), cs["bias"],
+                               "relu", alpha=0.25)
+    assert cases.rel_err(be.ops.read(y), ref) <= TOL_F32
+    for t in (y, xt, bt, wt.scales, wt):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# errors: reported by status + message, nothing launched
+# ---------------------------------------------------------------------------
+
+def test_argument_errors(backend):
+    be = backend
+    lib, ctx = be._lib, be._ctx
+    buf = be._alloc(4096)
+    q = B.QuantDesc(1, 64, B.TL_F16, 0)
+    launches = be.getKernelLaunchCount()
+
+    def call(fn=lib.tl_qgemv_nt, a=buf, packed=buf, scales=buf, out=buf, m=1, n=8, k=64, qd=q, epi=None, adt=B.TL_F32):
+        return fn(ctx, a, adt, packed, scales, out, B.TL_F32, m, n, k, C.byref(qd) if qd else None, 1.0, epi)
+
+    assert call(m=17) == B.TL_ERR_INVALID_ARG and b"[1,16]" in lib.tl_last_error(ctx)
+    assert call(k=66) == B.TL_ERR_INVALID_ARG and b"divisible by 4" in lib.tl_last_error(ctx)
+    assert call(k=96) == B.TL_ERR_INVALID_ARG and b"groupSize=64" in lib.tl_last_error(ctx)
+    assert call(scales=None) == B.TL_ERR_INVALID_ARG and b"scales" in lib.tl_last_error(ctx)
+    assert call(packed=None) == B.TL_ERR_INVALID_ARG
+    assert call(out=None) == B.TL_ERR_INVALID_ARG
+    assert call(qd=None) == B.TL_ERR_INVALID_ARG and b"packing" in lib.tl_last_error(ctx)
+    assert call(qd=B.QuantDesc(7, 64, B.TL_F16, 0)) == B.TL_ERR_UNSUPPORTED and b"scheme" in lib.tl_last_error(ctx)
+    assert call(adt=9) == B.TL_ERR_INVALID_ARG
+    assert call(a=buf + 2, adt=B.TL_F32) == B.TL_ERR_INVALID_ARG and b"misaligned" in lib.tl_last_error(ctx)
+    e = B.Epilogue()
+    e.n_ops = 1
+    e.ops[0] = B.EpilogueOp(B.TL_EPI_BIAS, 0, 0, 0)
+    e.n_inputs = 0
+    assert call(epi=C.byref(e)) == B.TL_ERR_INVALID_ARG and b"input" in lib.tl_last_error(ctx)
+    e.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, 99, 0, 0)
+    assert call(epi=C.byref(e)) == B.TL_ERR_UNSUPPORTED
+    assert be.getKernelLaunchCount() == launches
+    assert lib.tl_qgemv_nt(None, buf, 0, buf, buf, buf, 0, 1, 8, 64, C.byref(q), 1.0, None) == B.TL_ERR_INVALID_ARG
+    be._free(buf)
+    with pytest.raises(tb.TlError, match="packed length"):
+        be.createQuantizedWeight(np.zeros(10, np.uint32), np.zeros(4, np.uint16), 4, 64, tb.resolveWeightFormat("int8-64"))
+    with pytest.raises(tb.TlError, match="scales length"):
+        be.createQuantizedWeight(np.zeros(64, np.uint32), np.zeros(3, np.uint16), 4, 64, tb.resolveWeightFormat("int8-64"))
+    with pytest.raises(tb.TlError, match="packing is required"):
+        be.createQuantizedWeight(np.zeros(64, np.uint32), np.zeros(4, np.uint16), 4, 64, tb.StorageFormat("f16"))
+
+
+def test_forced_variant_must_be_applicable(backend):
+    be = backend
+    cs = cases.per_channel_case(32, 80, 1, seed=1)  # K % 64 != 0: the mma kernel cannot run it
+    wt = be.createQuantizedWeight(cs["packed"], cs["scales"], 32, 80, tb.perChannelFormat(80))
+    xt = be.ops.tensorFromArray(cs["x"].astype(np.float16), [1, 80], "f16")
+    be.forceVariant((1, 2, 8, 4, 1, 0))
+    try:
+        with pytest.raises(tb.TlError, match="forced variant"):
+            be.linear(xt, wt)
+    finally:
+        be.forceVariant(None)
+    for t in (xt, wt.scales, wt):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# replay (captured graph) and counters
+# ---------------------------------------------------------------------------
+
+def test_graph_replay_matches_eager_and_counts(backend):
+    """The reference's compiled plans engage on the 2nd+ run (probe-quant-compiled.ts
+    loops 12 iterations at N=2048, K=2304, G=64, seed 0x93, w = rng()*0.05, drift <= 5e-3)."""
+    be = backend
+    n, k, group = 2048, 2304, 64
+    w, st = orc.lcg_fill(0x93, n * k, 0.05)
+    packed, scales = be.quantizeLinearWeight(w.reshape(n, k), group)
+    wt = be.createQuantizedWeight(packed, scales, n, k, tb.resolveWeightFormat("int8-64"))
+    deq = orc.dequantize_to_f32(packed, scales, k, group)
+    xt = be.ops.empty([1, k], "f32")
+    out = be.ops.empty([1, n], "f32")
+    x0, st = orc.lcg_fill(st, k)
+    be._upload(xt.buffer, x0)
+    be.dispatchQuantizedGemvNT(xt, wt, wt.scales, out, n, k, group)  # eager run first
+    be.beginCapture()
+    be.dispatchQuantizedGemvNT(xt, wt, wt.scales, out, n, k, group)
+    graph = be.endCapture()
+    total_hits = 0
+    for _ in range(12):
+        x, st = orc.lcg_fill(st, k)
+        be._upload(xt.buffer, x)
+        q0 = be.getQuantGemvDispatchCount()
+        be.replay(graph)
+        total_hits += be.getQuantGemvDispatchCount() - q0
+        ref = orc.matmul_nt(x.reshape(1, k), deq)
+        assert cases.drift(be.ops.read(out), ref) <= 5e-3
+    assert total_hits == 12
+    be.destroyGraph(graph)
+    for t in (out, xt, wt.scales, wt):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# autotune surface (test/webgpu/matmul-autotune.spec.ts:310-464, 518-764)
+# ---------------------------------------------------------------------------
+
+def test_autotune_cache_semantics(backend):
+    be = backend
+    pk = tb.perChannelFormat(1024).packing
+    be.clearPerShapeMatmulChoices()
+    assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) is None
+    default = be.planQuantizedMatmul(1, 2048, 1024, "f16", "f32", pk)
+    assert default["family"] == "gemv" and not default["fromTuningCache"]
+    runs = be.getAutotuneRunCount()
+    be.pretuneMatmulShapes([(1, 2048, 1024)], "f16", "f32", pk)
+    assert be.getAutotuneRunCount() == runs + 1
+    won = be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk)
+    assert won is not None and won[0] == B.TL_FAMILY_QGEMV
+    be.pretuneMatmulShapes([(1, 2048, 1024)], "f16", "f32", pk)  # cache hit: no new search
+    assert be.getAutotuneRunCount() == runs + 1
+    assert be.planQuantizedMatmul(1, 2048, 1024, "f16", "f32", pk)["fromTuningCache"]
+    # per-dtype separation
+    assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f32", pk) is None
+    # a seeded winner short-circuits planning and changes the launch geometry
+    be.seedPerShapeMatmulChoice(1, 2048, 1024, "f16", pk, (1, 1, 4, 2, 1, 0))
+    seeded = be.planQuantizedMatmul(1, 2048, 1024, "f16", "f32", pk)
+    assert ".simt" in seeded["variant"] and seeded["grid"][0] == 2048 // 8 and seeded["block"] == 128
+    # a seeded winner is re-gated on applicability: f32 activations cannot use the mma kernel
+    be.seedPerShapeMatmulChoice(1, 2048, 1024, "f32", pk, (1, 2, 8, 4, 1, 0))
+    assert ".simt" in be.planQuantizedMatmul(1, 2048, 1024, "f32", "f32", pk)["variant"]
+    # export / import round trip, invalid JSON rejected without touching the cache
+    text = be.exportTuningCache()
+    be.clearPerShapeMatmulChoices()
+    assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) is None
+    with pytest.raises(tb.TlError, match="invalid"):
+        be.importTuningCache("{not json")
+    assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) is None
+    be.importTuningCache(text)
+    assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) == (1, 1, 4, 2, 1, 0)
+    be.clearPerShapeMatmulChoices()
+    be.setAutotuneEnabled(True)
+    assert be.isAutotuneEnabled()
+    be.setAutotuneEnabled(False)
+    assert not be.isAutotuneEnabled()
+
+
+def test_tuned_winner_still_matches_oracle(backend):
+    be = backend
+    n, k = 3072, 1024
+    pk = tb.perChannelFormat(k).packing
+    be.pretuneMatmulShapes([(1, n, k), (8, n, k)], "f16", "f32", pk)
+    for m in (1, 8):
+        cs = cases.per_channel_case(n, k, m, seed=31 + m, act_dtype="f16")
+        got, ref = _run_direct(be, cs, m, n, k, "f16", "f32")
+        assert cases.rel_err(got, ref) <= TOL_F32
+    be.clearPerShapeMatmulChoices()

@@ -1,0 +1,572 @@
+"""Host-side mirror of torchlette's backend interface for the quantized-weight
+matmul path, over the C ABI in ``include/tlcuda.h``.
+
+Names, argument meaning and error behaviour follow the reference (paths relative
+to the torchlette repository root):
+
+  Backend / BackendOps.matmul        src/backend/types.ts:340-745
+  StorageFormat / resolveWeightFormat src/backend/types.ts:38-67
+  createQuantizedWeight              src/runtime/engine.ts:2041-2149
+  api.linear                         src/frontend/torchlette.ts:878-894
+  matmul seam / matmulQuantizedB     src/backend/webgpu/ops/matmul-ops.ts:42-182
+  dispatchQuantizedGemvNT            src/backend/webgpu/matmul/dispatch.ts:875-931
+  dispatchDequantizeInt8Grouped      src/backend/webgpu/matmul/dispatch.ts:949-1037
+  route counters                     src/backend/webgpu/matmul/dispatch.ts:833-864, 943-947
+  epilogue-fusion decision           src/compiler/matmul-epilogue.ts:131-262
+  autotune surface                   src/backend/webgpu/matmul/dispatch.ts:79-141, 405-578
+
+Python stands in for the TypeScript frontend because no node toolchain exists
+where this was built; every function here is a thin call into the C ABI, which
+is what an N-API addon would bind.  There is no CPU or WebGPU fallback: without
+the CUDA library and an sm_100 GPU, ``initCuda`` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass, field
+from typing import Optional, Sequence
+
+import numpy as np
+
+from . import binding as B
+from .binding import TlError
+
+# ---------------------------------------------------------------------------
+# StorageFormat (src/backend/types.ts:38-67), widened with the scale convention
+# ---------------------------------------------------------------------------
+
+
+@dataclass(frozen=True)
+class QuantPacking:
+    scheme: str = "int8-grouped"
+    groupSize: int = 64
+    scalesDtype: str = "f16"
+    scaleConvention: str = "snorm127"  # "snorm127": w=(q/127)*s ; "direct": w=q*s
+
+
+@dataclass(frozen=True)
+class StorageFormat:
+    elementType: str = "f16"
+    packing: Optional[QuantPacking] = None
+
+
+def resolveWeightFormat(name: str, elementType: str = "f16") -> StorageFormat:
+    """"int8-64" | "int8-128" -> StorageFormat (types.ts:57-67)."""
+    if name not in ("int8-64", "int8-128"):
+        raise ValueError(f"unknown weight format {name}")
+    return StorageFormat(elementType, QuantPacking("int8-grouped", 64 if name == "int8-64" else 128, "f16"))
+
+
+def perChannelFormat(k: int, elementType: str = "f16") -> StorageFormat:
+    """Per-output-channel f32 scales, w = q*s (the benchmark configurations)."""
+    return StorageFormat(elementType, QuantPacking("int8-grouped", k, "f32", "direct"))
+
+
+# ---------------------------------------------------------------------------
+# EpilogueConfig (src/backend/webgpu/matmul/types.ts:13-24)
+# ---------------------------------------------------------------------------
+
+
+@dataclass
+class EpilogueConfig:
+    ops: list = field(default_factory=list)  # dicts: {"kind": "bias", "inputIndex": 0} ...
+    additionalInputCount: int = 0
+    outputDtype: str = "f32"
+
+
+_FUSIBLE_UNARY = {"relu", "silu", "sigmoid", "tanh", "gelu", "gelu_tanh", "gelu_erf"}
+
+
+def detectMatmulEpilogue(chain: Sequence[tuple], matmulDtype: str = "f32"):
+    """The lazy graph's epilogue-fusion decision for the ops that follow a matmul
+    (matmul-epilogue.ts:131-262), applied to a linear chain description.
+
+    ``chain`` is a list of (opName, operand) where operand is a CudaTensor for
+    add/sub/mul, a dtype name for cast, a dict of options for gelu
+    ({"approximate": "none"} selects gelu_erf, matmul-epilogue.ts:52-56) and
+    None otherwise.  Returns (EpilogueConfig, inputs, consumed) claiming at most
+    four ops, or None when nothing fuses.  Unlike the reference
+    (graph-compiler.ts:150-152) a quantized B operand does not veto the fusion.
+    """
+    ops, inputs = [], []
+    out_dtype = matmulDtype
+    consumed = 0
+    for name, operand in chain:
+        if consumed >= 4:
+            break
+        if name == "cast":
+            ops.append({"kind": "cast", "toDtype": operand})
+            out_dtype = operand
+        elif name == "add":
+            if len(inputs) >= 4:
+                break
+            kind = "bias" if len(operand.shape) == 1 else "binary"
+            op = {"kind": kind, "inputIndex": len(inputs)}
+            if kind == "binary":
+                op["op"] = "add"
+            ops.append(op)
+            inputs.append(operand)
+        elif name in ("mul", "sub"):
+            if len(inputs) >= 4:
+                break
+            ops.append({"kind": "binary", "op": name, "inputIndex": len(inputs)})
+            inputs.append(operand)
+        elif name in _FUSIBLE_UNARY:
+            opname = name
+            if name == "gelu" and isinstance(operand, dict) and operand.get("approximate") == "none":
+                opname = "gelu_erf"
+            ops.append({"kind": "unary", "op": opname})
+        else:
+            break
+        consumed += 1
+    if consumed == 0:
+        return None
+    return EpilogueConfig(ops, len(inputs), out_dtype), inputs, consumed
+
+
+# ---------------------------------------------------------------------------
+# Tensors
+# ---------------------------------------------------------------------------
+
+
+class CudaTensor:
+    """BackendTensor (types.ts:5-27): shape, dtype, ownsBuffer, format, scales.
+    ``buffer`` is a raw device pointer.  ``transposed`` marks the [K,N] view of a
+    contiguous [N,K] buffer produced by ``transpose`` (the only view the path
+    needs; src/backend/webgpu/ops/views.ts:925-933 propagates format/scales)."""
+
+    def __init__(self, backend, shape, dtype, buffer, nbytes, ownsBuffer=True, format=None, scales=None,
+                 transposed=False):
+        self.backend = backend
+        self.shape = list(shape)
+        self.dtype = dtype
+        self.buffer = buffer
+        self.nbytes = nbytes
+        self.ownsBuffer = ownsBuffer
+        self.format = format
+        self.scales = scales
+        self.transposed = transposed
+
+    def destroy(self):
+        if self.ownsBuffer and self.buffer:
+            self.backend._free(self.buffer)
+        self.buffer = None
+
+    def toArray(self):
+        return self.backend.ops.read(self)
+
+
+_NP_OF = {"f32": np.float32, "f16": np.float16, "bf16": np.uint16, "u32": np.uint32, "u16": np.uint16,
+          "i8": np.int8}
+
+
+class CudaOps:
+    """BackendOps subset the path needs (types.ts:340-680)."""
+
+    def __init__(self, backend):
+        self._b = backend
+
+    # tensorFromArray: f32 uploads verbatim; "f16" takes np.float16 values or raw
+    # uint16 bit patterns; "bf16" takes raw uint16 bit patterns; u32/u16 verbatim.
+    def tensorFromArray(self, values, shape, dtype="f32") -> CudaTensor:
+        arr = np.asarray(values)
+        if dtype == "f16" and arr.dtype == np.uint16:
+            host = np.ascontiguousarray(arr)
+        elif dtype == "bf16":
+            if arr.dtype != np.uint16:
+                raise TypeError("bf16 tensors are created from uint16 bit patterns")
+            host = np.ascontiguousarray(arr)
+        else:
+            host = np.ascontiguousarray(arr, dtype=_NP_OF[dtype])
+        n = int(np.prod(shape)) if len(shape) else 1
+        if host.size != n:
+            raise ValueError(f"tensorFromArray: expected {n} elements, got {host.size}")
+        buf = self._b._alloc(host.nbytes)
+        self._b._upload(buf, host)
+        return CudaTensor(self._b, shape, dtype, buf, host.nbytes)
+
+    def empty(self, shape, dtype="f32") -> CudaTensor:
+        n = int(np.prod(shape)) if len(shape) else 1
+        nbytes = n * np.dtype(_NP_OF[dtype]).itemsize
+        return CudaTensor(self._b, shape, dtype, self._b._alloc(nbytes), nbytes)
+
+    def read(self, t: CudaTensor) -> np.ndarray:
+        if t.transposed:
+            raise ValueError("read: materialize the transposed view first")
+        host = np.empty(int(np.prod(t.shape)) if t.shape else 1, dtype=_NP_OF[t.dtype])
+        self._b._download(host, t.buffer)
+        if t.dtype == "f16":
+            host = host.view(np.float16)
+        return host.reshape(t.shape)
+
+    def transpose(self, t: CudaTensor, dim0: int = -2, dim1: int = -1) -> CudaTensor:
+        nd = len(t.shape)
+        if nd < 2 or {dim0 % nd, dim1 % nd} != {nd - 2, nd - 1}:
+            raise ValueError("transpose: only the last two dims can be swapped on this path")
+        shape = t.shape[:-2] + [t.shape[-1], t.shape[-2]]
+        return CudaTensor(self._b, shape, t.dtype, t.buffer, t.nbytes, ownsBuffer=False, format=t.format,
+                          scales=t.scales, transposed=not t.transposed)
+
+    def matmul(self, a: CudaTensor, b: CudaTensor, options: Optional[dict] = None) -> CudaTensor:
+        """Backend matmul; the storage-format seam (matmul-ops.ts:42-59)."""
+        if b.format is not None and b.format.packing is not None:
+            return self._b._matmulQuantizedB(a, b, options or {})
+        raise TlError(B.TL_ERR_UNIMPLEMENTED,
+                      "matmul: only a packed (quantized) B operand is served by the cuda backend")
+
+
+class CudaBackend:
+    """``Backend`` named "cuda" (types.ts:681-696)."""
+
+    name = "cuda"
+
+    def __init__(self, device: int = 0):
+        self._lib = B.load()
+        ctx = C.c_void_p()
+        B.check(None, self._lib.tl_ctx_create(device, C.byref(ctx)))
+        self._ctx = ctx
+        self.device = device
+        self.ops = CudaOps(self)
+
+    # -- lifetime -----------------------------------------------------------
+    def destroy(self):
+        if self._ctx:
+            self._lib.tl_ctx_destroy(self._ctx)
+            self._ctx = None
+
+    def sync(self):
+        B.check(self._ctx, self._lib.tl_sync(self._ctx))
+
+    def getGpuUncapturedErrorCount(self) -> int:
+        return int(self._lib.tl_async_error_count(self._ctx))
+
+    def stream(self) -> int:
+        s = C.c_void_p()
+        B.check(self._ctx, self._lib.tl_ctx_stream(self._ctx, C.byref(s)))
+        return s.value or 0
+
+    def smCount(self) -> int:
+        v = C.c_int32()
+        B.check(self._ctx, self._lib.tl_device_sm_count(self._ctx, C.byref(v)))
+        return v.value
+
+    # -- raw memory ---------------------------------------------------------
+    def _alloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        B.check(self._ctx, self._lib.tl_alloc(self._ctx, nbytes, C.byref(p)))
+        return p.value
+
+    def _free(self, ptr: int):
+        B.check(self._ctx, self._lib.tl_free(self._ctx, C.c_void_p(ptr)))
+
+    def _upload(self, ptr: int, host: np.ndarray):
+        B.check(self._ctx, self._lib.tl_upload(self._ctx, C.c_void_p(ptr), host.ctypes.data_as(C.c_void_p),
+                                               host.nbytes))
+        self.sync()
+
+    def _download(self, host: np.ndarray, ptr: int):
+        B.check(self._ctx, self._lib.tl_download(self._ctx, host.ctypes.data_as(C.c_void_p), C.c_void_p(ptr),
+                                                 host.nbytes))
+        self.sync()
+
+    # -- quantized weights --------------------------------------------------
+    def quantizeLinearWeight(self, weight: np.ndarray, groupSize: int = 64):
+        """quantizeLinearWeight (quantize.ts:77-131) through the library's host
+        quantizer.  Returns (packed u32 [N,K/4], scales u16 [N,K/G])."""
+        w = np.ascontiguousarray(weight, dtype=np.float32)
+        if w.ndim != 2:
+            raise ValueError("quantize: weight must be [N, K]")
+        n, k = w.shape
+        if k % 4 != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by 4")
+        if groupSize <= 0 or k % groupSize != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by groupSize={groupSize}")
+        packed = np.zeros((n, k // 4), dtype=np.uint32)
+        scales = np.zeros((n, k // groupSize), dtype=np.uint16)
+        B.check(None, self._lib.tl_quantize_linear_weight(w.ctypes.data_as(C.c_void_p), n, k, groupSize,
+                                                          packed.ctypes.data_as(C.c_void_p),
+                                                          scales.ctypes.data_as(C.c_void_p)))
+        return packed, scales
+
+    def createQuantizedWeight(self, packed, scales, n: int, k: int, format: StorageFormat) -> CudaTensor:
+        """engine.ts:2041-2149: validate lengths, upload the packed words and the
+        scales, return the logical [N,K] tensor carrying format + scales."""
+        packing = format.packing
+        if packing is None:
+            raise TlError(B.TL_ERR_INVALID_ARG, "createQuantizedWeight: format.packing is required")
+        if k % 4 != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: K={k} must be divisible by 4")
+        packed = np.ascontiguousarray(packed, dtype=np.uint32)
+        if packed.size != n * (k // 4):
+            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: packed length {packed.size} != {n * (k // 4)}")
+        if packing.groupSize <= 0 or k % packing.groupSize != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG,
+                          f"createQuantizedWeight: K={k} must be divisible by groupSize={packing.groupSize}")
+        groups = k // packing.groupSize
+        sdt = np.uint16 if packing.scalesDtype == "f16" else np.float32
+        scales = np.asarray(scales)
+        if packing.scalesDtype == "f16" and scales.dtype == np.float16:
+            scales = scales.view(np.uint16)
+        scales = np.ascontiguousarray(scales, dtype=sdt)
+        if scales.size != n * groups:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: scales length {scales.size} != {n * groups}")
+        st = self.ops.tensorFromArray(scales, [n, groups], "u16" if packing.scalesDtype == "f16" else "f32")
+        wt = self.ops.tensorFromArray(packed, [n, k // 4], "u32")
+        wt.shape = [n, k]  # logical shape; the buffer stays u32 [N, K/4]
+        wt.dtype = format.elementType
+        wt.format = format
+        wt.scales = st
+        return wt
+
+    # -- descriptors ----------------------------------------------------------
+    @staticmethod
+    def _qdesc(packing: QuantPacking) -> B.QuantDesc:
+        if packing.scheme != "int8-grouped":
+            raise TlError(B.TL_ERR_UNSUPPORTED, f"matmulQuantizedB: unsupported scheme {packing.scheme}")
+        return B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, packing.groupSize, B.DTYPE_ID[packing.scalesDtype],
+                           B.TL_SCALE_SNORM127 if packing.scaleConvention == "snorm127" else B.TL_SCALE_DIRECT)
+
+    @staticmethod
+    def _epilogue(epilogue: Optional[EpilogueConfig], epilogueInputs: Sequence[CudaTensor]):
+        if epilogue is None:
+            return None
+        e = B.Epilogue()
+        if len(epilogue.ops) > B.TL_EPI_MAX_OPS:
+            raise TlError(B.TL_ERR_INVALID_ARG, "epilogue: too many ops")
+        if len(epilogueInputs) > B.TL_EPI_MAX_INPUTS:
+            raise TlError(B.TL_ERR_INVALID_ARG, "epilogue: at most 4 extra inputs")
+        e.n_ops = len(epilogue.ops)
+        for i, op in enumerate(epilogue.ops):
+            kind = op["kind"]
+            if kind == "none":
+                e.ops[i] = B.EpilogueOp(B.TL_EPI_NONE, 0, 0, 0)
+            elif kind == "bias":
+                e.ops[i] = B.EpilogueOp(B.TL_EPI_BIAS, 0, op["inputIndex"], 0)
+            elif kind == "unary":
+                if op["op"] not in B.TL_UNARY:
+                    raise TlError(B.TL_ERR_UNSUPPORTED, f"epilogue: unsupported unary op {op['op']}")
+                e.ops[i] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY[op["op"]], 0, 0)
+            elif kind == "binary":
+                if op["op"] not in B.TL_BINARY:
+                    raise TlError(B.TL_ERR_UNSUPPORTED, f"epilogue: unsupported binary op {op['op']}")
+                e.ops[i] = B.EpilogueOp(B.TL_EPI_BINARY, B.TL_BINARY[op["op"]], op["inputIndex"], 0)
+            elif kind == "cast":
+                e.ops[i] = B.EpilogueOp(B.TL_EPI_CAST, 0, 0, B.DTYPE_ID[op["toDtype"]])
+            else:
+                raise TlError(B.TL_ERR_INVALID_ARG, f"epilogue: unknown op kind {kind}")
+        e.n_inputs = len(epilogueInputs)
+        for i, t in enumerate(epilogueInputs):
+            if t.dtype != "f32":
+                raise TlError(B.TL_ERR_UNSUPPORTED, "epilogue inputs must be f32")
+            e.inputs[i] = t.buffer
+        return e
+
+    # -- the hot path ---------------------------------------------------------
+    def dispatchQuantizedGemvNT(self, aBuffer: CudaTensor, packedWeight: CudaTensor, scales: CudaTensor,
+                                outBuffer: CudaTensor, n: int, k: int, groupSize: int, outputDtype: str = "f32",
+                                alpha: float = 1.0, *, m: int = 1, epilogue: Optional[EpilogueConfig] = None,
+                                epilogueInputs: Sequence[CudaTensor] = (), packing: Optional[QuantPacking] = None):
+        """dispatch.ts:875-931.  ``m``, ``epilogue`` and ``packing`` are the
+        widenings; with the defaults the call is the reference's."""
+        if packing is None:
+            packing = QuantPacking("int8-grouped", groupSize, "f16" if scales.dtype == "u16" else "f32")
+        q = self._qdesc(packing)
+        e = self._epilogue(epilogue, epilogueInputs)
+        B.check(self._ctx, self._lib.tl_qgemv_nt(
+            self._ctx, aBuffer.buffer, B.DTYPE_ID[aBuffer.dtype], packedWeight.buffer, scales.buffer,
+            outBuffer.buffer, B.DTYPE_ID[outputDtype], m, n, k, C.byref(q), alpha,
+            C.byref(e) if e is not None else None))
+
+    def dispatchDequantizeInt8Grouped(self, packedWeight: CudaTensor, scales: CudaTensor, outBuffer: CudaTensor,
+                                      n: int, k: int, groupSize: int, *, packing: Optional[QuantPacking] = None):
+        """dispatch.ts:949-1037: explicit dequant to [N,K] of outBuffer.dtype."""
+        if packing is None:
+            packing = QuantPacking("int8-grouped", groupSize, "f16" if scales.dtype == "u16" else "f32")
+        q = self._qdesc(packing)
+        B.check(self._ctx, self._lib.tl_dequant_int8(self._ctx, packedWeight.buffer, scales.buffer, outBuffer.buffer,
+                                                     B.DTYPE_ID[outBuffer.dtype], n, k, C.byref(q)))
+
+    def unpackInt8(self, packedWeight: CudaTensor, n: int, k: int) -> np.ndarray:
+        out = self.ops.empty([n, k], "i8")
+        B.check(self._ctx, self._lib.tl_unpack_int8(self._ctx, packedWeight.buffer, out.buffer, n, k))
+        r = self.ops.read(out)
+        out.destroy()
+        return r
+
+    def _matmulQuantizedB(self, a: CudaTensor, b: CudaTensor, options: dict) -> CudaTensor:
+        """matmul-ops.ts:113-182.  B is the transposed [K,N] view of a packed
+        [N,K] weight.  Every M goes to a fused-dequant kernel (small-batch GEMV
+        for M <= 16, tensor-core GEMM above), so no dequantized weight is ever
+        materialized; the reference falls back to explicit dequant for M > 1."""
+        packing = b.format.packing if b.format else None
+        scales = b.scales
+        if packing is None or scales is None:
+            raise TlError(B.TL_ERR_INVALID_ARG, "matmulQuantizedB: missing packing/scales on B operand")
+        if not b.transposed:
+            raise TlError(B.TL_ERR_UNSUPPORTED, "matmulQuantizedB: B must be the transposed view of the [N,K] weight")
+        k, n = b.shape[-2], b.shape[-1]
+        if a.shape[-1] != k:
+            raise TlError(B.TL_ERR_INVALID_ARG, "matmul dimension mismatch")
+        m = int(np.prod(a.shape[:-1])) if len(a.shape) > 1 else 1
+        epilogue: Optional[EpilogueConfig] = options.get("epilogue")
+        epilogueInputs = options.get("epilogueInputs", ())
+        out_dtype = epilogue.outputDtype if epilogue is not None else options.get("outputDtype", "f32")
+        out_shape = (a.shape[:-1] if len(a.shape) > 1 else [1]) + [n]
+        out = options.get("outBuffer") or self.ops.empty(out_shape, out_dtype)
+        q = self._qdesc(packing)
+        e = self._epilogue(epilogue, epilogueInputs)
+        B.check(self._ctx, self._lib.tl_qmatmul_nt(
+            self._ctx, a.buffer, B.DTYPE_ID[a.dtype], b.buffer, scales.buffer, out.buffer, B.DTYPE_ID[out_dtype],
+            m, n, k, C.byref(q), float(options.get("alpha", 1.0)), C.byref(e) if e is not None else None))
+        return out
+
+    def linear(self, x: CudaTensor, weight: CudaTensor, bias: Optional[CudaTensor] = None,
+               activation: Optional[str] = None, outputDtype: str = "f32") -> CudaTensor:
+        """api.linear (torchlette.ts:878-894): transpose(weight) -> matmul -> add
+        bias, with the following bias/activation/cast chain fused by the
+        epilogue decision (matmul-epilogue.ts:131-262)."""
+        chain = []
+        if bias is not None:
+            chain.append(("add", bias))
+        if activation is not None:
+            chain.append((activation, None))
+        if outputDtype != "f32":
+            chain.append(("cast", outputDtype))
+        plan = detectMatmulEpilogue(chain)
+        wT = self.ops.transpose(weight)
+        opts: dict = {"outputDtype": outputDtype}
+        if plan is not None:
+            opts["epilogue"], opts["epilogueInputs"], _ = plan
+        return self.ops.matmul(x, wT, opts)
+
+    # -- selection / counters / autotune --------------------------------------
+    def planQuantizedMatmul(self, m, n, k, aDtype, outDtype, packing: QuantPacking,
+                            epilogue: Optional[EpilogueConfig] = None):
+        q = self._qdesc(packing)
+        r = B.PlanReceipt()
+        e = None
+        if epilogue is not None:
+            e = B.Epilogue()
+            e.n_ops = 0  # geometry only; presence is reported through epilogue_engaged below
+        B.check(self._ctx, self._lib.tl_plan_qmatmul(self._ctx, m, n, k, B.DTYPE_ID[aDtype], B.DTYPE_ID[outDtype],
+                                                     C.byref(q), C.byref(e) if e is not None else None, C.byref(r)))
+        name = self._lib.tl_variant_name(C.byref(r.choice)).decode()
+        return {"family": "gemv" if r.choice.family == B.TL_FAMILY_QGEMV else "gemm", "variant": name,
+                "choice": r.choice.as_tuple(), "grid": list(r.grid), "block": r.block, "splitK": r.split_k,
+                "fromTuningCache": bool(r.from_tuning_cache)}
+
+    def forceVariant(self, choice: Optional[tuple]):
+        if choice is None:
+            B.check(self._ctx, self._lib.tl_force_variant(self._ctx, None))
+        else:
+            v = B.Variant(*choice)
+            B.check(self._ctx, self._lib.tl_force_variant(self._ctx, C.byref(v)))
+
+    def getQuantGemvDispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_QGEMV))
+
+    def getDequantI8DispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_DEQUANT))
+
+    def getGemvEpilogueDispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_QGEMV_EPILOGUE))
+
+    def getQuantGemmDispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_QGEMM))
+
+    def getKernelLaunchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_KERNEL_LAUNCHES))
+
+    def resetCounters(self):
+        B.check(self._ctx, self._lib.tl_counters_reset(self._ctx))
+
+    def setAutotuneEnabled(self, enabled: bool):
+        B.check(self._ctx, self._lib.tl_autotune_set_enabled(self._ctx, 1 if enabled else 0))
+
+    def isAutotuneEnabled(self) -> bool:
+        return bool(self._lib.tl_autotune_is_enabled(self._ctx))
+
+    def pretuneMatmulShapes(self, shapes, aDtype: str, outDtype: str, packing: QuantPacking):
+        arr = (B.Shape * len(shapes))(*[B.Shape(*s) for s in shapes])
+        q = self._qdesc(packing)
+        B.check(self._ctx, self._lib.tl_pretune(self._ctx, arr, len(shapes), B.DTYPE_ID[aDtype],
+                                                B.DTYPE_ID[outDtype], C.byref(q)))
+
+    def seedPerShapeMatmulChoice(self, m, n, k, aDtype, packing: QuantPacking, choice: tuple):
+        q = self._qdesc(packing)
+        v = B.Variant(*choice)
+        B.check(self._ctx, self._lib.tl_tune_seed(self._ctx, m, n, k, B.DTYPE_ID[aDtype], C.byref(q), C.byref(v)))
+
+    def getPerShapeMatmulChoice(self, m, n, k, aDtype, packing: QuantPacking):
+        q = self._qdesc(packing)
+        v = B.Variant()
+        found = self._lib.tl_tune_get(self._ctx, m, n, k, B.DTYPE_ID[aDtype], C.byref(q), C.byref(v))
+        if found < 0:
+            B.check(self._ctx, found)
+        return v.as_tuple() if found == 1 else None
+
+    def clearPerShapeMatmulChoices(self):
+        B.check(self._ctx, self._lib.tl_tune_clear(self._ctx))
+
+    def getAutotuneRunCount(self) -> int:
+        return int(self._lib.tl_tune_run_count(self._ctx))
+
+    def exportTuningCache(self) -> str:
+        need = C.c_size_t()
+        B.check(self._ctx, self._lib.tl_tune_export_json(self._ctx, None, 0, C.byref(need)))
+        buf = C.create_string_buffer(need.value)
+        B.check(self._ctx, self._lib.tl_tune_export_json(self._ctx, buf, need.value, C.byref(need)))
+        return buf.value.decode()
+
+    def importTuningCache(self, text: str):
+        B.check(self._ctx, self._lib.tl_tune_import_json(self._ctx, text.encode()))
+
+    # -- replay ---------------------------------------------------------------
+    def beginCapture(self):
+        B.check(self._ctx, self._lib.tl_graph_begin(self._ctx))
+
+    def endCapture(self) -> int:
+        g = C.c_void_p()
+        B.check(self._ctx, self._lib.tl_graph_end(self._ctx, C.byref(g)))
+        return g.value
+
+    def replay(self, graph: int):
+        B.check(self._ctx, self._lib.tl_graph_launch(self._ctx, C.c_void_p(graph)))
+
+    def destroyGraph(self, graph: int):
+        B.check(self._ctx, self._lib.tl_graph_destroy(self._ctx, C.c_void_p(graph)))
+
+
+_backend: Optional[CudaBackend] = None
+_init_error: Optional[str] = None
+
+
+def initCuda(device: int = 0) -> bool:
+    """initWebGPU's counterpart (src/backend/webgpu/index.ts:39-70): returns
+    False and records the error when no usable device/library exists."""
+    global _backend, _init_error
+    if _backend is not None:
+        return True
+    try:
+        _backend = CudaBackend(device)
+        return True
+    except (TlError, ImportError, OSError) as e:  # no GPU, or library not built
+        _init_error = str(e)
+        return False
+
+
+def getCudaInitError() -> Optional[str]:
+    return _init_error
+
+
+def getBackend() -> CudaBackend:
+    if _backend is None and not initCuda():
+        raise RuntimeError(f"cuda backend unavailable: {_init_error}")
+    return _backend
+
+
+def destroyCuda():
+    global _backend
+    if _backend is not None:
+        _backend.destroy()
+        _backend = None

@@ -1,0 +1,216 @@
+// Shared internals of libtlcuda: the context object, error plumbing, dtype
+// helpers and the fused-epilogue evaluator used by every kernel family.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/tlcuda.h"
+
+// ---------------------------------------------------------------------------
+// Context
+// ---------------------------------------------------------------------------
+struct TuneKey {
+  int64_t m, n, k;
+  int32_t a_dtype, group, scales_dtype, convention;
+  bool operator<(const TuneKey& o) const {
+    if (m != o.m) return m < o.m;
+    if (n != o.n) return n < o.n;
+    if (k != o.k) return k < o.k;
+    if (a_dtype != o.a_dtype) return a_dtype < o.a_dtype;
+    if (group != o.group) return group < o.group;
+    if (scales_dtype != o.scales_dtype) return scales_dtype < o.scales_dtype;
+    return convention < o.convention;
+  }
+};
+
+struct tl_ctx {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  int sm_count = 0;
+  int l2_bytes = 0;
+  int64_t counters[TL_COUNTER_COUNT] = {0, 0, 0, 0, 0};
+  int64_t async_errors = 0;
+  std::string last_error;
+  // library-owned scratch (split-K partials, GEMM staging), grown on demand and
+  // kept until teardown (the reference caches its K-split scratch the same way:
+  // src/backend/webgpu/matmul/dispatch.ts:695-718)
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  // selection
+  bool has_forced = false;
+  tl_variant forced{};
+  bool autotune_enabled = false;
+  int64_t tune_runs = 0;
+  std::map<TuneKey, tl_variant> tuned;
+  bool capturing = false;
+  // multi-GPU
+  void* nccl_comm = nullptr;
+  int rank = 0, world = 1;
+};
+
+int32_t tl_set_error(tl_ctx* ctx, int32_t code, const char* fmt, ...);
+int32_t tl_ensure_scratch(tl_ctx* ctx, size_t bytes, void** out);
+
+#define TL_CHECK_CTX(ctx)                                                       \
+  do {                                                                          \
+    if ((ctx) == nullptr) return tl_set_error(nullptr, TL_ERR_INVALID_ARG, "%s: null context", __func__); \
+  } while (0)
+
+#define TL_CUDA(ctx, expr)                                                      \
+  do {                                                                          \
+    cudaError_t _e = (expr);                                                    \
+    if (_e != cudaSuccess) {                                                    \
+      if (ctx) (ctx)->async_errors++;                                           \
+      return tl_set_error((ctx), TL_ERR_CUDA, "%s: %s failed: %s", __func__, #expr, cudaGetErrorString(_e)); \
+    }                                                                           \
+  } while (0)
+
+// Sets the calling thread's current device to the context's for one scope.
+struct DeviceGuard {
+  int prev = -1;
+  explicit DeviceGuard(int dev) {
+    cudaGetDevice(&prev);
+    if (prev != dev) cudaSetDevice(dev);
+    else prev = -1;
+  }
+  ~DeviceGuard() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+static inline size_t tl_dtype_size(int32_t dt) { return dt == TL_F32 ? 4 : 2; }
+static inline bool tl_dtype_valid(int32_t dt) { return dt == TL_F32 || dt == TL_F16 || dt == TL_BF16; }
+static inline const char* tl_dtype_name(int32_t dt) {
+  return dt == TL_F32 ? "f32" : dt == TL_F16 ? "f16" : dt == TL_BF16 ? "bf16" : "?";
+}
+
+// ---------------------------------------------------------------------------
+// Epilogue parameters as passed (by value) to kernels
+// ---------------------------------------------------------------------------
+struct EpiParams {
+  int32_t n_ops;
+  int32_t kind[TL_EPI_MAX_OPS];
+  int32_t op[TL_EPI_MAX_OPS];
+  int32_t idx[TL_EPI_MAX_OPS];  // input index (bias/binary) or to_dtype (cast)
+  const float* inputs[TL_EPI_MAX_INPUTS];
+  float alpha;
+};
+
+// Validates an epilogue description and flattens it; returns TL_OK or an error
+// (with the message set on ctx).
+int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* out, bool* has_ops);
+
+// Common argument validation of the quantized entry points.
+int32_t tl_check_qargs(tl_ctx* ctx, const char* who, const void* a, int32_t a_dtype,
+                       const void* packed, const void* scales, const void* out, int32_t out_dtype,
+                       int64_t m, int64_t n, int64_t k, const tl_quant_desc* q);
+
+// Launchers implemented by the kernel translation units.
+int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t a_dtype,
+                        const void* packed, const void* scales, void* out, int32_t out_dtype,
+                        int32_t m, int64_t n, int64_t k, const tl_quant_desc& q,
+                        const EpiParams& epi, tl_plan_receipt* receipt_only);
+int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t a_dtype,
+                        const void* packed, const void* scales, void* out, int32_t out_dtype,
+                        int64_t m, int64_t n, int64_t k, const tl_quant_desc& q,
+                        const EpiParams& epi, tl_plan_receipt* receipt_only);
+int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
+                                 const tl_quant_desc& q, tl_variant* out);
+int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
+                            const tl_quant_desc& q, std::vector<tl_variant>* out);
+int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                                 const tl_quant_desc& q, tl_variant* out);
+int32_t tl_qgemm_candidates(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                            const tl_quant_desc& q, std::vector<tl_variant>* out);
+bool tl_variant_applicable(tl_ctx* ctx, const tl_variant& v, int64_t m, int64_t n, int64_t k,
+                           int32_t a_dtype, const tl_quant_desc& q);
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------
+// Device helpers
+// ---------------------------------------------------------------------------
+template <typename T> struct DT;
+template <> struct DT<float> {
+  static constexpr int id = TL_F32;
+  __device__ static float to_f32(float v) { return v; }
+  __device__ static float from_f32(float v) { return v; }
+};
+template <> struct DT<__half> {
+  static constexpr int id = TL_F16;
+  __device__ static float to_f32(__half v) { return __half2float(v); }
+  __device__ static __half from_f32(float v) { return __float2half_rn(v); }
+};
+template <> struct DT<__nv_bfloat16> {
+  static constexpr int id = TL_BF16;
+  __device__ static float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+  __device__ static __nv_bfloat16 from_f32(float v) { return __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float tl_load_scale(const void* scales, int scales_dtype, int64_t idx) {
+  return scales_dtype == TL_F16 ? __half2float(reinterpret_cast<const __half*>(scales)[idx])
+                                : reinterpret_cast<const float*>(scales)[idx];
+}
+
+// Activation bodies in f32: the reference's GPU path folds the same terms to
+// f32 (src/backend/webgpu/fusion-tile-ir.ts:44-78); the CPU path evaluates them
+// in f64 (src/ops/semantic/interpret.ts:25-98).
+__device__ __forceinline__ float tl_unary(int op, float x) {
+  switch (op) {
+    case TL_UNARY_RELU: return x > 0.f ? x : 0.f;
+    case TL_UNARY_SILU: return x / (1.f + expf(-x));
+    case TL_UNARY_SIGMOID: return 1.f / (1.f + expf(-x));
+    case TL_UNARY_TANH: return tanhf(x);
+    case TL_UNARY_GELU_TANH:
+      return (0.5f * x) * (1.f + tanhf(0.7978845608f * (x + 0.044715f * (x * (x * x)))));
+    case TL_UNARY_GELU_ERF: {
+      // Abramowitz-Stegun 7.1.26, the polynomial the reference uses for erf
+      // (src/ops/semantic/erf.ts:28-56)
+      float u = x * 0.70710678118654752f;
+      float ax = fabsf(u);
+      float t = 1.f / (1.f + 0.3275911f * ax);
+      float poly = ((((1.061405429f * t - 1.453152027f) * t + 1.421413741f) * t - 0.284496736f) * t +
+                    0.254829592f) * t;
+      float er = 1.f - poly * expf(-ax * ax);
+      return (0.5f * x) * (1.f + (u < 0.f ? -er : er));
+    }
+    default: return x;
+  }
+}
+
+// v = acc (unscaled by alpha); row/col index the [M,N] output.
+__device__ __forceinline__ float tl_apply_epilogue(const EpiParams& e, float v, int64_t row,
+                                                   int64_t col, int64_t n) {
+  v *= e.alpha;
+#pragma unroll 1
+  for (int i = 0; i < e.n_ops; ++i) {
+    const int kind = e.kind[i];
+    if (kind == TL_EPI_BIAS) {
+      v += __ldg(e.inputs[e.idx[i]] + col);
+    } else if (kind == TL_EPI_UNARY) {
+      v = tl_unary(e.op[i], v);
+    } else if (kind == TL_EPI_BINARY) {
+      float o = __ldg(e.inputs[e.idx[i]] + row * n + col);
+      v = e.op[i] == TL_BINARY_ADD ? v + o : e.op[i] == TL_BINARY_SUB ? v - o : v * o;
+    } else if (kind == TL_EPI_CAST) {
+      if (e.idx[i] == TL_F16) v = __half2float(__float2half_rn(v));
+      else if (e.idx[i] == TL_BF16) v = __bfloat162float(__float2bfloat16_rn(v));
+    }
+  }
+  return v;
+}
+
+__device__ __forceinline__ void tl_store_out(void* out, int out_dtype, int64_t idx, float v) {
+  if (out_dtype == TL_F32) reinterpret_cast<float*>(out)[idx] = v;
+  else if (out_dtype == TL_F16) reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+  else reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+}
+#endif  // __CUDACC__

@@ -1,0 +1,536 @@
+// Small-batch (m = 1..16) weight-only int8 matmul: out[m,n] = epi(alpha * a[m,k] . W[n,k]).
+// HBM-bound: the int8 weight is streamed once with 128-bit loads, dequantized in
+// registers and never materialized.  Replaces the WGSL GEMV builder
+// (src/backend/webgpu/matmul/gemv.ts:311-466, quant load :400-429).
+//
+// Kernel ids (tl_variant.kernel) of family TL_FAMILY_QGEMV:
+//   0 "scalar" one lane per packed word, per-element dequant in the reference's
+//              own order; any K % 4 == 0 and any group size.  The fallback.
+//   1 "simt"   one warp per R rows, 16-byte weight loads, byte->f32 by exponent
+//              stuffing (prmt), f32 FMA, per-chunk group scale.  K % 16 == 0,
+//              G % 16 == 0.  Exact f32 activations.
+//   2 "mma"    one CTA per 16 rows, warps interleaved over 64-wide k blocks, raw
+//              bytes -> f16/bf16 pairs in registers -> mma.sync m16n8k16 with f32
+//              accumulators; the batch is the MMA n dimension.  f16/bf16
+//              activations, K % 64 == 0, G % 64 == 0.
+// Variant parameters: p0 = warps per CTA, p1 = rows per warp (simt) / unused,
+// p2 = k-split cluster size (mma; 1 = none), p3 = reserved.
+#include <algorithm>
+
+#include "tl_common.cuh"
+
+namespace {
+
+constexpr int kScalar = 0, kSimt = 1, kMma = 2;
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  // weights are read exactly once: keep them out of L1
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+struct GemvArgs {
+  const void* a;
+  const uint32_t* packed;
+  const void* scales;
+  void* out;
+  int32_t m, n, k;
+  int32_t group, groups_per_row;
+  int32_t scales_dtype, out_dtype;
+  float wscale;    // 1/127 for the snorm convention, 1 for direct
+  int32_t row0;    // first batch row of this launch (epilogue binary inputs index absolute rows)
+  int32_t m_total;
+};
+
+// ---------------------------------------------------------------------------
+// 0: scalar fallback.  One warp per output row; lane l walks words l, l+32, ...
+// Element arithmetic as in the reference kernel: acc += a[k] * ((q/127) * s).
+// ---------------------------------------------------------------------------
+template <typename AT>
+__global__ void __launch_bounds__(256) qgemv_scalar_kernel(GemvArgs p, EpiParams epi) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row = int64_t(blockIdx.x) * warps + (threadIdx.x >> 5);
+  if (row >= p.n) return;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const int words = p.k >> 2;
+  const uint32_t* wrow = p.packed + row * words;
+  float acc[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) acc[i] = 0.f;
+  for (int w = lane; w < words; w += 32) {
+    const uint32_t word = __ldg(wrow + w);
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int kk = 4 * w + b;
+      const float s = tl_load_scale(p.scales, p.scales_dtype, row * p.groups_per_row + kk / p.group);
+      const int q = int(int8_t((word >> (8 * b)) & 0xffu));
+      const float wv = (float(q) * p.wscale) * s;
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (i < p.m) acc[i] = fmaf(DT<AT>::to_f32(a[int64_t(i) * p.k + kk]), wv, acc[i]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (i < p.m) {
+      const float v = warp_sum(acc[i]);
+      if (lane == 0) {
+        const float r = tl_apply_epilogue(epi, v, p.row0 + i, row, p.n);
+        tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + i) * p.n + row, r);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 1: SIMT.  Byte b of x = word ^ 0x80808080 is q+128; prmt drops it into the
+// low mantissa byte of 0x4B000000 (2^23), so the float is 2^23 + 128 + q exactly
+// and one subtraction yields q.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void bytes_to_f32(uint32_t word, float (&f)[4]) {
+  const uint32_t x = word ^ 0x80808080u;
+  f[0] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f;
+  f[1] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f;
+  f[2] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f;
+  f[3] = __uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f;
+}
+
+template <typename AT> struct ActChunk;  // 16 activations of one batch row as f32
+template <> struct ActChunk<float> {
+  __device__ static void load(const float* p, float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(p) + i);
+      x[4 * i] = v.x; x[4 * i + 1] = v.y; x[4 * i + 2] = v.z; x[4 * i + 3] = v.w;
+    }
+  }
+};
+template <> struct ActChunk<__half> {
+  __device__ static void load(const __half* p, float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        x[8 * i + 2 * j] = f.x; x[8 * i + 2 * j + 1] = f.y;
+      }
+    }
+  }
+};
+template <> struct ActChunk<__nv_bfloat16> {
+  __device__ static void load(const __nv_bfloat16* p, float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p) + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        x[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+        x[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+  }
+};
+
+// MT batch rows, R output rows per warp.  Lane l handles 16-byte chunks l, l+32, ...
+template <typename AT, int MT, int R, bool GROUPED>
+__global__ void __launch_bounds__(256) qgemv_simt_kernel(GemvArgs p, EpiParams epi) {
+  const int warps = blockDim.x >> 5, lane = threadIdx.x & 31;
+  const int64_t row_base = (int64_t(blockIdx.x) * warps + (threadIdx.x >> 5)) * R;
+  if (row_base >= p.n) return;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const int chunks = p.k >> 4;
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  int64_t rows[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) rows[r] = min(row_base + r, int64_t(p.n) - 1);  // tail rows clamp, stores mask
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int i = 0; i < MT; ++i) acc[r][i] = 0.f;
+
+  for (int c = lane; c < chunks; c += 32) {
+    uint4 wv[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) wv[r] = ldg_stream(wbytes + rows[r] * p.k + int64_t(c) * 16);
+    float x[MT][16];
+#pragma unroll
+    for (int i = 0; i < MT; ++i) ActChunk<AT>::load(a + int64_t(i) * p.k + int64_t(c) * 16, x[i]);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const uint32_t w4[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+      float part[MT];
+#pragma unroll
+      for (int i = 0; i < MT; ++i) part[i] = GROUPED ? 0.f : acc[r][i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float f[4];
+        bytes_to_f32(w4[j], f);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+#pragma unroll
+          for (int i = 0; i < MT; ++i) part[i] = fmaf(f[b], x[i][4 * j + b], part[i]);
+      }
+      if (GROUPED) {
+        const float s = tl_load_scale(p.scales, p.scales_dtype, rows[r] * p.groups_per_row + (c * 16) / p.group);
+#pragma unroll
+        for (int i = 0; i < MT; ++i) acc[r][i] = fmaf(s, part[i], acc[r][i]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < MT; ++i) acc[r][i] = part[i];
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int64_t row = row_base + r;
+    float s = p.wscale;
+    if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, rows[r]);
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      const float v = warp_sum(acc[r][i]) * s;
+      if (lane == 0 && row < p.n) {
+        const float o = tl_apply_epilogue(epi, v, p.row0 + i, row, p.n);
+        tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + i) * p.n + row, o);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 2: tensor-core small-batch kernel.
+//
+// CTA = W warps, one 16-row weight tile.  Warp w owns k blocks kb = w, w+W, ...
+// (64 bytes of every row each), so at any moment the CTA reads W*64 contiguous
+// bytes per row.  Thread (g = lane/4, t = lane%4) loads 16 bytes of row g and of
+// row g+8 at k = 64*kb + 16*t.  Word j of that chunk feeds MMA j of the block:
+// its bytes 0,1 sit in k slots 2t,2t+1 and bytes 2,3 in slots 2t+8,2t+9.  The
+// k order inside a block is therefore permuted, identically for the weight (A)
+// and activation (B) fragments, which leaves the dot product unchanged.
+// B for MMA j: halves [4j, 4j+4) of the thread's 16 contiguous activations of
+// batch row g (columns of the MMA n dimension = batch rows).
+// ---------------------------------------------------------------------------
+template <typename AT> struct MmaOps;
+template <> struct MmaOps<__half> {
+  // bytes (b0,b1) / (b2,b3) of x = word ^ 0x80808080 -> f16 pairs holding q exactly:
+  // 0x6400 | u is 1024 + u; subtracting 1152 (0x6480) leaves u - 128 = q.
+  __device__ static void cvt(uint32_t word, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x = word ^ 0x80808080u;
+    uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);
+    uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
+    const uint32_t magic = 0x64806480u;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(l), "r"(magic));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h), "r"(magic));
+  }
+  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                             uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+template <> struct MmaOps<__nv_bfloat16> {
+  // bf16 keeps 8 significant bits, so the byte cannot be stuffed whole.  With s the
+  // sign bit and l the low 7 bits of the raw byte, q = l - 128*s:
+  // (0x4300 | l) is 128 + l and (0x4300 | s<<7) is 128 or 256; their difference is q.
+  __device__ static void cvt(uint32_t word, uint32_t& lo, uint32_t& hi) {
+    const uint32_t l = __byte_perm(word, 0u, 0x4140);  // [b0,0,b1,0]
+    const uint32_t h = __byte_perm(word, 0u, 0x4342);
+    const uint32_t lm = (l & 0x007f007fu) | 0x43004300u, lc = (l & 0x00800080u) | 0x43004300u;
+    const uint32_t hm = (h & 0x007f007fu) | 0x43004300u, hc = (h & 0x00800080u) | 0x43004300u;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(lm), "r"(lc));
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(hm), "r"(hc));
+  }
+  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                             uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+  }
+};
+
+constexpr int kMmaMaxWarps = 16;
+
+// NT = number of 8-wide batch tiles (1: m <= 8, 2: m <= 16); UNROLL k blocks in flight per warp.
+template <typename AT, int NT, bool GROUPED, int UNROLL>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_mma_kernel(GemvArgs p, EpiParams epi) {
+  __shared__ float red[kMmaMaxWarps][NT][4][32];
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t tile_row = int64_t(blockIdx.x) * 16;
+  const int64_t r_lo = min(tile_row + g, int64_t(p.n) - 1);
+  const int64_t r_hi = min(tile_row + g + 8, int64_t(p.n) - 1);
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  const uint8_t* w_lo = wbytes + r_lo * p.k + 16 * t;
+  const uint8_t* w_hi = wbytes + r_hi * p.k + 16 * t;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  // batch rows this thread supplies as MMA columns: g (tile 0) and g+8 (tile 1)
+  const AT* a_col[NT];
+  bool a_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    a_ok[nt] = (g + 8 * nt) < p.m;
+    a_col[nt] = a + int64_t(a_ok[nt] ? g + 8 * nt : 0) * p.k + 16 * t;
+  }
+  const int kblocks = p.k >> 6;
+
+  float total[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
+
+  for (int kb0 = warp; kb0 < kblocks; kb0 += warps * UNROLL) {
+    uint4 wl[UNROLL], wh[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int kb = kb0 + u * warps;
+      if (kb < kblocks) {
+        wl[u] = ldg_stream(w_lo + int64_t(kb) * 64);
+        wh[u] = ldg_stream(w_hi + int64_t(kb) * 64);
+      } else {
+        wl[u] = make_uint4(0x0, 0x0, 0x0, 0x0);
+        wh[u] = make_uint4(0x0, 0x0, 0x0, 0x0);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int kb = kb0 + u * warps;
+      if (kb >= kblocks) break;
+      uint4 bx[NT][2];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        if (a_ok[nt]) {
+          const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(kb) * 64);
+          bx[nt][0] = __ldg(src);
+          bx[nt][1] = __ldg(src + 1);
+        } else {
+          bx[nt][0] = make_uint4(0, 0, 0, 0);
+          bx[nt][1] = make_uint4(0, 0, 0, 0);
+        }
+      }
+      float c[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) c[nt][i] = GROUPED ? 0.f : total[nt][i];
+      const uint32_t wlo[4] = {wl[u].x, wl[u].y, wl[u].z, wl[u].w};
+      const uint32_t whi[4] = {wh[u].x, wh[u].y, wh[u].z, wh[u].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t a0, a1, a2, a3;
+        MmaOps<AT>::cvt(wlo[j], a0, a2);  // row g   : slots (2t,2t+1) and (2t+8,2t+9)
+        MmaOps<AT>::cvt(whi[j], a1, a3);  // row g+8
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4 v = bx[nt][j >> 1];
+          const uint32_t b0 = (j & 1) ? v.z : v.x, b1 = (j & 1) ? v.w : v.y;
+          MmaOps<AT>::mma(c[nt], a0, a1, a2, a3, b0, b1);
+        }
+      }
+      if (GROUPED) {
+        const int gi = (kb * 64) / p.group;
+        const float s_lo = tl_load_scale(p.scales, p.scales_dtype, r_lo * p.groups_per_row + gi);
+        const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + gi);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          total[nt][0] = fmaf(s_lo, c[nt][0], total[nt][0]);
+          total[nt][1] = fmaf(s_lo, c[nt][1], total[nt][1]);
+          total[nt][2] = fmaf(s_hi, c[nt][2], total[nt][2]);
+          total[nt][3] = fmaf(s_hi, c[nt][3], total[nt][3]);
+        }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) total[nt][i] = c[nt][i];
+      }
+    }
+  }
+
+  // cross-warp sum of the k partitions, then scale + epilogue + store
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[warp][nt][i][lane] = total[nt][i];
+  __syncthreads();
+  // one thread per (tile nt, fragment slot i, lane): NT*128 outputs
+  for (int o = threadIdx.x; o < NT * 128; o += blockDim.x) {
+    const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+    float v = 0.f;
+    for (int w = 0; w < warps; ++w) v += red[w][nt][i][ln];
+    const int gg = ln >> 2, tt = ln & 3;
+    const int64_t row = tile_row + gg + ((i & 2) ? 8 : 0);  // c0,c1: row g ; c2,c3: row g+8
+    const int col = 8 * nt + 2 * tt + (i & 1);                // batch row
+    if (row < p.n && col < p.m) {
+      float s = p.wscale;
+      if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
+      const float r = tl_apply_epilogue(epi, v * s, p.row0 + col, row, p.n);
+      tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+template <typename AT, int MT, int R>
+void launch_simt(bool grouped, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (grouped) qgemv_simt_kernel<AT, MT, R, true><<<grid, block, 0, s>>>(p, e);
+  else qgemv_simt_kernel<AT, MT, R, false><<<grid, block, 0, s>>>(p, e);
+}
+template <typename AT, int R>
+void launch_simt_m(int mt, bool grouped, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  switch (mt) {
+    case 1: launch_simt<AT, 1, R>(grouped, grid, block, s, p, e); break;
+    case 2: launch_simt<AT, 2, R>(grouped, grid, block, s, p, e); break;
+    case 3: launch_simt<AT, 3, R>(grouped, grid, block, s, p, e); break;
+    default: launch_simt<AT, 4, R>(grouped, grid, block, s, p, e); break;
+  }
+}
+template <typename AT>
+void launch_simt_r(int r, int mt, bool grouped, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (r >= 4) launch_simt_m<AT, 4>(mt, grouped, grid, block, s, p, e);
+  else if (r >= 2) launch_simt_m<AT, 2>(mt, grouped, grid, block, s, p, e);
+  else launch_simt_m<AT, 1>(mt, grouped, grid, block, s, p, e);
+}
+
+template <typename AT, int NT>
+void launch_mma(bool grouped, int unroll, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (grouped) {
+    if (unroll >= 4) qgemv_mma_kernel<AT, NT, true, 4><<<grid, block, 0, s>>>(p, e);
+    else qgemv_mma_kernel<AT, NT, true, 2><<<grid, block, 0, s>>>(p, e);
+  } else {
+    if (unroll >= 4) qgemv_mma_kernel<AT, NT, false, 4><<<grid, block, 0, s>>>(p, e);
+    else qgemv_mma_kernel<AT, NT, false, 2><<<grid, block, 0, s>>>(p, e);
+  }
+}
+
+}  // namespace
+
+bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                                 const tl_quant_desc& q) {
+  (void)n;
+  if (v.family != TL_FAMILY_QGEMV || m < 1 || m > 16) return false;
+  if (v.p0 < 1 || v.p0 > kMmaMaxWarps) return false;
+  switch (v.kernel) {
+    case kScalar: return v.p0 <= 8;
+    case kSimt: return v.p0 <= 8 && k % 16 == 0 && q.group_size % 16 == 0 && (v.p1 == 1 || v.p1 == 2 || v.p1 == 4);
+    case kMma:
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
+             (v.p1 == 2 || v.p1 == 4);
+    default: return false;
+  }
+}
+
+int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
+                                 const tl_quant_desc& q, tl_variant* out) {
+  (void)ctx; (void)n; (void)m;
+  tl_variant v{};
+  v.family = TL_FAMILY_QGEMV;
+  if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
+    v.kernel = kMma; v.p0 = 8; v.p1 = 4; v.p2 = 1;
+  } else if (k % 16 == 0 && q.group_size % 16 == 0) {
+    v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
+  } else {
+    v.kernel = kScalar; v.p0 = 8;
+  }
+  *out = v;
+  return TL_OK;
+}
+
+int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
+                            const tl_quant_desc& q, std::vector<tl_variant>* out) {
+  tl_variant d;
+  tl_qgemv_default_variant(ctx, m, n, k, a_dtype, q, &d);
+  out->clear();
+  out->push_back(d);  // the default is always a candidate (variants.ts:194-205)
+  auto add = [&](int kernel, int p0, int p1) {
+    tl_variant v{};
+    v.family = TL_FAMILY_QGEMV; v.kernel = kernel; v.p0 = p0; v.p1 = p1; v.p2 = 1;
+    if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q)) return;
+    for (const auto& o : *out)
+      if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1) return;
+    out->push_back(v);
+  };
+  for (int w : {4, 8, 16})
+    for (int u : {2, 4}) add(kMma, w, u);
+  if (m <= 4 || a_dtype == TL_F32)
+    for (int w : {4, 8})
+      for (int r : {1, 2, 4}) add(kSimt, w, r);
+  return TL_OK;
+}
+
+int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t a_dtype, const void* packed,
+                        const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n, int64_t k,
+                        const tl_quant_desc& q, const EpiParams& epi, tl_plan_receipt* receipt) {
+  if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q))
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "qgemv: variant %s cannot run m=%d n=%lld k=%lld G=%d %s",
+                        tl_variant_name(&v), m, (long long)n, (long long)k, q.group_size, tl_dtype_name(a_dtype));
+  GemvArgs p{};
+  p.a = a; p.packed = reinterpret_cast<const uint32_t*>(packed); p.scales = scales; p.out = out;
+  p.m = m; p.n = int32_t(n); p.k = int32_t(k);
+  p.group = q.group_size; p.groups_per_row = int32_t(k / q.group_size);
+  p.scales_dtype = q.scales_dtype; p.out_dtype = out_dtype;
+  p.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+  p.row0 = 0; p.m_total = m;
+  const bool grouped = q.group_size != k;
+  const int block = v.p0 * 32;
+  int grid = 0, launches = 1;
+  if (v.kernel == kScalar) grid = int((n + v.p0 - 1) / v.p0);
+  else if (v.kernel == kSimt) { grid = int((n + int64_t(v.p0) * v.p1 - 1) / (int64_t(v.p0) * v.p1)); launches = (m + 3) / 4; }
+  else grid = int((n + 15) / 16);
+  if (receipt) {
+    receipt->choice = v;
+    receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = launches;
+    receipt->block = block; receipt->split_k = 1;
+    return TL_OK;
+  }
+  if (v.kernel != kScalar) {
+    // 16-byte vector loads need 16-byte aligned bases (rows are K bytes apart, K % 16 == 0)
+    if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
+      return tl_set_error(ctx, TL_ERR_INVALID_ARG, "qgemv: %s needs 16-byte aligned weight and activation pointers",
+                          tl_variant_name(&v));
+  }
+  cudaStream_t s = ctx->stream;
+  if (v.kernel == kScalar) {
+    if (a_dtype == TL_F32) qgemv_scalar_kernel<float><<<grid, block, 0, s>>>(p, epi);
+    else if (a_dtype == TL_F16) qgemv_scalar_kernel<__half><<<grid, block, 0, s>>>(p, epi);
+    else qgemv_scalar_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(p, epi);
+  } else if (v.kernel == kSimt) {
+    // batch rows go through in slices of four; each slice re-streams the weight
+    for (int m0 = 0; m0 < m; m0 += 4) {
+      GemvArgs ps = p;
+      const int mt = std::min(4, m - m0);
+      ps.m = mt; ps.row0 = m0;
+      ps.a = reinterpret_cast<const uint8_t*>(a) + size_t(m0) * k * tl_dtype_size(a_dtype);
+      if (a_dtype == TL_F32) launch_simt_r<float>(v.p1, mt, grouped, grid, block, s, ps, epi);
+      else if (a_dtype == TL_F16) launch_simt_r<__half>(v.p1, mt, grouped, grid, block, s, ps, epi);
+      else launch_simt_r<__nv_bfloat16>(v.p1, mt, grouped, grid, block, s, ps, epi);
+    }
+  } else {
+    const bool two = m > 8;
+    if (a_dtype == TL_F16) {
+      if (two) launch_mma<__half, 2>(grouped, v.p1, grid, block, s, p, epi);
+      else launch_mma<__half, 1>(grouped, v.p1, grid, block, s, p, epi);
+    } else {
+      if (two) launch_mma<__nv_bfloat16, 2>(grouped, v.p1, grid, block, s, p, epi);
+      else launch_mma<__nv_bfloat16, 1>(grouped, v.p1, grid, block, s, p, epi);
+    }
+  }
+  TL_CUDA(ctx, cudaGetLastError());
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES] += launches;
+  return TL_OK;
+}
