@@ -22,7 +22,9 @@ TOL_F32 = 1e-3
 TOL_HALF = 1e-2
 
 GEMV_VARIANTS_F32 = [(1, 0, 8, 0, 1, 0), (1, 1, 8, 1, 1, 0), (1, 1, 8, 2, 1, 0), (1, 1, 4, 4, 1, 0)]
-GEMV_VARIANTS_HALF = GEMV_VARIANTS_F32 + [(1, 2, 8, 4, 1, 0), (1, 2, 4, 2, 1, 0), (1, 2, 16, 2, 1, 0)]
+GEMV_VARIANTS_HALF = GEMV_VARIANTS_F32 + [(1, 2, 8, 4, 1, 0), (1, 2, 4, 2, 1, 0), (1, 2, 16, 2, 1, 0),
+                                          (1, 3, 4, 4, 0, 0), (1, 3, 2, 2, 0, 0), (1, 3, 8, 4, 0, 0),
+                                          (1, 4, 4, 4, 0, 0), (1, 4, 2, 8, 0, 0), (1, 4, 16, 2, 0, 0)]
 
 
 def _out_to_f32(arr, dtype):
@@ -299,7 +301,7 @@ def test_grouped_and_ragged_shapes(backend, n, k, group, m, act_dtype):
     elif act_dtype == "f32" or k % 64 or group % 64:
         assert ".simt" in plan["variant"]
     else:
-        assert ".mma" in plan["variant"]
+        assert ".ring" in plan["variant"]
     for t in (y, xt, wt.scales, wt):
         t.destroy()
 
@@ -453,7 +455,7 @@ def test_forced_variant_must_be_applicable(backend):
     cs = cases.per_channel_case(32, 80, 1, seed=1)  # K % 64 != 0: the mma kernel cannot run it
     wt = be.createQuantizedWeight(cs["packed"], cs["scales"], 32, 80, tb.perChannelFormat(80))
     xt = be.ops.tensorFromArray(cs["x"].astype(np.float16), [1, 80], "f16")
-    be.forceVariant((1, 2, 8, 4, 1, 0))
+    be.forceVariant((1, 3, 4, 4, 0, 0))
     try:
         with pytest.raises(tb.TlError, match="forced variant"):
             be.linear(xt, wt)

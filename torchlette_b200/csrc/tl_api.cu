@@ -42,6 +42,32 @@ int32_t tl_ensure_scratch(tl_ctx* ctx, size_t bytes, void** out) {
   return TL_OK;
 }
 
+int32_t tl_ensure_zeroed_scratch(tl_ctx* ctx, size_t bytes, void** out) {
+  if (bytes > ctx->zscratch_bytes) {
+    if (ctx->capturing)
+      return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                          "scratch must grow from %zu to %zu bytes during graph capture; run the "
+                          "call once before capturing", ctx->zscratch_bytes, bytes);
+    if (ctx->zscratch) {
+      TL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+      TL_CUDA(ctx, cudaFree(ctx->zscratch));
+      ctx->zscratch = nullptr;
+      ctx->zscratch_bytes = 0;
+    }
+    size_t want = bytes < (size_t(1) << 20) ? (size_t(1) << 20) : bytes;
+    cudaError_t e = cudaMalloc(&ctx->zscratch, want);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return tl_set_error(ctx, TL_ERR_OOM, "scratch allocation of %zu bytes failed: %s", want,
+                          cudaGetErrorString(e));
+    }
+    ctx->zscratch_bytes = want;
+    TL_CUDA(ctx, cudaMemsetAsync(ctx->zscratch, 0, want, ctx->stream));
+  }
+  *out = ctx->zscratch;
+  return TL_OK;
+}
+
 extern "C" {
 
 int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx) {
@@ -85,6 +111,7 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   if (ctx->nccl_comm) tl_comm_destroy(ctx);
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
+  if (ctx->zscratch) cudaFree(ctx->zscratch);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return TL_OK;

@@ -45,6 +45,10 @@ struct tl_ctx {
   // src/backend/webgpu/matmul/dispatch.ts:695-718)
   void* scratch = nullptr;
   size_t scratch_bytes = 0;
+  // second scratch that is all zero between launches: kernels that use it restore
+  // the zeros themselves (partial-sum meeting point of the balanced GEMV)
+  void* zscratch = nullptr;
+  size_t zscratch_bytes = 0;
   // selection
   bool has_forced = false;
   tl_variant forced{};
@@ -59,6 +63,7 @@ struct tl_ctx {
 
 int32_t tl_set_error(tl_ctx* ctx, int32_t code, const char* fmt, ...);
 int32_t tl_ensure_scratch(tl_ctx* ctx, size_t bytes, void** out);
+int32_t tl_ensure_zeroed_scratch(tl_ctx* ctx, size_t bytes, void** out);
 
 #define TL_CHECK_CTX(ctx)                                                       \
   do {                                                                          \

@@ -13,15 +13,20 @@
 //              bytes -> f16/bf16 pairs in registers -> mma.sync m16n8k16 with f32
 //              accumulators; the batch is the MMA n dimension.  f16/bf16
 //              activations, K % 64 == 0, G % 64 == 0.
-// Variant parameters: p0 = warps per CTA, p1 = rows per warp (simt) / unused,
-// p2 = k-split cluster size (mma; 1 = none), p3 = reserved.
+//   4 "ring"   kernel 2's tiling with the weight bytes prefetched global -> shared by
+//              per-thread cp.async rings (no registers held in flight).
+//   3 "sk"     persistent grid, the weight dealt out to warps in equal contiguous
+//              shares of 8-row x 128-byte units; partial tiles meet in an f32
+//              scratch.  f16/bf16 activations, K % 128 == 0, G % 64 == 0.
+// Variant parameters: p0 = warps per CTA (sk: CTAs per SM), p1 = rows per warp
+// (simt) / k blocks in flight (mma, sk), p2, p3 = reserved.
 #include <algorithm>
 
 #include "tl_common.cuh"
 
 namespace {
 
-constexpr int kScalar = 0, kSimt = 1, kMma = 2;
+constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   // weights are read exactly once: keep them out of L1
@@ -384,8 +389,378 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_mma_kernel(GemvArgs p
 }
 
 // ---------------------------------------------------------------------------
+// 3: balanced streaming kernel ("sk").
+//
+// The weight is cut into units of 8 rows x 128 bytes.  Units are numbered with k
+// fastest inside an 8-row tile, and the flat range is dealt out to the warps of a
+// persistent grid in equal contiguous shares, so every SM streams the same number
+// of bytes whatever N is (no wave quantisation).  Warps never synchronise with
+// one another: a warp that owns only part of a tile's k range adds its partial
+// sums to a zero-initialised f32 scratch [M,N] and bumps the tile's unit counter;
+// the warp that completes the count applies scale + epilogue, stores, and zeroes
+// the scratch and the counter again.  Nobody waits on anybody.
+//
+// Here the roles of the MMA operands are swapped with respect to kernel 2: the
+// batch is the 16-row A operand (so m = 9..16 costs no extra MMA) and 8 weight
+// rows are the B operand.  Thread (g,t) loads 32 contiguous bytes of weight row g
+// (word j feeds MMA j: bytes 0,1 -> k slots 2t,2t+1; bytes 2,3 -> 2t+8,2t+9) and
+// the matching 32 activations of batch rows g and g+8.
+// ---------------------------------------------------------------------------
+struct SkArgs {
+  float* scratch;       // [m, n] f32, all zero between launches
+  unsigned* counters;   // [tiles], all zero between launches
+  int32_t upt;          // units per tile = k / 128
+  int32_t warps_used;
+  int64_t total_units;
+};
+
+template <typename AT, bool M16, bool GROUPED, int D>
+__global__ void __launch_bounds__(256) qgemv_sk_kernel(GemvArgs p, EpiParams epi, SkArgs sk) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const int wg = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (wg >= sk.warps_used) return;
+  const int64_t q = sk.total_units / sk.warps_used, r = sk.total_units % sk.warps_used;
+  const int64_t u0 = wg * q + min(int64_t(wg), r);
+  const int cnt = int(q + (wg < r ? 1 : 0));
+  if (cnt == 0) return;
+
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const bool lo_ok = g < p.m, hi_ok = M16 && (g + 8) < p.m;
+  const AT* a_lo = a + int64_t(lo_ok ? g : 0) * p.k + 32 * t;
+  const AT* a_hi = a + int64_t(hi_ok ? g + 8 : 0) * p.k + 32 * t;
+
+  // load cursor and compute cursor over (tile, unit-in-tile)
+  int tile_l = int(u0 / sk.upt), ku_l = int(u0 % sk.upt);
+  int tile_c = tile_l, ku_c = ku_l;
+  auto wptr = [&](int tile, int ku) {
+    const int64_t row = min(int64_t(tile) * 8 + g, int64_t(p.n) - 1);
+    return wbytes + row * p.k + int64_t(ku) * 128 + 32 * t;
+  };
+  uint4 buf[D][2];
+#pragma unroll
+  for (int d = 0; d < D; ++d) {
+    if (d < cnt) {
+      const uint8_t* ptr = wptr(tile_l, ku_l);
+      buf[d][0] = ldg_stream(ptr);
+      buf[d][1] = ldg_stream(ptr + 16);
+      if (++ku_l == sk.upt) { ku_l = 0; ++tile_l; }
+    }
+  }
+
+  float total[4] = {0.f, 0.f, 0.f, 0.f};
+  int mine = 0;  // units of the current tile accumulated by this warp
+  for (int i = 0; i < cnt; i += D) {
+#pragma unroll
+    for (int d = 0; d < D; ++d) {
+      if (i + d < cnt) {
+        const uint32_t w8[8] = {buf[d][0].x, buf[d][0].y, buf[d][0].z, buf[d][0].w,
+                                buf[d][1].x, buf[d][1].y, buf[d][1].z, buf[d][1].w};
+        if (i + d + D < cnt) {  // refill this slot D units ahead
+          const uint8_t* ptr = wptr(tile_l, ku_l);
+          buf[d][0] = ldg_stream(ptr);
+          buf[d][1] = ldg_stream(ptr + 16);
+          if (++ku_l == sk.upt) { ku_l = 0; ++tile_l; }
+        }
+        // activations of this unit: 32 halves per batch row
+        uint32_t xl[16], xh[16];
+        {
+          const uint4* s0 = reinterpret_cast<const uint4*>(a_lo + int64_t(ku_c) * 128);
+          const uint4* s1 = reinterpret_cast<const uint4*>(a_hi + int64_t(ku_c) * 128);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 lo4 = lo_ok ? __ldg(s0 + v) : make_uint4(0, 0, 0, 0);
+            xl[4 * v] = lo4.x; xl[4 * v + 1] = lo4.y; xl[4 * v + 2] = lo4.z; xl[4 * v + 3] = lo4.w;
+            if (M16) {
+              uint4 hi4 = hi_ok ? __ldg(s1 + v) : make_uint4(0, 0, 0, 0);
+              xh[4 * v] = hi4.x; xh[4 * v + 1] = hi4.y; xh[4 * v + 2] = hi4.z; xh[4 * v + 3] = hi4.w;
+            } else {
+              xh[4 * v] = 0; xh[4 * v + 1] = 0; xh[4 * v + 2] = 0; xh[4 * v + 3] = 0;
+            }
+          }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float c[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[e] = GROUPED ? 0.f : total[e];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int j = half * 4 + jj;
+            uint32_t b0, b1;
+            MmaOps<AT>::cvt(w8[j], b0, b1);
+            MmaOps<AT>::mma(c, xl[2 * j], xh[2 * j], xl[2 * j + 1], xh[2 * j + 1], b0, b1);
+          }
+          if (GROUPED) {
+            const int gi = (ku_c * 128 + half * 64) / p.group;
+            const int64_t r0 = min(int64_t(tile_c) * 8 + 2 * t, int64_t(p.n) - 1);
+            const int64_t r1 = min(int64_t(tile_c) * 8 + 2 * t + 1, int64_t(p.n) - 1);
+            const float s0 = tl_load_scale(p.scales, p.scales_dtype, r0 * p.groups_per_row + gi);
+            const float s1 = tl_load_scale(p.scales, p.scales_dtype, r1 * p.groups_per_row + gi);
+            total[0] = fmaf(s0, c[0], total[0]);
+            total[1] = fmaf(s1, c[1], total[1]);
+            total[2] = fmaf(s0, c[2], total[2]);
+            total[3] = fmaf(s1, c[3], total[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) total[e] = c[e];
+          }
+        }
+        ++mine;
+        const bool tile_done = (ku_c + 1 == sk.upt);
+        if (tile_done || i + d + 1 == cnt) {
+          // flush the accumulators of tile_c: c0,c1 = batch g, rows 2t,2t+1 ; c2,c3 = batch g+8
+          const int64_t rbase = int64_t(tile_c) * 8 + 2 * t;
+          bool finalize = (mine == sk.upt);
+          if (!finalize) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int b = g + ((e & 2) ? 8 : 0);
+              const int64_t row = rbase + (e & 1);
+              if (b < p.m && row < p.n) atomicAdd(sk.scratch + int64_t(b) * p.n + row, total[e]);
+            }
+            __threadfence();
+            __syncwarp();  // every lane's partial sums are published before the count moves
+            unsigned old = 0;
+            if (lane == 0) old = atomicAdd(sk.counters + tile_c, unsigned(mine));
+            old = __shfl_sync(0xffffffffu, old, 0);
+            finalize = (old + unsigned(mine) == unsigned(sk.upt));
+            if (finalize) {
+              __threadfence();
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int b = g + ((e & 2) ? 8 : 0);
+                const int64_t row = rbase + (e & 1);
+                if (b < p.m && row < p.n) {
+                  float* sp = sk.scratch + int64_t(b) * p.n + row;
+                  total[e] = __ldcg(sp);
+                  __stcg(sp, 0.f);
+                }
+              }
+              if (lane == 0) sk.counters[tile_c] = 0;
+            }
+          }
+          if (finalize) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int b = g + ((e & 2) ? 8 : 0);
+              const int64_t row = rbase + (e & 1);
+              if (b < p.m && row < p.n) {
+                float s = p.wscale;
+                if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
+                const float o = tl_apply_epilogue(epi, total[e] * s, p.row0 + b, row, p.n);
+                tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + b) * p.n + row, o);
+              }
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) total[e] = 0.f;
+          mine = 0;
+        }
+        if (++ku_c == sk.upt) { ku_c = 0; ++tile_c; }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 4: tensor-core kernel with an asynchronous prefetch ring ("ring").
+//
+// Same tiling and fragment mapping as kernel 2 (one CTA per 16 rows, warps
+// interleaved over 64-wide k blocks, weights as the MMA A operand), but the weight
+// bytes travel global -> shared with 16-byte cp.async copies that hold no
+// registers while in flight.  Every thread owns S private slots of 2 x 16 bytes
+// (row g and row g+8 of one k block): it copies, waits for and reads only its own
+// slots, so no barrier is needed and consecutive lanes touch consecutive 16-byte
+// words (no bank conflicts).  With S k blocks in flight per thread and small CTAs
+// (so that many are resident per SM) an SM keeps ~100 KB of loads outstanding,
+// which is what it takes to cover HBM latency at full bandwidth.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs p, EpiParams epi) {
+  extern __shared__ __align__(16) uint8_t ring_raw[];
+  uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [S][2][blockDim.x]
+  const int nthreads = blockDim.x, tid = threadIdx.x;
+  float* red = reinterpret_cast<float*>(ring_raw + size_t(S) * 2 * nthreads * 16);  // [warps][NT][4][32]
+  const int warps = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t tile_row = int64_t(blockIdx.x) * 16;
+  const int64_t r_lo = min(tile_row + g, int64_t(p.n) - 1);
+  const int64_t r_hi = min(tile_row + g + 8, int64_t(p.n) - 1);
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  const uint8_t* w_lo = wbytes + r_lo * p.k + 16 * t + warp * 64;
+  const uint8_t* w_hi = wbytes + r_hi * p.k + 16 * t + warp * 64;
+  const int kstride = warps * 64;  // bytes between this warp's consecutive k blocks
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const AT* a_col[NT];
+  bool a_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    a_ok[nt] = (g + 8 * nt) < p.m;
+    a_col[nt] = a + int64_t(a_ok[nt] ? g + 8 * nt : 0) * p.k + 16 * t + warp * 64;
+  }
+  const int kblocks = p.k >> 6;
+  const int nkb = (kblocks - warp + warps - 1) / warps;  // k blocks of this warp
+  const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
+  const uint32_t slot_bytes = uint32_t(nthreads) * 16u;  // one [blockDim] row of 16-byte words
+
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    if (s < nkb) {
+      cp_async16(ring_base + (2 * s) * slot_bytes, w_lo + int64_t(s) * kstride);
+      cp_async16(ring_base + (2 * s + 1) * slot_bytes, w_hi + int64_t(s) * kstride);
+    }
+    cp_async_commit();
+  }
+
+  float total[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
+
+  for (int i0 = 0; i0 < nkb; i0 += S) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int i = i0 + s;
+      if (i < nkb) {
+        uint4 bx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          if (a_ok[nt]) {
+            const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(i) * kstride);
+            bx[nt][0] = __ldg(src);
+            bx[nt][1] = __ldg(src + 1);
+          } else {
+            bx[nt][0] = make_uint4(0, 0, 0, 0);
+            bx[nt][1] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        cp_async_wait<S - 1>();
+        const uint4 wl = ring[(2 * s) * nthreads + tid];
+        const uint4 wh = ring[(2 * s + 1) * nthreads + tid];
+        float c[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[nt][e] = GROUPED ? 0.f : total[nt][e];
+        const uint32_t wlo[4] = {wl.x, wl.y, wl.z, wl.w};
+        const uint32_t whi[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t a0, a1, a2, a3;
+          MmaOps<AT>::cvt(wlo[j], a0, a2);
+          MmaOps<AT>::cvt(whi[j], a1, a3);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 v = bx[nt][j >> 1];
+            const uint32_t b0 = (j & 1) ? v.z : v.x, b1 = (j & 1) ? v.w : v.y;
+            MmaOps<AT>::mma(c[nt], a0, a1, a2, a3, b0, b1);
+          }
+        }
+        // the slot's words now live in registers that have been consumed: refill it
+        if (i + S < nkb) {
+          cp_async16(ring_base + (2 * s) * slot_bytes, w_lo + int64_t(i + S) * kstride);
+          cp_async16(ring_base + (2 * s + 1) * slot_bytes, w_hi + int64_t(i + S) * kstride);
+        }
+        cp_async_commit();
+        if (GROUPED) {
+          const int gi = ((warp + i * warps) * 64) / p.group;
+          const float s_lo = tl_load_scale(p.scales, p.scales_dtype, r_lo * p.groups_per_row + gi);
+          const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + gi);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            total[nt][0] = fmaf(s_lo, c[nt][0], total[nt][0]);
+            total[nt][1] = fmaf(s_lo, c[nt][1], total[nt][1]);
+            total[nt][2] = fmaf(s_hi, c[nt][2], total[nt][2]);
+            total[nt][3] = fmaf(s_hi, c[nt][3], total[nt][3]);
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) total[nt][e] = c[nt][e];
+        }
+      } else {
+        cp_async_commit();  // keeps the group count uniform for wait_group
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red[((warp * NT + nt) * 4 + i) * 32 + lane] = total[nt][i];
+  __syncthreads();
+  for (int o = tid; o < NT * 128; o += nthreads) {
+    const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+    float v = 0.f;
+    for (int w = 0; w < warps; ++w) v += red[((w * NT + nt) * 4 + i) * 32 + ln];
+    const int gg = ln >> 2, tt = ln & 3;
+    const int64_t row = tile_row + gg + ((i & 2) ? 8 : 0);
+    const int col = 8 * nt + 2 * tt + (i & 1);
+    if (row < p.n && col < p.m) {
+      float s = p.wscale;
+      if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
+      const float r = tl_apply_epilogue(epi, v * s, p.row0 + col, row, p.n);
+      tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+template <typename K>
+void launch_with_smem(K kernel, int grid, int block, size_t smem, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  kernel<<<grid, block, smem, s>>>(p, e);
+}
+template <typename AT, int NT, bool GROUPED>
+void launch_ring_s(int depth, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  const size_t smem = size_t(depth >= 8 ? 8 : depth >= 4 ? 4 : 2) * 2 * block * 16 + size_t(block / 32) * NT * 128 * 4;
+  if (depth >= 8) launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 8>, grid, block, smem, s, p, e);
+  else if (depth >= 4) launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 4>, grid, block, smem, s, p, e);
+  else launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 2>, grid, block, smem, s, p, e);
+}
+template <typename AT>
+void launch_ring(bool two, bool grouped, int depth, int grid, int block, cudaStream_t s, const GemvArgs& p,
+                 const EpiParams& e) {
+  if (two) {
+    if (grouped) launch_ring_s<AT, 2, true>(depth, grid, block, s, p, e);
+    else launch_ring_s<AT, 2, false>(depth, grid, block, s, p, e);
+  } else {
+    if (grouped) launch_ring_s<AT, 1, true>(depth, grid, block, s, p, e);
+    else launch_ring_s<AT, 1, false>(depth, grid, block, s, p, e);
+  }
+}
+
+template <typename AT, bool M16, bool GROUPED>
+void launch_sk_d(int depth, int grid, cudaStream_t s, const GemvArgs& p, const EpiParams& e, const SkArgs& sk) {
+  if (depth >= 4) qgemv_sk_kernel<AT, M16, GROUPED, 4><<<grid, 256, 0, s>>>(p, e, sk);
+  else qgemv_sk_kernel<AT, M16, GROUPED, 2><<<grid, 256, 0, s>>>(p, e, sk);
+}
+template <typename AT>
+void launch_sk(bool m16, bool grouped, int depth, int grid, cudaStream_t s, const GemvArgs& p, const EpiParams& e,
+               const SkArgs& sk) {
+  if (m16) {
+    if (grouped) launch_sk_d<AT, true, true>(depth, grid, s, p, e, sk);
+    else launch_sk_d<AT, true, false>(depth, grid, s, p, e, sk);
+  } else {
+    if (grouped) launch_sk_d<AT, false, true>(depth, grid, s, p, e, sk);
+    else launch_sk_d<AT, false, false>(depth, grid, s, p, e, sk);
+  }
+}
+
 template <typename AT, int MT, int R>
 void launch_simt(bool grouped, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
   if (grouped) qgemv_simt_kernel<AT, MT, R, true><<<grid, block, 0, s>>>(p, e);
@@ -431,6 +806,12 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
     case kMma:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
              (v.p1 == 2 || v.p1 == 4);
+    case kRing:
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
+             (v.p1 == 2 || v.p1 == 4 || v.p1 == 8);
+    case kSk:
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 64 == 0 && v.p0 <= 8 &&
+             (v.p1 == 2 || v.p1 == 4);
     default: return false;
   }
 }
@@ -441,7 +822,7 @@ int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, i
   tl_variant v{};
   v.family = TL_FAMILY_QGEMV;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
-    v.kernel = kMma; v.p0 = 8; v.p1 = 4; v.p2 = 1;
+    v.kernel = kRing; v.p0 = 4; v.p1 = 4;
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -459,12 +840,16 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
   out->push_back(d);  // the default is always a candidate (variants.ts:194-205)
   auto add = [&](int kernel, int p0, int p1) {
     tl_variant v{};
-    v.family = TL_FAMILY_QGEMV; v.kernel = kernel; v.p0 = p0; v.p1 = p1; v.p2 = 1;
+    v.family = TL_FAMILY_QGEMV; v.kernel = kernel; v.p0 = p0; v.p1 = p1; v.p2 = kernel == kMma ? 1 : 0;
     if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q)) return;
     for (const auto& o : *out)
       if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1) return;
     out->push_back(v);
   };
+  for (int w : {2, 4, 8, 16})
+    for (int u : {2, 4, 8}) add(kRing, w, u);
+  for (int b : {2, 4, 8})
+    for (int u : {2, 4}) add(kSk, b, u);
   for (int w : {4, 8, 16})
     for (int u : {2, 4}) add(kMma, w, u);
   if (m <= 4 || a_dtype == TL_F32)
@@ -487,9 +872,19 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   p.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
   p.row0 = 0; p.m_total = m;
   const bool grouped = q.group_size != k;
-  const int block = v.p0 * 32;
+  int block = v.p0 * 32;
   int grid = 0, launches = 1;
-  if (v.kernel == kScalar) grid = int((n + v.p0 - 1) / v.p0);
+  SkArgs sk{};
+  if (v.kernel == kSk) {
+    block = 256;
+    const int64_t tiles = (n + 7) / 8;
+    sk.upt = int32_t(k / 128);
+    sk.total_units = tiles * sk.upt;
+    const int64_t resident = int64_t(ctx->sm_count) * v.p0 * 8;          // warps the persistent grid can hold
+    const int64_t useful = std::max<int64_t>(1, sk.total_units / 4);     // at least 4 units (4 KB) per warp
+    sk.warps_used = int32_t(std::min(resident, useful));
+    grid = (sk.warps_used + 7) / 8;
+  } else if (v.kernel == kScalar) grid = int((n + v.p0 - 1) / v.p0);
   else if (v.kernel == kSimt) { grid = int((n + int64_t(v.p0) * v.p1 - 1) / (int64_t(v.p0) * v.p1)); launches = (m + 3) / 4; }
   else grid = int((n + 15) / 16);
   if (receipt) {
@@ -505,7 +900,17 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
                           tl_variant_name(&v));
   }
   cudaStream_t s = ctx->stream;
-  if (v.kernel == kScalar) {
+  if (v.kernel == kSk) {
+    const int64_t tiles = (n + 7) / 8;
+    const size_t sbytes = size_t(m) * n * sizeof(float);
+    void* base = nullptr;
+    int32_t rc = tl_ensure_zeroed_scratch(ctx, sbytes + size_t(tiles) * sizeof(unsigned), &base);
+    if (rc != TL_OK) return rc;
+    sk.scratch = reinterpret_cast<float*>(base);
+    sk.counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(base) + sbytes);
+    if (a_dtype == TL_F16) launch_sk<__half>(m > 8, grouped, v.p1, grid, s, p, epi, sk);
+    else launch_sk<__nv_bfloat16>(m > 8, grouped, v.p1, grid, s, p, epi, sk);
+  } else if (v.kernel == kScalar) {
     if (a_dtype == TL_F32) qgemv_scalar_kernel<float><<<grid, block, 0, s>>>(p, epi);
     else if (a_dtype == TL_F16) qgemv_scalar_kernel<__half><<<grid, block, 0, s>>>(p, epi);
     else qgemv_scalar_kernel<__nv_bfloat16><<<grid, block, 0, s>>>(p, epi);
@@ -520,6 +925,9 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
       else if (a_dtype == TL_F16) launch_simt_r<__half>(v.p1, mt, grouped, grid, block, s, ps, epi);
       else launch_simt_r<__nv_bfloat16>(v.p1, mt, grouped, grid, block, s, ps, epi);
     }
+  } else if (v.kernel == kRing) {
+    if (a_dtype == TL_F16) launch_ring<__half>(m > 8, grouped, v.p1, grid, block, s, p, epi);
+    else launch_ring<__nv_bfloat16>(m > 8, grouped, v.p1, grid, block, s, p, epi);
   } else {
     const bool two = m > 8;
     if (a_dtype == TL_F16) {
