@@ -24,7 +24,9 @@ TOL_HALF = 1e-2
 GEMV_VARIANTS_F32 = [(1, 0, 8, 0, 1, 0), (1, 1, 8, 1, 1, 0), (1, 1, 8, 2, 1, 0), (1, 1, 4, 4, 1, 0)]
 GEMV_VARIANTS_HALF = GEMV_VARIANTS_F32 + [(1, 2, 8, 4, 1, 0), (1, 2, 4, 2, 1, 0), (1, 2, 16, 2, 1, 0),
                                           (1, 3, 4, 4, 0, 0), (1, 3, 2, 2, 0, 0), (1, 3, 8, 4, 0, 0),
-                                          (1, 4, 4, 4, 0, 0), (1, 4, 2, 8, 0, 0), (1, 4, 16, 2, 0, 0)]
+                                          (1, 4, 4, 4, 0, 0), (1, 4, 2, 8, 0, 0), (1, 4, 16, 2, 0, 0),
+                                          (1, 5, 6, 0, 0, 0), (1, 5, 4, 0, 0, 0),
+                                          (1, 6, 16, 32, 0, 0), (1, 6, 8, 64, 0, 0)]
 
 
 def _out_to_f32(arr, dtype):

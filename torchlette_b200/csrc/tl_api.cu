@@ -101,6 +101,12 @@ int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx) {
     delete ctx;
     return tl_set_error(nullptr, TL_ERR_CUDA, "tl_ctx_create: stream: %s", cudaGetErrorString(e));
   }
+  if (cudaMalloc(&ctx->dev_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess) {
+    cudaGetLastError();
+    cudaStreamDestroy(ctx->stream);
+    delete ctx;
+    return tl_set_error(nullptr, TL_ERR_OOM, "tl_ctx_create: cannot allocate the device status word");
+  }
   *out_ctx = ctx;
   return TL_OK;
 }
@@ -112,6 +118,7 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->zscratch) cudaFree(ctx->zscratch);
+  if (ctx->dev_status) cudaFree(ctx->dev_status);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return TL_OK;
@@ -121,6 +128,15 @@ int32_t tl_sync(tl_ctx* ctx) {
   TL_CHECK_CTX(ctx);
   DeviceGuard guard(ctx->device);
   TL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  int status = 0;
+  TL_CUDA(ctx, cudaMemcpy(&status, ctx->dev_status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (status != 0) {
+    // a bounded device-side wait ran out: the scratch may hold partial sums, so clear it
+    cudaMemset(ctx->dev_status, 0, sizeof(int));
+    if (ctx->zscratch) cudaMemset(ctx->zscratch, 0, ctx->zscratch_bytes);
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_TIMEOUT, "tl_sync: a kernel gave up a bounded wait (device code %d)", status);
+  }
   return TL_OK;
 }
 
@@ -564,3 +580,39 @@ int32_t tl_force_variant(tl_ctx* ctx, const tl_variant* v) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Tensor-map encoding through the driver entry point (no libcuda link).
+// ---------------------------------------------------------------------------
+#include "tl_tma.cuh"
+
+typedef CUresult (*TlEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                    const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+bool tl_encode_tmap_2d(CUtensorMap* map, int elem_bytes, const void* base, uint64_t inner, uint64_t outer,
+                       uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, int swizzle) {
+  static TlEncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return false;
+    }
+    fn = reinterpret_cast<TlEncodeTiledFn>(p);
+  }
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_UINT16
+                                                   : CU_TENSOR_MAP_DATA_TYPE_UINT32;
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {row_stride_bytes};
+  cuuint32_t box[2] = {box_inner, box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapSwizzle sw = swizzle == 3 ? CU_TENSOR_MAP_SWIZZLE_128B
+                                : swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                : swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_32B
+                                               : CU_TENSOR_MAP_SWIZZLE_NONE;
+  return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}

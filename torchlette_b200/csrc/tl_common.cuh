@@ -49,6 +49,7 @@ struct tl_ctx {
   // the zeros themselves (partial-sum meeting point of the balanced GEMV)
   void* zscratch = nullptr;
   size_t zscratch_bytes = 0;
+  int* dev_status = nullptr;  // written by kernels whose bounded waits ran out; read back by tl_sync
   // selection
   bool has_forced = false;
   tl_variant forced{};

@@ -15,6 +15,12 @@
 //              activations, K % 64 == 0, G % 64 == 0.
 //   4 "ring"   kernel 2's tiling with the weight bytes prefetched global -> shared by
 //              per-thread cp.async rings (no registers held in flight).
+//   6 "bulk"   persistent grid fed by contiguous cp.async.bulk copies of whole 8-row
+//              blocks; batch as the MMA A operand; no cross-CTA partial sums.
+//              p0 = consumer warps, p1 = stage size target in KB.
+//   5 "tma"    persistent grid fed by 32 KB tensor-map TMA boxes through a shared-memory
+//              ring; 16 consumer warps x 16 rows; balanced contiguous shares of boxes.
+//              f16/bf16 activations, K % 128 == 0, G % 64 == 0.  p0 = stages.
 //   3 "sk"     persistent grid, the weight dealt out to warps in equal contiguous
 //              shares of 8-row x 128-byte units; partial tiles meet in an f32
 //              scratch.  f16/bf16 activations, K % 128 == 0, G % 64 == 0.
@@ -23,10 +29,29 @@
 #include <algorithm>
 
 #include "tl_common.cuh"
+#include "tl_tma.cuh"
 
 namespace {
 
-constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4;
+constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4, kTma = 5, kBulk = 6;
+
+// geometry of the "bulk" kernel for a given k: tiles per stage, stage bytes, stages, warps per tile
+struct BulkGeom { int rt, nstages, p; uint32_t stage_bytes; size_t smem; bool ok; };
+inline BulkGeom bulk_geom(int64_t k, int cwarps, int target_kb) {
+  BulkGeom gm{};
+  const int64_t tile_bytes = 8 * k;
+  gm.rt = int(std::max<int64_t>(1, (int64_t(target_kb) * 1024) / tile_bytes));
+  gm.stage_bytes = uint32_t(gm.rt * tile_bytes);
+  int kb128 = int(k / 128), pw = 1;
+  while (pw * 2 <= kb128 && pw * 2 <= cwarps) pw *= 2;
+  gm.p = pw;
+  const size_t red = size_t(2) * gm.rt * gm.p * 128 * sizeof(float);
+  const size_t budget = 220 * 1024;
+  gm.ok = tile_bytes <= 100 * 1024 && red + 2 * size_t(gm.stage_bytes) + 128 <= budget;
+  gm.nstages = gm.ok ? int(std::min<size_t>(8, (budget - red - 128) / gm.stage_bytes)) : 0;
+  gm.smem = size_t(gm.nstages) * gm.stage_bytes + red + 128;
+  return gm;
+}
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   // weights are read exactly once: keep them out of L1
@@ -600,13 +625,12 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
   const uint8_t* w_hi = wbytes + r_hi * p.k + 16 * t + warp * 64;
   const int kstride = warps * 64;  // bytes between this warp's consecutive k blocks
   const AT* a = reinterpret_cast<const AT*>(p.a);
+  // MMA column c of a tile is batch row c.  Columns past m are never stored and no
+  // column feeds another, so lanes past m simply re-read the last batch row instead
+  // of branching to a zero fill.
   const AT* a_col[NT];
-  bool a_ok[NT];
 #pragma unroll
-  for (int nt = 0; nt < NT; ++nt) {
-    a_ok[nt] = (g + 8 * nt) < p.m;
-    a_col[nt] = a + int64_t(a_ok[nt] ? g + 8 * nt : 0) * p.k + 16 * t + warp * 64;
-  }
+  for (int nt = 0; nt < NT; ++nt) a_col[nt] = a + int64_t(min(g + 8 * nt, p.m - 1)) * p.k + 16 * t + warp * 64;
   const int kblocks = p.k >> 6;
   const int nkb = (kblocks - warp + warps - 1) / warps;  // k blocks of this warp
   const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
@@ -635,14 +659,9 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
         uint4 bx[NT][2];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          if (a_ok[nt]) {
-            const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(i) * kstride);
-            bx[nt][0] = __ldg(src);
-            bx[nt][1] = __ldg(src + 1);
-          } else {
-            bx[nt][0] = make_uint4(0, 0, 0, 0);
-            bx[nt][1] = make_uint4(0, 0, 0, 0);
-          }
+          const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(i) * kstride);
+          bx[nt][0] = __ldg(src);
+          bx[nt][1] = __ldg(src + 1);
         }
         cp_async_wait<S - 1>();
         const uint4 wl = ring[(2 * s) * nthreads + tid];
@@ -713,6 +732,427 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
       if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
       const float r = tl_apply_epilogue(epi, v * s, p.row0 + col, row, p.n);
       tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 5: TMA-fed persistent kernel ("tma").
+//
+// A producer thread streams the weight with 2-D tensor-map TMA loads: one box is
+// 256 rows x 128 bytes (32 KB, 128-byte swizzle), the size at which a single
+// load per SM at a time already saturates HBM.  STAGES boxes are in flight per SM
+// (192 KB at 6 stages) and cost no registers and almost no issue slots.  Boxes
+// are numbered with k fastest inside a 256-row band; the persistent grid deals
+// the flat range out in equal contiguous shares (no wave quantisation).
+//
+// Sixteen consumer warps own 16 rows of the band each (one MMA tile, weights as the
+// A operand as in kernel 2) for the whole k range, so warps never reduce
+// across each other.  A warp whose CTA covered only part of a band's k range adds
+// its partial sums to the zero-initialised scratch and bumps its (band, warp)
+// counter; the warp that completes the count finalises.  Nobody waits on anybody.
+//
+// Shared-memory reads are conflict-free: with the 128-byte swizzle the 16-byte
+// chunk c of row r sits at chunk c ^ (r & 7).  Per-channel scales: thread (g,t)
+// reads chunks 2t and 2t+1 of rows g and g+8 (32 contiguous weight bytes, k order
+// permuted identically for the activations).  Grouped scales need every MMA to
+// stay inside one 64-wide group, so there the thread reads chunk 4h+t for half h.
+// ---------------------------------------------------------------------------
+constexpr int kTmaBoxRows = 256, kTmaBoxBytes = 128, kTmaStageBytes = kTmaBoxRows * kTmaBoxBytes;
+constexpr int kTmaConsumerWarps = 16;
+
+struct TmaArgs {
+  float* scratch;      // [m, n] f32, all zero between launches
+  unsigned* counters;  // [bands * consumer warps], all zero between launches
+  int* status;         // device error word (0 = ok)
+  int32_t spb;         // stages (boxes) per band = k / 128
+  int32_t total_stages;
+};
+
+template <typename AT, int NT, bool GROUPED, int STAGES>
+__global__ void __launch_bounds__((kTmaConsumerWarps + 1) * 32, 1)
+qgemv_tma_kernel(const __grid_constant__ CUtensorMap wmap, GemvArgs p, EpiParams epi, TmaArgs ta) {
+  extern __shared__ uint8_t tma_smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES];
+  __shared__ int abort_flag;
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(tma_smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t T = ta.total_stages;
+  const int i0 = int(T * blockIdx.x / gridDim.x), i1 = int(T * (blockIdx.x + 1) / gridDim.x);
+  const int n = i1 - i0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], kTmaConsumerWarps);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (n <= 0) return;
+
+  if (warp == kTmaConsumerWarps) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      tma_prefetch_desc(&wmap);
+      for (int i = 0; i < n; ++i) {
+        const int s = i % STAGES;
+        if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, &abort_flag)) {
+          if (!abort_flag) { abort_flag = 1; atomicExch(ta.status, TL_DEV_TIMEOUT_EMPTY); }
+          break;
+        }
+        const int gi = i0 + i;
+        mbar_expect_tx(&full_bar[s], kTmaStageBytes);
+        tma_load_2d(stages + size_t(s) * kTmaStageBytes, &wmap, (gi % ta.spb) * kTmaBoxBytes,
+                    (gi / ta.spb) * kTmaBoxRows, &full_bar[s]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  const int g = lane >> 2, t = lane & 3;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const AT* a_col[NT];
+  bool a_ok[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    a_ok[nt] = (g + 8 * nt) < p.m;
+    a_col[nt] = a + int64_t(a_ok[nt] ? g + 8 * nt : 0) * p.k;
+  }
+  const uint32_t row_off = uint32_t(warp * 16 + g) * kTmaBoxBytes;  // + 8*128 for the high row
+  // byte offsets of this thread's 16-byte chunks inside a swizzled 128-byte row
+  const uint32_t c32_0 = uint32_t((2 * t) ^ g) << 4, c32_1 = c32_0 ^ 16u;        // chunks 2t, 2t+1
+  const uint32_t c16_0 = uint32_t(t ^ g) << 4, c16_1 = uint32_t((4 + t) ^ g) << 4;  // chunks t, 4+t
+
+  float acc[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+  int mine = 0;
+
+  for (int i = 0; i < n; ++i) {
+    const int s = i % STAGES;
+    const int gi = i0 + i, band = gi / ta.spb, ks = gi - band * ta.spb;
+    // activations of this 128-wide k block (independent of the weight stream: load first)
+    uint32_t xb[NT][16];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      if (GROUPED) {
+        const uint4* s0 = reinterpret_cast<const uint4*>(a_col[nt] + ks * 128 + 16 * t);
+        const uint4* s1 = reinterpret_cast<const uint4*>(a_col[nt] + ks * 128 + 64 + 16 * t);
+#pragma unroll
+        for (int v = 0; v < 2; ++v) {
+          const uint4 q0 = a_ok[nt] ? __ldg(s0 + v) : make_uint4(0, 0, 0, 0);
+          const uint4 q1 = a_ok[nt] ? __ldg(s1 + v) : make_uint4(0, 0, 0, 0);
+          xb[nt][4 * v] = q0.x; xb[nt][4 * v + 1] = q0.y; xb[nt][4 * v + 2] = q0.z; xb[nt][4 * v + 3] = q0.w;
+          xb[nt][8 + 4 * v] = q1.x; xb[nt][8 + 4 * v + 1] = q1.y; xb[nt][8 + 4 * v + 2] = q1.z; xb[nt][8 + 4 * v + 3] = q1.w;
+        }
+      } else {
+        const uint4* s0 = reinterpret_cast<const uint4*>(a_col[nt] + ks * 128 + 32 * t);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const uint4 q0 = a_ok[nt] ? __ldg(s0 + v) : make_uint4(0, 0, 0, 0);
+          xb[nt][4 * v] = q0.x; xb[nt][4 * v + 1] = q0.y; xb[nt][4 * v + 2] = q0.z; xb[nt][4 * v + 3] = q0.w;
+        }
+      }
+    }
+    if (!mbar_wait(&full_bar[s], (i / STAGES) & 1, &abort_flag)) {
+      if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(ta.status, TL_DEV_TIMEOUT_FULL); }
+      return;
+    }
+    const uint32_t sb = smem_u32(stages + size_t(s) * kTmaStageBytes) + row_off;
+    uint4 wl[2], wh[2];
+    {
+      const uint32_t lo = sb, hi = sb + 8 * kTmaBoxBytes;
+      wl[0] = lds128(lo + (GROUPED ? c16_0 : c32_0));
+      wl[1] = lds128(lo + (GROUPED ? c16_1 : c32_1));
+      wh[0] = lds128(hi + (GROUPED ? c16_0 : c32_0));
+      wh[1] = lds128(hi + (GROUPED ? c16_1 : c32_1));
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);  // the words are in registers: the box may be refilled
+
+    {
+      const uint32_t wlo[8] = {wl[0].x, wl[0].y, wl[0].z, wl[0].w, wl[1].x, wl[1].y, wl[1].z, wl[1].w};
+      const uint32_t whi[8] = {wh[0].x, wh[0].y, wh[0].z, wh[0].w, wh[1].x, wh[1].y, wh[1].z, wh[1].w};
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float c[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[nt][e] = GROUPED ? 0.f : acc[nt][e];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const int j = 4 * h + jj;
+          uint32_t a0, a1, a2, a3;
+          MmaOps<AT>::cvt(wlo[j], a0, a2);
+          MmaOps<AT>::cvt(whi[j], a1, a3);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) MmaOps<AT>::mma(c[nt], a0, a1, a2, a3, xb[nt][2 * j], xb[nt][2 * j + 1]);
+        }
+        if (GROUPED) {
+          const int grp = (ks * 128 + h * 64) / p.group;
+          const int64_t r_lo = min(int64_t(band) * kTmaBoxRows + warp * 16 + g, int64_t(p.n) - 1);
+          const int64_t r_hi = min(r_lo + 8, int64_t(p.n) - 1);
+          const float s_lo = tl_load_scale(p.scales, p.scales_dtype, r_lo * p.groups_per_row + grp);
+          const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + grp);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            acc[nt][0] = fmaf(s_lo, c[nt][0], acc[nt][0]);
+            acc[nt][1] = fmaf(s_lo, c[nt][1], acc[nt][1]);
+            acc[nt][2] = fmaf(s_hi, c[nt][2], acc[nt][2]);
+            acc[nt][3] = fmaf(s_hi, c[nt][3], acc[nt][3]);
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = c[nt][e];
+        }
+      }
+    }
+    ++mine;
+
+    if (ks + 1 == ta.spb || i + 1 == n) {
+      // flush this warp's 32 rows of the band
+      bool finalize = (mine == ta.spb);
+      if (!finalize) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int64_t row = int64_t(band) * kTmaBoxRows + warp * 16 + g + ((e & 2) ? 8 : 0);
+              const int col = 8 * nt + 2 * t + (e & 1);
+              if (row < p.n && col < p.m) atomicAdd(ta.scratch + int64_t(col) * p.n + row, acc[nt][e]);
+            }
+        __threadfence();
+        __syncwarp();  // every lane's partial sums are published before the count moves
+        unsigned old = 0;
+        if (lane == 0) old = atomicAdd(ta.counters + band * kTmaConsumerWarps + warp, unsigned(mine));
+        old = __shfl_sync(0xffffffffu, old, 0);
+        finalize = (old + unsigned(mine) == unsigned(ta.spb));
+        if (finalize) {
+          __threadfence();
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int64_t row = int64_t(band) * kTmaBoxRows + warp * 16 + g + ((e & 2) ? 8 : 0);
+                const int col = 8 * nt + 2 * t + (e & 1);
+                if (row < p.n && col < p.m) {
+                  float* sp = ta.scratch + int64_t(col) * p.n + row;
+                  acc[nt][e] = __ldcg(sp);
+                  __stcg(sp, 0.f);
+                }
+              }
+          if (lane == 0) ta.counters[band * kTmaConsumerWarps + warp] = 0;
+        }
+      }
+      if (finalize) {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int64_t row = int64_t(band) * kTmaBoxRows + warp * 16 + g + ((e & 2) ? 8 : 0);
+              const int col = 8 * nt + 2 * t + (e & 1);
+              if (row < p.n && col < p.m) {
+                float sc = p.wscale;
+                if (!GROUPED) sc *= tl_load_scale(p.scales, p.scales_dtype, row);
+                const float o = tl_apply_epilogue(epi, acc[nt][e] * sc, p.row0 + col, row, p.n);
+                tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, o);
+              }
+            }
+      }
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+      mine = 0;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// 6: contiguous bulk-copy persistent kernel ("bulk").
+//
+// Eight consecutive weight rows are one contiguous block of 8*K bytes.  A stage is
+// RT such blocks (about 32 KB or more), fetched with plain cp.async.bulk copies of
+// whole contiguous memory -- the access pattern HBM likes best -- into a ring of
+// shared-memory stages.  Stages are dealt to a persistent grid (one CTA per SM) in
+// equal contiguous shares.  Every stage holds complete rows, so no partial sums
+// ever cross CTAs: no scratch, no atomics.
+//
+// The batch is the 16-row MMA A operand and 8 weight rows are the B operand.
+// P consumer warps split the k range of a tile (128-wide k blocks, interleaved),
+// Q = W/P tiles are worked on at once; the P partial fragments of a tile meet in a
+// double-buffered shared array after one named barrier per stage, where
+// scale + epilogue + store happen.
+// ---------------------------------------------------------------------------
+struct BulkArgs {
+  int* status;
+  int32_t rt;            // 8-row tiles per stage
+  int32_t total_stages;
+  int32_t kb128;         // k / 128
+  int32_t p;             // warps per tile
+  uint32_t stage_bytes;  // rt * 8 * k
+};
+
+template <typename AT, bool M16, bool GROUPED>
+__global__ void __launch_bounds__(17 * 32, 1) qgemv_bulk_kernel(GemvArgs p, EpiParams epi, BulkArgs ba, int nstages,
+                                                               int cwarps) {
+  extern __shared__ uint8_t bulk_smem_raw[];
+  __shared__ uint64_t full_bar[8], empty_bar[8];
+  __shared__ int abort_flag;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(bulk_smem_raw) + 127) & ~uintptr_t(127));
+  // layout: [nstages][stage_bytes] weights, then red[2][rt][p][128] floats
+  float* red = reinterpret_cast<float*>(base + size_t(nstages) * ba.stage_bytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t T = ba.total_stages;
+  const int i0 = int(T * blockIdx.x / gridDim.x), i1 = int(T * (blockIdx.x + 1) / gridDim.x);
+  const int n = i1 - i0;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < nstages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], cwarps);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (n <= 0) return;
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  const int64_t total_bytes = int64_t(p.n) * p.k;
+
+  if (warp == cwarps) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      for (int i = 0; i < n; ++i) {
+        const int s = i % nstages;
+        if (i >= nstages && !mbar_wait(&empty_bar[s], ((i / nstages) - 1) & 1, &abort_flag)) {
+          if (!abort_flag) { abort_flag = 1; atomicExch(ba.status, TL_DEV_TIMEOUT_EMPTY); }
+          break;
+        }
+        const int64_t off = int64_t(i0 + i) * ba.stage_bytes;
+        const uint32_t bytes = uint32_t(min(int64_t(ba.stage_bytes), total_bytes - off));  // the last stage may be short
+        mbar_expect_tx(&full_bar[s], bytes);
+        uint8_t* dst = base + size_t(s) * ba.stage_bytes;
+        for (uint32_t o = 0; o < bytes; o += 32768u) {
+          const uint32_t piece = min(32768u, bytes - o);
+          asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                       ::"r"(smem_u32(dst + o)), "l"(wbytes + off + o), "r"(piece), "r"(smem_u32(&full_bar[s]))
+                       : "memory");
+        }
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers ----------------
+  const int g = lane >> 2, t = lane & 3;
+  const int kp = warp % ba.p, tq = warp / ba.p, q = cwarps / ba.p;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const bool lo_ok = g < p.m, hi_ok = M16 && (g + 8) < p.m;
+  const AT* a_lo = a + int64_t(lo_ok ? g : 0) * p.k;
+  const AT* a_hi = a + int64_t(hi_ok ? g + 8 : 0) * p.k;
+  const int cthreads = cwarps * 32;
+
+  for (int i = 0; i < n; ++i) {
+    const int s = i % nstages;
+    if (!mbar_wait(&full_bar[s], (i / nstages) & 1, &abort_flag)) {
+      if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(ba.status, TL_DEV_TIMEOUT_FULL); }
+      return;
+    }
+    const uint32_t sb = smem_u32(base + size_t(s) * ba.stage_bytes);
+    float* redbuf = red + size_t(i & 1) * ba.rt * ba.p * 128;
+    const int64_t row0 = int64_t(i0 + i) * ba.rt * 8;  // first weight row of this stage
+    for (int tile = tq; tile < ba.rt; tile += q) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      const uint32_t trow = sb + uint32_t(tile * 8 + g) * uint32_t(p.k);
+      for (int kb = kp; kb < ba.kb128; kb += ba.p) {
+        uint32_t xl[16], xh[16], w8[8];
+        if (GROUPED) {
+          // 16-byte chunks: half h covers k = 128*kb + 64*h + 16*t .. +16
+          const uint4 w0 = lds128(trow + kb * 128 + 16 * t), w1 = lds128(trow + kb * 128 + 64 + 16 * t);
+          w8[0] = w0.x; w8[1] = w0.y; w8[2] = w0.z; w8[3] = w0.w; w8[4] = w1.x; w8[5] = w1.y; w8[6] = w1.z; w8[7] = w1.w;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4* s0 = reinterpret_cast<const uint4*>(a_lo + kb * 128 + 64 * h + 16 * t);
+            const uint4* s1 = reinterpret_cast<const uint4*>(a_hi + kb * 128 + 64 * h + 16 * t);
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+              const uint4 l4 = lo_ok ? __ldg(s0 + v) : make_uint4(0, 0, 0, 0);
+              const uint4 h4 = hi_ok ? __ldg(s1 + v) : make_uint4(0, 0, 0, 0);
+              const int b = 8 * h + 4 * v;
+              xl[b] = l4.x; xl[b + 1] = l4.y; xl[b + 2] = l4.z; xl[b + 3] = l4.w;
+              xh[b] = h4.x; xh[b + 1] = h4.y; xh[b + 2] = h4.z; xh[b + 3] = h4.w;
+            }
+          }
+        } else {
+          // 32 contiguous bytes: k = 128*kb + 32*t .. +32
+          const uint4 w0 = lds128(trow + kb * 128 + 32 * t), w1 = lds128(trow + kb * 128 + 32 * t + 16);
+          w8[0] = w0.x; w8[1] = w0.y; w8[2] = w0.z; w8[3] = w0.w; w8[4] = w1.x; w8[5] = w1.y; w8[6] = w1.z; w8[7] = w1.w;
+          const uint4* s0 = reinterpret_cast<const uint4*>(a_lo + kb * 128 + 32 * t);
+          const uint4* s1 = reinterpret_cast<const uint4*>(a_hi + kb * 128 + 32 * t);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint4 l4 = lo_ok ? __ldg(s0 + v) : make_uint4(0, 0, 0, 0);
+            const uint4 h4 = hi_ok ? __ldg(s1 + v) : make_uint4(0, 0, 0, 0);
+            xl[4 * v] = l4.x; xl[4 * v + 1] = l4.y; xl[4 * v + 2] = l4.z; xl[4 * v + 3] = l4.w;
+            xh[4 * v] = h4.x; xh[4 * v + 1] = h4.y; xh[4 * v + 2] = h4.z; xh[4 * v + 3] = h4.w;
+          }
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          float c[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) c[e] = GROUPED ? 0.f : acc[e];
+#pragma unroll
+          for (int jj = 0; jj < 4; ++jj) {
+            const int j = 4 * h + jj;
+            uint32_t b0, b1;
+            MmaOps<AT>::cvt(w8[j], b0, b1);
+            MmaOps<AT>::mma(c, xl[2 * j], xh[2 * j], xl[2 * j + 1], xh[2 * j + 1], b0, b1);
+          }
+          if (GROUPED) {
+            const int grp = (kb * 128 + h * 64) / p.group;
+            const int64_t r0 = min(row0 + tile * 8 + 2 * t, int64_t(p.n) - 1), r1 = min(r0 + 1, int64_t(p.n) - 1);
+            const float s0 = tl_load_scale(p.scales, p.scales_dtype, r0 * p.groups_per_row + grp);
+            const float s1 = tl_load_scale(p.scales, p.scales_dtype, r1 * p.groups_per_row + grp);
+            acc[0] = fmaf(s0, c[0], acc[0]);
+            acc[1] = fmaf(s1, c[1], acc[1]);
+            acc[2] = fmaf(s0, c[2], acc[2]);
+            acc[3] = fmaf(s1, c[3], acc[3]);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = c[e];
+          }
+        }
+      }
+      float* dst = redbuf + (size_t(tile) * ba.p + kp) * 128;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) dst[e * 32 + lane] = acc[e];
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty_bar[s]);  // this warp no longer reads the stage
+    asm volatile("bar.sync 1, %0;" ::"r"(cthreads) : "memory");
+    // reduce the P partial fragments of every tile of the stage, then scale + epilogue + store
+    for (int o = threadIdx.x; o < ba.rt * 128; o += cthreads) {
+      const int tile = o >> 7, e = (o >> 5) & 3, ln = o & 31;
+      const float* src = redbuf + size_t(tile) * ba.p * 128 + e * 32 + ln;
+      float v = 0.f;
+      for (int w = 0; w < ba.p; ++w) v += src[w * 128];
+      const int gg = ln >> 2, tt = ln & 3;
+      const int col = gg + ((e & 2) ? 8 : 0);                      // batch row
+      const int64_t row = row0 + tile * 8 + 2 * tt + (e & 1);      // weight row = output column
+      if (row < p.n && col < p.m) {
+        float sc = p.wscale;
+        if (!GROUPED) sc *= tl_load_scale(p.scales, p.scales_dtype, row);
+        const float r = tl_apply_epilogue(epi, v * sc, p.row0 + col, row, p.n);
+        tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+      }
     }
   }
 }
@@ -806,6 +1246,12 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
     case kMma:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
              (v.p1 == 2 || v.p1 == 4);
+    case kBulk:
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 64 == 0 &&
+             (v.p0 == 8 || v.p0 == 16) && (v.p1 == 32 || v.p1 == 64) && bulk_geom(k, v.p0, v.p1).ok;
+    case kTma:
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 64 == 0 &&
+             (v.p0 == 4 || v.p0 == 5 || v.p0 == 6);
     case kRing:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
              (v.p1 == 2 || v.p1 == 4 || v.p1 == 8);
@@ -818,11 +1264,15 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
 
 int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q, tl_variant* out) {
-  (void)ctx; (void)n; (void)m;
+  (void)m;
   tl_variant v{};
   v.family = TL_FAMILY_QGEMV;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
-    v.kernel = kRing; v.p0 = 4; v.p1 = 4;
+    // few tiles: spread each tile's k range over many warps so everything is in flight at once
+    const int64_t tiles = (n + 15) / 16;
+    v.kernel = kRing;
+    if (tiles >= int64_t(ctx->sm_count) * 4) { v.p0 = 4; v.p1 = 4; }
+    else { v.p0 = 16; v.p1 = 2; }
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -846,6 +1296,9 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
       if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1) return;
     out->push_back(v);
   };
+  for (int w : {8, 16})
+    for (int kb : {32, 64}) add(kBulk, w, kb);
+  for (int st : {4, 6}) add(kTma, st, 0);
   for (int w : {2, 4, 8, 16})
     for (int u : {2, 4, 8}) add(kRing, w, u);
   for (int b : {2, 4, 8})
@@ -875,7 +1328,22 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   int block = v.p0 * 32;
   int grid = 0, launches = 1;
   SkArgs sk{};
-  if (v.kernel == kSk) {
+  TmaArgs ta{};
+  BulkArgs ba{};
+  BulkGeom bg{};
+  if (v.kernel == kBulk) {
+    bg = bulk_geom(k, v.p0, v.p1);
+    block = (v.p0 + 1) * 32;
+    ba.rt = bg.rt; ba.kb128 = int32_t(k / 128); ba.p = bg.p; ba.stage_bytes = bg.stage_bytes;
+    ba.total_stages = int32_t((n + int64_t(8) * bg.rt - 1) / (int64_t(8) * bg.rt));
+    grid = int(std::min<int64_t>(ctx->sm_count, ba.total_stages));
+  } else if (v.kernel == kTma) {
+    block = (kTmaConsumerWarps + 1) * 32;
+    ta.spb = int32_t(k / kTmaBoxBytes);
+    const int64_t bands = (n + kTmaBoxRows - 1) / kTmaBoxRows;
+    ta.total_stages = int32_t(bands * ta.spb);
+    grid = int(std::min<int64_t>(ctx->sm_count, ta.total_stages));
+  } else if (v.kernel == kSk) {
     block = 256;
     const int64_t tiles = (n + 7) / 8;
     sk.upt = int32_t(k / 128);
@@ -900,7 +1368,63 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
                           tl_variant_name(&v));
   }
   cudaStream_t s = ctx->stream;
-  if (v.kernel == kSk) {
+  if (v.kernel == kBulk) {
+    ba.status = ctx->dev_status;
+    const bool m16 = m > 8;
+#define TL_BULK_LAUNCH(AT_, M16_, G_)                                                                  \
+  do {                                                                                                \
+    auto kern = qgemv_bulk_kernel<AT_, M16_, G_>;                                                     \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bg.smem));            \
+    kern<<<grid, block, bg.smem, s>>>(p, epi, ba, bg.nstages, v.p0);                                  \
+  } while (0)
+#define TL_BULK_AT(AT_)                                                                                \
+  do {                                                                                                \
+    if (m16) { if (grouped) TL_BULK_LAUNCH(AT_, true, true); else TL_BULK_LAUNCH(AT_, true, false); } \
+    else { if (grouped) TL_BULK_LAUNCH(AT_, false, true); else TL_BULK_LAUNCH(AT_, false, false); }   \
+  } while (0)
+    if (a_dtype == TL_F16) TL_BULK_AT(__half);
+    else TL_BULK_AT(__nv_bfloat16);
+#undef TL_BULK_AT
+#undef TL_BULK_LAUNCH
+  } else if (v.kernel == kTma) {
+    const int64_t bands = (n + kTmaBoxRows - 1) / kTmaBoxRows;
+    const size_t sbytes = size_t(m) * n * sizeof(float);
+    void* base = nullptr;
+    int32_t rc = tl_ensure_zeroed_scratch(ctx, sbytes + size_t(bands) * kTmaConsumerWarps * sizeof(unsigned), &base);
+    if (rc != TL_OK) return rc;
+    ta.scratch = reinterpret_cast<float*>(base);
+    ta.counters = reinterpret_cast<unsigned*>(reinterpret_cast<uint8_t*>(base) + sbytes);
+    ta.status = ctx->dev_status;
+    CUtensorMap wmap;
+    if (!tl_encode_tmap_2d(&wmap, 1, packed, uint64_t(k), uint64_t(n), uint64_t(k), kTmaBoxBytes, kTmaBoxRows, 3))
+      return tl_set_error(ctx, TL_ERR_CUDA, "qgemv: cuTensorMapEncodeTiled failed for the %lldx%lld weight",
+                          (long long)n, (long long)k);
+    const bool two = m > 8;
+    const int st = v.p0;
+    const size_t smem = size_t(st) * kTmaStageBytes + 1024;
+#define TL_TMA_LAUNCH(AT_, NT_, G_, ST_)                                                                   \
+  do {                                                                                                    \
+    auto kern = qgemv_tma_kernel<AT_, NT_, G_, ST_>;                                                      \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));                   \
+    kern<<<grid, block, smem, s>>>(wmap, p, epi, ta);                                                     \
+  } while (0)
+#define TL_TMA_ST(AT_, NT_, G_)                                          \
+  do {                                                                  \
+    if (st == 4) TL_TMA_LAUNCH(AT_, NT_, G_, 4);                        \
+    else if (st == 5) TL_TMA_LAUNCH(AT_, NT_, G_, 5);                   \
+    else TL_TMA_LAUNCH(AT_, NT_, G_, 6);                                \
+  } while (0)
+#define TL_TMA_AT(AT_)                                                   \
+  do {                                                                  \
+    if (two) { if (grouped) TL_TMA_ST(AT_, 2, true); else TL_TMA_ST(AT_, 2, false); }  \
+    else { if (grouped) TL_TMA_ST(AT_, 1, true); else TL_TMA_ST(AT_, 1, false); }      \
+  } while (0)
+    if (a_dtype == TL_F16) TL_TMA_AT(__half);
+    else TL_TMA_AT(__nv_bfloat16);
+#undef TL_TMA_AT
+#undef TL_TMA_ST
+#undef TL_TMA_LAUNCH
+  } else if (v.kernel == kSk) {
     const int64_t tiles = (n + 7) / 8;
     const size_t sbytes = size_t(m) * n * sizeof(float);
     void* base = nullptr;
