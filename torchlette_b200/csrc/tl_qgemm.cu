@@ -1,21 +1,553 @@
-// Prefill GEMM with fused dequantization (tcgen05 / TMEM) — placeholder until the kernel lands.
+// Quantized matmul on the 5th-generation tensor cores (tcgen05 + TMEM), with the
+// int8 -> f16/bf16 dequantization fused into the operand path.  Replaces the
+// reference's explicit-dequant + tiled-matmul pair for m > 1
+// (src/backend/webgpu/ops/matmul-ops.ts:163-181, src/schedule/matmul-skeleton.ts:738-966).
+//
+//   out[m, n] = epilogue(alpha * sum_k a[m, k] * W[n, k])
+//
+// The problem is run "swapped": the WEIGHT rows are the 128-row M dimension of the
+// MMA and the tokens are its N dimension, D[128 weight rows, BN tokens] in TMEM.
+//   - a producer thread streams raw int8 weight boxes [128 rows x KSTEP bytes] and
+//     activation boxes [BN tokens x 64 k] into a shared-memory ring with TMA;
+//   - converter warps own one weight row per thread (= one TMEM lane): they read the
+//     row's bytes from the swizzled box, turn them into f16/bf16 pairs in registers
+//     (exactly; grouped scales are multiplied in here) and write them with
+//     tcgen05.st into a TMEM operand slot -- the dequantized weight never touches
+//     shared or global memory;
+//   - one thread issues tcgen05.mma with the A operand in TMEM and the activations
+//     (B) read from shared memory through a 128-byte-swizzle descriptor;
+//   - epilogue warps read the f32 accumulator back with tcgen05.ld (one weight row
+//     = one output column per thread, so the per-channel scale and the bias are
+//     per-thread constants), apply alpha / scale / the fused op chain and store.
+// Accumulators are double buffered in TMEM so the epilogue of tile i overlaps the
+// main loop of tile i+1.  One persistent CTA per SM walks the tiles, token tiles
+// fastest so that CTAs running side by side share weight boxes through L2.
+//
+// Every wait is bounded; a wait that runs out raises a status word, all roles
+// drain, TMEM is released and the kernel returns.
+#include <algorithm>
+
 #include "tl_common.cuh"
+#include "tl_tma.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------------------
+// tcgen05 wrappers
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]
+__device__ __forceinline__ void tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{ .reg .pred p; setp.ne.b32 p, %4, 0; tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p; }"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+               ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// K-major shared-memory operand descriptor, 128-byte swizzle: rows of 128 bytes,
+// 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_b_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr >> 4) & 0x3fffu);        // start address
+  d |= uint64_t(1) << 16;                           // leading byte offset (unused for swizzled K-major)
+  d |= uint64_t((1024 >> 4) & 0x3fff) << 32;        // stride byte offset between 8-row groups
+  d |= uint64_t(1) << 46;                           // descriptor version (sm_100)
+  d |= uint64_t(2) << 61;                           // layout: 128-byte swizzle
+  return d;
+}
+
+// int8 word -> two packed pairs holding q exactly (see the GEMV kernels for the bit tricks)
+template <typename AT> struct Cvt;
+template <> struct Cvt<__half> {
+  static constexpr uint32_t kFmt = 0;  // instruction-descriptor operand format
+  __device__ static void word(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t x = w ^ 0x80808080u;
+    const uint32_t l = __byte_perm(x, 0x64646464u, 0x4140), h = __byte_perm(x, 0x64646464u, 0x4342);
+    const uint32_t magic = 0x64806480u;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(l), "r"(magic));
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h), "r"(magic));
+  }
+  __device__ static uint32_t mul(uint32_t a, uint32_t s) {
+    uint32_t r;
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(s));
+    return r;
+  }
+  __device__ static uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+  }
+  __device__ static uint32_t splat(float s) {
+    const __half2 h = __float2half2_rn(s);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  __device__ static uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+};
+template <> struct Cvt<__nv_bfloat16> {
+  static constexpr uint32_t kFmt = 1;
+  __device__ static void word(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t l = __byte_perm(w, 0u, 0x4140), h = __byte_perm(w, 0u, 0x4342);
+    const uint32_t lm = (l & 0x007f007fu) | 0x43004300u, lc = (l & 0x00800080u) | 0x43004300u;
+    const uint32_t hm = (h & 0x007f007fu) | 0x43004300u, hc = (h & 0x00800080u) | 0x43004300u;
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(lm), "r"(lc));
+    asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(hm), "r"(hc));
+  }
+  __device__ static uint32_t mul(uint32_t a, uint32_t s) {
+    uint32_t r;
+    asm("mul.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(s));
+    return r;
+  }
+  __device__ static uint32_t fma(uint32_t a, uint32_t b, uint32_t c) {
+    uint32_t r;
+    asm("fma.rn.bf16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+  }
+  __device__ static uint32_t splat(float s) {
+    const __nv_bfloat162 h = __float2bfloat162_rn(s);
+    return *reinterpret_cast<const uint32_t*>(&h);
+  }
+  __device__ static uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+};
+
+struct GemmArgs {
+  const void* scales;
+  void* out;
+  int64_t m, n, k;
+  int32_t group, groups_per_row, scales_dtype, out_dtype;
+  float wscale;
+  int* status;
+  int32_t n_tiles, m_tiles, ksteps;
+};
+
+constexpr int kTileRows = 128;  // weight rows per CTA tile = TMEM lanes
+
+__host__ __device__ constexpr uint32_t pow2_at_least(uint32_t v) {
+  uint32_t p = 32;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+template <typename AT, int BN, int KSTEP, int STAGES, int NCW, bool GROUPED>
+__global__ void __launch_bounds__((NCW + 6) * 32, 1)
+qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap, GemmArgs p,
+                EpiParams epi) {
+  static_assert(KSTEP == 64 || KSTEP == 128, "one weight box row is 64 or 128 bytes");
+  static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
+  static_assert(NCW == 4 || NCW == 8, "converter warps");
+  constexpr int kWBytes = kTileRows * KSTEP;        // int8 weight box
+  constexpr int kABox = BN * 128;                   // one [BN x 64] activation box
+  constexpr int kABoxes = KSTEP / 64;
+  constexpr int kStageBytes = kWBytes + kABoxes * kABox;
+  constexpr int kSlotCols = KSTEP / 2;              // TMEM columns of one dequantized operand slot
+  constexpr uint32_t kTmemCols = pow2_at_least(2 * BN + STAGES * kSlotCols);
+  static_assert(kTmemCols <= 512, "TMEM budget");
+  constexpr int kParts = NCW / 4;                   // converter threads per weight row
+  constexpr int kChunks = KSTEP / 16 / kParts;      // 16-byte chunks per converter thread and stage
+  constexpr int kEpiWarp0 = NCW, kProducerWarp = NCW + 4, kMmaWarp = NCW + 5;
+  constexpr uint32_t kIdesc = (1u << 4) | (Cvt<AT>::kFmt << 7) | (Cvt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
+                              (uint32_t(kTileRows >> 4) << 24);
+
+  extern __shared__ uint8_t gemm_smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], aready_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint32_t tmem_base_smem;
+  __shared__ int abort_flag;
+  uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&aready_bar[s], NCW * 32);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tfull_bar[b], 1);
+      mbar_init(&tempty_bar[b], 4 * 32);
+    }
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kMmaWarp) {
+    tmem_alloc(&tmem_base_smem, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_smem;
+  const int total_tiles = p.n_tiles * p.m_tiles;
+
+  if (warp == kProducerWarp) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&wmap);
+      tma_prefetch_desc(&amap);
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
+        const int n_tile = tile / p.m_tiles, m_tile = tile - n_tile * p.m_tiles;
+        for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, &abort_flag)) {
+            if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_EMPTY); }
+            break;
+          }
+          uint8_t* st = stages + size_t(s) * kStageBytes;
+          mbar_expect_tx(&full_bar[s], kStageBytes);
+          tma_load_2d(st, &wmap, ks * KSTEP, n_tile * kTileRows, &full_bar[s]);
+#pragma unroll
+          for (int b = 0; b < kABoxes; ++b)
+            tma_load_2d(st + kWBytes + b * kABox, &amap, ks * KSTEP + b * 64, m_tile * BN, &full_bar[s]);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      int it = 0, tl = 0;
+      for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x, ++tl) {
+        const int acc = tl & 1;
+        if (tl >= 2 && !mbar_wait(&tempty_bar[acc], ((tl >> 1) - 1) & 1, &abort_flag)) {
+          if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        bool ok = true;
+        for (int ks = 0; ks < p.ksteps && ok; ++ks, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          ok = mbar_wait(&full_bar[s], ph, &abort_flag) && mbar_wait(&aready_bar[s], ph, &abort_flag);
+          if (!ok) {
+            if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(stages + size_t(s) * kStageBytes + kWBytes);
+          const uint32_t a_tmem = tmem_base + uint32_t(2 * BN + s * kSlotCols);
+#pragma unroll
+          for (int kk = 0; kk < KSTEP / 16; ++kk) {
+            const uint64_t bdesc = make_b_desc(a_base + (kk >> 2) * kABox + (kk & 3) * 32);
+            tc_mma_ts(d_tmem, a_tmem + kk * 8, bdesc, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[s]);  // the stage (both operands) is free once these MMAs have run
+        }
+        if (!ok) break;
+        tc_commit(&tfull_bar[acc]);
+      }
+    }
+  } else if (warp < NCW) {
+    // ------------------------------ converters ------------------------------
+    const int quad = warp & 3, part = warp >> 2;
+    const int r = quad * 32 + lane;  // weight row inside the tile = TMEM lane
+    const uint32_t swz = KSTEP == 128 ? uint32_t(r & 7) : uint32_t((r >> 1) & 3);
+    const uint32_t row_off = uint32_t(r) * KSTEP;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      const int n_tile = tile / p.m_tiles;
+      const int64_t grow = min(int64_t(n_tile) * kTileRows + r, p.n - 1);
+      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+        const int s = it % STAGES;
+        if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag)) {
+          if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t wb = smem_u32(stages + size_t(s) * kStageBytes) + row_off;
+        const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + s * kSlotCols);
+        uint4 raw[kChunks];
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) raw[i] = lds128(wb + ((uint32_t(part * kChunks + i) ^ swz) << 4));
+#pragma unroll
+        for (int i = 0; i < kChunks; ++i) {
+          const int c = part * kChunks + i;
+          uint32_t v[8];
+          if (GROUPED) {
+            // exact: q -> f32 by exponent stuffing, one f32 multiply by the group scale, one
+            // rounding to the 16-bit operand type (the oracle's dequantize-then-round)
+            const int grp = (ks * KSTEP + c * 16) / p.group;
+            const float sc = (grp < p.groups_per_row ? tl_load_scale(p.scales, p.scales_dtype, grow * p.groups_per_row + grp) : 0.f) * p.wscale;
+            const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint32_t x = w4[j] ^ 0x80808080u;
+              const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
+              const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
+              const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
+              const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
+              v[2 * j] = Cvt<AT>::pack(f0, f1);
+              v[2 * j + 1] = Cvt<AT>::pack(f2, f3);
+            }
+          } else {
+            Cvt<AT>::word(raw[i].x, v[0], v[1]);
+            Cvt<AT>::word(raw[i].y, v[2], v[3]);
+            Cvt<AT>::word(raw[i].z, v[4], v[5]);
+            Cvt<AT>::word(raw[i].w, v[6], v[7]);
+          }
+          tmem_st8(slot + c * 8, v);
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive(&aready_bar[s]);
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ------------------------------
+    const int quad = (warp - kEpiWarp0) & 3;
+    const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    int tl = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tl) {
+      const int acc = tl & 1;
+      const int n_tile = tile / p.m_tiles, m_tile = tile - n_tile * p.m_tiles;
+      const int64_t ncol = int64_t(n_tile) * kTileRows + quad * 32 + lane;  // this thread's output column
+      const bool n_ok = ncol < p.n;
+      float sc = p.wscale;
+      if (!GROUPED) sc *= n_ok ? tl_load_scale(p.scales, p.scales_dtype, ncol) : 0.f;
+      if (GROUPED) sc = 1.f;  // group scales (and the convention factor) went in at conversion
+      if (!mbar_wait(&tfull_bar[acc], (tl >> 1) & 1, &abort_flag)) {
+        if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
+        break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 16) {
+        uint32_t v[16];
+        tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + c0), v);
+        tmem_ld_wait();
+        const int64_t m0 = int64_t(m_tile) * BN + c0;
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int64_t row = m0 + j;  // token
+          if (n_ok && row < p.m) {
+            const float o = tl_apply_epilogue(epi, __uint_as_float(v[j]) * sc, row, ncol, p.n);
+            tl_store_out(p.out, p.out_dtype, row * p.n + ncol, o);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty_bar[acc]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+constexpr int kTc = 0, kSliced = 1;
+
+struct TcConfig { int bn, kstep, stages, ncw; };
+// the instantiated tile configurations (tl_variant p0..p3)
+const TcConfig kTcConfigs[] = {{192, 64, 4, 4}, {192, 64, 4, 8}, {128, 64, 6, 4}, {128, 64, 6, 8},
+                               {64, 128, 6, 8}, {32, 128, 7, 8}, {16, 128, 7, 8}};
+
+bool tc_config_known(const tl_variant& v) {
+  for (const auto& c : kTcConfigs)
+    if (c.bn == v.p0 && c.kstep == v.p1 && c.stages == v.p2 && c.ncw == v.p3) return true;
+  return false;
+}
+
+template <typename AT, int BN, int KSTEP, int STAGES, int NCW>
+cudaError_t launch_tc(bool grouped, int grid, cudaStream_t s, const CUtensorMap& wmap, const CUtensorMap& amap,
+                      const GemmArgs& p, const EpiParams& e) {
+  constexpr size_t smem = size_t(STAGES) * (kTileRows * KSTEP + (KSTEP / 64) * BN * 128) + 1024;
+  constexpr int block = (NCW + 6) * 32;
+  if (grouped) {
+    auto kern = qgemm_tc_kernel<AT, BN, KSTEP, STAGES, NCW, true>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    kern<<<grid, block, smem, s>>>(wmap, amap, p, e);
+  } else {
+    auto kern = qgemm_tc_kernel<AT, BN, KSTEP, STAGES, NCW, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    kern<<<grid, block, smem, s>>>(wmap, amap, p, e);
+  }
+  return cudaGetLastError();
+}
+
+template <typename AT>
+cudaError_t launch_tc_cfg(const tl_variant& v, bool grouped, int grid, cudaStream_t s, const CUtensorMap& wmap,
+                          const CUtensorMap& amap, const GemmArgs& p, const EpiParams& e) {
+#define TL_TC_CASE(BN_, KS_, ST_, NCW_)                                             \
+  if (v.p0 == BN_ && v.p1 == KS_ && v.p2 == ST_ && v.p3 == NCW_)                   \
+    return launch_tc<AT, BN_, KS_, ST_, NCW_>(grouped, grid, s, wmap, amap, p, e);
+  TL_TC_CASE(192, 64, 4, 4)
+  TL_TC_CASE(192, 64, 4, 8)
+  TL_TC_CASE(128, 64, 6, 4)
+  TL_TC_CASE(128, 64, 6, 8)
+  TL_TC_CASE(64, 128, 6, 8)
+  TL_TC_CASE(32, 128, 7, 8)
+  TL_TC_CASE(16, 128, 7, 8)
+#undef TL_TC_CASE
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace
 
 bool tl_qgemm_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q) {
-  (void)v; (void)m; (void)n; (void)k; (void)a_dtype; (void)q;
-  return false;
+  (void)n;
+  if (v.family != TL_FAMILY_QGEMM || m < 1) return false;
+  if (v.kernel == kSliced) return true;
+  if (v.kernel != kTc) return false;
+  return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0 && tc_config_known(v);
 }
-int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t, int64_t, int64_t, int32_t, const tl_quant_desc&, tl_variant* out) {
-  (void)ctx;
-  *out = tl_variant{TL_FAMILY_QGEMM, 0, 0, 0, 0, 0};
+
+int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
+                                 const tl_quant_desc& q, tl_variant* out) {
+  (void)ctx; (void)n;
+  tl_variant v{};
+  v.family = TL_FAMILY_QGEMM;
+  if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0) {
+    v.kernel = kTc;
+    if (m <= 16) { v.p0 = 16; v.p1 = 128; v.p2 = 7; v.p3 = 8; }
+    else if (m <= 32) { v.p0 = 32; v.p1 = 128; v.p2 = 7; v.p3 = 8; }
+    else if (m <= 64) { v.p0 = 64; v.p1 = 128; v.p2 = 6; v.p3 = 8; }
+    else {
+      // fewest padded token rows; ties go to the wider tile
+      const int64_t pad192 = (m + 191) / 192 * 192, pad128 = (m + 127) / 128 * 128;
+      if (pad192 <= pad128) { v.p0 = 192; v.p1 = 64; v.p2 = 4; v.p3 = 4; }
+      else { v.p0 = 128; v.p1 = 64; v.p2 = 6; v.p3 = 4; }
+    }
+  } else {
+    v.kernel = kSliced;  // f32 activations or odd K: sixteen-row slices through the small-batch kernels
+  }
+  *out = v;
   return TL_OK;
 }
-int32_t tl_qgemm_candidates(tl_ctx*, int64_t, int64_t, int64_t, int32_t, const tl_quant_desc&, std::vector<tl_variant>* out) {
+
+int32_t tl_qgemm_candidates(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q,
+                            std::vector<tl_variant>* out) {
+  tl_variant d;
+  tl_qgemm_default_variant(ctx, m, n, k, a_dtype, q, &d);
   out->clear();
+  out->push_back(d);
+  if (d.kernel != kTc) return TL_OK;
+  for (const auto& c : kTcConfigs) {
+    if (c.bn < 64 && m > 4 * c.bn) continue;  // narrow token tiles re-stream the weight too often
+    tl_variant v{TL_FAMILY_QGEMM, kTc, c.bn, c.kstep, c.stages, c.ncw};
+    bool dup = false;
+    for (const auto& o : *out) dup = dup || (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1 && o.p2 == v.p2 && o.p3 == v.p3);
+    if (!dup) out->push_back(v);
+  }
   return TL_OK;
 }
-int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant&, const void*, int32_t, const void*, const void*, void*, int32_t,
-                        int64_t, int64_t, int64_t, const tl_quant_desc&, const EpiParams&, tl_plan_receipt*) {
-  return tl_set_error(ctx, TL_ERR_UNIMPLEMENTED, "tl_qgemm_nt: not implemented yet");
+
+int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t a_dtype, const void* packed,
+                        const void* scales, void* out, int32_t out_dtype, int64_t m, int64_t n, int64_t k,
+                        const tl_quant_desc& q, const EpiParams& epi, tl_plan_receipt* receipt) {
+  if (!tl_qgemm_variant_applicable(v, m, n, k, a_dtype, q))
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "qgemm: variant %s cannot run m=%lld n=%lld k=%lld G=%d %s",
+                        tl_variant_name(&v), (long long)m, (long long)n, (long long)k, q.group_size,
+                        tl_dtype_name(a_dtype));
+  if (v.kernel == kSliced) {
+    if (receipt) {
+      receipt->choice = v;
+      receipt->grid[0] = int32_t((m + 15) / 16); receipt->grid[1] = 1; receipt->grid[2] = 1;
+      receipt->block = 0; receipt->split_k = 1;
+      return TL_OK;
+    }
+    for (int64_t m0 = 0; m0 < m; m0 += 16) {
+      const int32_t ms = int32_t(std::min<int64_t>(16, m - m0));
+      tl_variant gv;
+      int32_t rc = tl_qgemv_default_variant(ctx, ms, n, k, a_dtype, q, &gv);
+      if (rc != TL_OK) return rc;
+      EpiParams e = epi;  // full-size binary operands are indexed by absolute token row: shift them per slice
+      const float* shifted[TL_EPI_MAX_INPUTS];
+      bool is_binary[TL_EPI_MAX_INPUTS] = {false, false, false, false};
+      for (int i = 0; i < e.n_ops; ++i)
+        if (e.kind[i] == TL_EPI_BINARY) is_binary[e.idx[i]] = true;
+      for (int i = 0; i < TL_EPI_MAX_INPUTS; ++i) {
+        shifted[i] = (is_binary[i] && epi.inputs[i]) ? epi.inputs[i] + m0 * n : epi.inputs[i];
+        e.inputs[i] = shifted[i];
+      }
+      rc = tl_launch_qgemv(ctx, gv, reinterpret_cast<const uint8_t*>(a) + size_t(m0) * k * tl_dtype_size(a_dtype),
+                           a_dtype, packed, scales,
+                           reinterpret_cast<uint8_t*>(out) + size_t(m0) * n * tl_dtype_size(out_dtype), out_dtype, ms, n,
+                           k, q, e, nullptr);
+      if (rc != TL_OK) return rc;
+    }
+    return TL_OK;
+  }
+
+  const int bn = v.p0, kstep = v.p1;
+  GemmArgs p{};
+  p.scales = scales; p.out = out; p.m = m; p.n = n; p.k = k;
+  p.group = q.group_size; p.groups_per_row = int32_t(k / q.group_size);
+  p.scales_dtype = q.scales_dtype; p.out_dtype = out_dtype;
+  p.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+  p.status = ctx->dev_status;
+  p.n_tiles = int32_t((n + kTileRows - 1) / kTileRows);
+  p.m_tiles = int32_t((m + bn - 1) / bn);
+  p.ksteps = int32_t((k + kstep - 1) / kstep);
+  const int64_t tiles = int64_t(p.n_tiles) * p.m_tiles;
+  const int grid = int(std::min<int64_t>(ctx->sm_count, tiles));
+  if (receipt) {
+    receipt->choice = v;
+    receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
+    receipt->block = (v.p3 + 6) * 32; receipt->split_k = 1;
+    return TL_OK;
+  }
+  if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "qgemm: weight and activation pointers must be 16-byte aligned");
+  CUtensorMap wmap, amap;
+  if (!tl_encode_tmap_2d(&wmap, 1, packed, uint64_t(k), uint64_t(n), uint64_t(k), uint32_t(kstep), kTileRows,
+                         kstep == 128 ? 3 : 2) ||
+      !tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, 64, uint32_t(bn), 3))
+    return tl_set_error(ctx, TL_ERR_CUDA, "qgemm: cuTensorMapEncodeTiled failed (m=%lld n=%lld k=%lld)", (long long)m,
+                        (long long)n, (long long)k);
+  const bool grouped = q.group_size != k;
+  cudaError_t e = a_dtype == TL_F16 ? launch_tc_cfg<__half>(v, grouped, grid, ctx->stream, wmap, amap, p, epi)
+                                    : launch_tc_cfg<__nv_bfloat16>(v, grouped, grid, ctx->stream, wmap, amap, p, epi);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "qgemm: launch failed: %s", cudaGetErrorString(e));
+  }
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  return TL_OK;
 }
