@@ -16,8 +16,8 @@ from torchlette_b200 import binding as B
 
 pytestmark = pytest.mark.gpu
 
-TC_CONFIGS = [(2, 0, 192, 64, 4, 4), (2, 0, 192, 64, 4, 8), (2, 0, 128, 64, 6, 4), (2, 0, 128, 64, 6, 8),
-              (2, 0, 64, 128, 6, 8), (2, 0, 32, 128, 7, 8), (2, 0, 16, 128, 7, 8)]
+TC_CONFIGS = [(2, 0, 192, 64, 6, 4), (2, 0, 192, 64, 6, 8), (2, 0, 128, 64, 8, 4), (2, 0, 128, 64, 8, 8),
+              (2, 0, 64, 128, 6, 8), (2, 0, 32, 128, 8, 8), (2, 0, 16, 128, 8, 8)]
 
 
 def _gemm_case(be, m, n, k, act_dtype, out_dtype, variant=None, bias=False, act=None, seed=0, rows=None):
@@ -62,7 +62,7 @@ def test_qgemm_default_selection_shapes(backend, m, n, k):
 
 def test_qgemm_many_tiles_per_cta_exercises_both_accumulators(backend):
     # 8 x 40 = 320 tiles of 128 x 128 on 148 CTAs: every CTA walks several tiles and both TMEM buffers
-    got, ref = _gemm_case(backend, 1024, 5120, 256, "bf16", "f32", (2, 0, 128, 64, 6, 4), bias=True, seed=11,
+    got, ref = _gemm_case(backend, 1024, 5120, 256, "bf16", "f32", (2, 0, 128, 64, 8, 4), bias=True, seed=11,
                           rows=[0, 1, 127, 128, 129, 511, 512, 1023])
     assert cases.rel_err(got, ref) <= 1e-3
 

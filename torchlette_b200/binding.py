@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "csrc", "libtlcuda.so")
+LIB_PATH = os.environ.get("TLCUDA_LIB") or os.path.join(_HERE, "csrc", "libtlcuda.so")
 
 TL_OK = 0
 TL_ERR_INVALID_ARG, TL_ERR_UNSUPPORTED, TL_ERR_CUDA, TL_ERR_NCCL = -1, -2, -3, -4

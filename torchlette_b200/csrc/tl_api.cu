@@ -411,6 +411,7 @@ int32_t tl_check_qargs(tl_ctx* ctx, const char* who, const void* a, int32_t a_dt
 int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* out, bool* has_ops) {
   memset(out, 0, sizeof(*out));
   out->alpha = alpha;
+  out->fast = 1;
   *has_ops = false;
   if (!e) return TL_OK;
   if (e->n_ops < 0 || e->n_ops > TL_EPI_MAX_OPS)
@@ -453,6 +454,18 @@ int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* o
   }
   out->n_ops = n;
   *has_ops = n > 0;
+  // recognise [bias] [unary] [cast]* (a trailing cast is repeated by the store, so only
+  // a cast to a type the store keeps exactly may be dropped: leave chains with casts generic
+  // unless the cast is last)
+  {
+    int i = 0;
+    out->fast = 1;
+    out->fast_unary = 0;
+    out->fast_bias = nullptr;
+    if (i < n && out->kind[i] == TL_EPI_BIAS) out->fast_bias = out->inputs[out->idx[i++]];
+    if (i < n && out->kind[i] == TL_EPI_UNARY) out->fast_unary = out->op[i++];
+    if (i != n) out->fast = 0;
+  }
   return TL_OK;
 }
 

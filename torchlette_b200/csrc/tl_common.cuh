@@ -109,6 +109,11 @@ struct EpiParams {
   int32_t idx[TL_EPI_MAX_OPS];  // input index (bias/binary) or to_dtype (cast)
   const float* inputs[TL_EPI_MAX_INPUTS];
   float alpha;
+  // Pre-decoded form of the common chain [bias] [unary] [cast to the output type]: kernels
+  // with many outputs per thread evaluate it without walking the op list.
+  int32_t fast;           // 1 when the chain has that form (an empty chain included)
+  int32_t fast_unary;     // TL_UNARY_* or 0
+  const float* fast_bias; // [N] or null
 };
 
 // Validates an epilogue description and flattens it; returns TL_OK or an error
@@ -189,6 +194,25 @@ __device__ __forceinline__ float tl_unary(int op, float x) {
       return (0.5f * x) * (1.f + (u < 0.f ? -er : er));
     }
     default: return x;
+  }
+}
+
+// Hardware-approximated bodies (tanh.approx / ex2.approx, ~2^-11 absolute on tanh): used
+// only when the result is stored as f16/bf16, whose own rounding is coarser.
+__device__ __forceinline__ float tl_tanh_approx(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float tl_unary_approx(int op, float x) {
+  switch (op) {
+    case TL_UNARY_RELU: return x > 0.f ? x : 0.f;
+    case TL_UNARY_SILU: return __fdividef(x, 1.f + __expf(-x));
+    case TL_UNARY_SIGMOID: return __fdividef(1.f, 1.f + __expf(-x));
+    case TL_UNARY_TANH: return tl_tanh_approx(x);
+    case TL_UNARY_GELU_TANH:
+      return (0.5f * x) * (1.f + tl_tanh_approx(0.7978845608f * (x + 0.044715f * (x * (x * x)))));
+    default: return tl_unary(op, x);
   }
 }
 

@@ -166,7 +166,7 @@ __host__ __device__ constexpr uint32_t pow2_at_least(uint32_t v) {
 }
 
 template <typename AT, int BN, int KSTEP, int STAGES, int NCW, bool GROUPED>
-__global__ void __launch_bounds__((NCW + 6) * 32, 1)
+__global__ void __launch_bounds__((NCW + 10) * 32, 1)
 qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap amap, GemmArgs p,
                 EpiParams epi) {
   static_assert(KSTEP == 64 || KSTEP == 128, "one weight box row is 64 or 128 bytes");
@@ -177,16 +177,21 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
   constexpr int kABoxes = KSTEP / 64;
   constexpr int kStageBytes = kWBytes + kABoxes * kABox;
   constexpr int kSlotCols = KSTEP / 2;              // TMEM columns of one dequantized operand slot
-  constexpr uint32_t kTmemCols = pow2_at_least(2 * BN + STAGES * kSlotCols);
+  // The shared-memory ring (STAGES deep) has to cover the TMA round trip; the TMEM operand
+  // ring only has to cover conversion -> MMA, so it is sized by what TMEM has left (TS slots).
+  constexpr int kFreeCols = 512 - 2 * BN;
+  constexpr int TS = (kFreeCols / kSlotCols) < STAGES ? (kFreeCols / kSlotCols) : STAGES;
+  static_assert(TS >= 2, "TMEM operand ring");
+  constexpr uint32_t kTmemCols = pow2_at_least(2 * BN + TS * kSlotCols);
   static_assert(kTmemCols <= 512, "TMEM budget");
   constexpr int kParts = NCW / 4;                   // converter threads per weight row
   constexpr int kChunks = KSTEP / 16 / kParts;      // 16-byte chunks per converter thread and stage
-  constexpr int kEpiWarp0 = NCW, kProducerWarp = NCW + 4, kMmaWarp = NCW + 5;
+  constexpr int kEpiWarp0 = NCW, kEpiWarps = 8, kProducerWarp = NCW + 8, kMmaWarp = NCW + 9;
   constexpr uint32_t kIdesc = (1u << 4) | (Cvt<AT>::kFmt << 7) | (Cvt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
                               (uint32_t(kTileRows >> 4) << 24);
 
   extern __shared__ uint8_t gemm_smem_raw[];
-  __shared__ uint64_t full_bar[STAGES], aready_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], aready_bar[TS], slotfree_bar[TS], tfull_bar[2], tempty_bar[2];
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -195,12 +200,15 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(&full_bar[s], 1);
-      mbar_init(&aready_bar[s], NCW * 32);
       mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < TS; ++s) {
+      mbar_init(&aready_bar[s], NCW * 32);
+      mbar_init(&slotfree_bar[s], 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
-      mbar_init(&tempty_bar[b], 4 * 32);
+      mbar_init(&tempty_bar[b], kEpiWarps * 32);
     }
     abort_flag = 0;
     mbar_fence_init();
@@ -252,22 +260,23 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         bool ok = true;
         for (int ks = 0; ks < p.ksteps && ok; ++ks, ++it) {
-          const int s = it % STAGES;
-          const uint32_t ph = (it / STAGES) & 1;
-          ok = mbar_wait(&full_bar[s], ph, &abort_flag) && mbar_wait(&aready_bar[s], ph, &abort_flag);
+          const int s = it % STAGES, sl = it % TS;
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag) &&
+               mbar_wait(&aready_bar[sl], (it / TS) & 1, &abort_flag);
           if (!ok) {
             if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
             break;
           }
           tc_fence_after();
           const uint32_t a_base = smem_u32(stages + size_t(s) * kStageBytes + kWBytes);
-          const uint32_t a_tmem = tmem_base + uint32_t(2 * BN + s * kSlotCols);
+          const uint32_t a_tmem = tmem_base + uint32_t(2 * BN + sl * kSlotCols);
 #pragma unroll
           for (int kk = 0; kk < KSTEP / 16; ++kk) {
             const uint64_t bdesc = make_b_desc(a_base + (kk >> 2) * kABox + (kk & 3) * 32);
             tc_mma_ts(d_tmem, a_tmem + kk * 8, bdesc, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
           }
-          tc_commit(&empty_bar[s]);  // the stage (both operands) is free once these MMAs have run
+          tc_commit(&empty_bar[s]);      // the shared-memory stage is free once these MMAs have run
+          tc_commit(&slotfree_bar[sl]);  // and so is the TMEM operand slot
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
@@ -280,61 +289,74 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     const uint32_t swz = KSTEP == 128 ? uint32_t(r & 7) : uint32_t((r >> 1) & 3);
     const uint32_t row_off = uint32_t(r) * KSTEP;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    int it = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-      const int n_tile = tile / p.m_tiles;
-      const int64_t grow = min(int64_t(n_tile) * kTileRows + r, p.n - 1);
-      for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
-        const int s = it % STAGES;
-        if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag)) {
-          if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
-          ok = false;
-          break;
-        }
-        tc_fence_after();
-        const uint32_t wb = smem_u32(stages + size_t(s) * kStageBytes) + row_off;
-        const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + s * kSlotCols);
-        uint4 raw[kChunks];
+    // Flat walk over (tile, k-step).  The loop is software pipelined: the bytes of step i+1 are
+    // read and converted into registers while the TMEM stores of step i are still landing, and
+    // only then does the thread wait for those stores and signal the MMA issuer.
+    const int my_tiles = (total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
+    const int total_it = my_tiles * p.ksteps;
+    uint32_t v[kChunks][8];
+    auto convert = [&](int it) -> bool {
+      const int s = it % STAGES;
+      const int tl = it / p.ksteps, ks = it - tl * p.ksteps;
+      if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag)) return false;
+      const uint32_t wb = smem_u32(stages + size_t(s) * kStageBytes) + row_off;
+      uint4 raw[kChunks];
 #pragma unroll
-        for (int i = 0; i < kChunks; ++i) raw[i] = lds128(wb + ((uint32_t(part * kChunks + i) ^ swz) << 4));
-#pragma unroll
-        for (int i = 0; i < kChunks; ++i) {
-          const int c = part * kChunks + i;
-          uint32_t v[8];
-          if (GROUPED) {
-            // exact: q -> f32 by exponent stuffing, one f32 multiply by the group scale, one
-            // rounding to the 16-bit operand type (the oracle's dequantize-then-round)
-            const int grp = (ks * KSTEP + c * 16) / p.group;
-            const float sc = (grp < p.groups_per_row ? tl_load_scale(p.scales, p.scales_dtype, grow * p.groups_per_row + grp) : 0.f) * p.wscale;
-            const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t x = w4[j] ^ 0x80808080u;
-              const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
-              const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
-              const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
-              const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
-              v[2 * j] = Cvt<AT>::pack(f0, f1);
-              v[2 * j + 1] = Cvt<AT>::pack(f2, f3);
-            }
-          } else {
-            Cvt<AT>::word(raw[i].x, v[0], v[1]);
-            Cvt<AT>::word(raw[i].y, v[2], v[3]);
-            Cvt<AT>::word(raw[i].z, v[4], v[5]);
-            Cvt<AT>::word(raw[i].w, v[6], v[7]);
-          }
-          tmem_st8(slot + c * 8, v);
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        mbar_arrive(&aready_bar[s]);
+      for (int i = 0; i < kChunks; ++i) raw[i] = lds128(wb + ((uint32_t(part * kChunks + i) ^ swz) << 4));
+      int64_t grow = 0;
+      if (GROUPED) {
+        const int n_tile = (int(blockIdx.x) + tl * int(gridDim.x)) / p.m_tiles;
+        grow = min(int64_t(n_tile) * kTileRows + r, p.n - 1);
       }
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) {
+        const int c = part * kChunks + i;
+        if (GROUPED) {
+          // exact: q -> f32 by exponent stuffing, one f32 multiply by the group scale, one
+          // rounding to the 16-bit operand type (the oracle's dequantize-then-round)
+          const int grp = (ks * KSTEP + c * 16) / p.group;
+          const float sc = (grp < p.groups_per_row ? tl_load_scale(p.scales, p.scales_dtype, grow * p.groups_per_row + grp) : 0.f) * p.wscale;
+          const uint32_t w4[4] = {raw[i].x, raw[i].y, raw[i].z, raw[i].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t x = w4[j] ^ 0x80808080u;
+            const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
+            const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
+            const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
+            const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
+            v[i][2 * j] = Cvt<AT>::pack(f0, f1);
+            v[i][2 * j + 1] = Cvt<AT>::pack(f2, f3);
+          }
+        } else {
+          Cvt<AT>::word(raw[i].x, v[i][0], v[i][1]);
+          Cvt<AT>::word(raw[i].y, v[i][2], v[i][3]);
+          Cvt<AT>::word(raw[i].z, v[i][4], v[i][5]);
+          Cvt<AT>::word(raw[i].w, v[i][6], v[i][7]);
+        }
+      }
+      return true;
+    };
+    bool ok = total_it > 0 && convert(0);
+    for (int it = 0; it < total_it && ok; ++it) {
+      const int sl = it % TS;
+      if (it >= TS && !mbar_wait(&slotfree_bar[sl], ((it / TS) - 1) & 1, &abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + sl * kSlotCols);
+#pragma unroll
+      for (int i = 0; i < kChunks; ++i) tmem_st8(slot + (part * kChunks + i) * 8, v[i]);
+      if (it + 1 < total_it) ok = convert(it + 1);  // overlaps the stores above
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&aready_bar[sl]);
     }
+    if (!ok && lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int quad = (warp - kEpiWarp0) & 3;
+    const int quad = (warp - kEpiWarp0) & 3, ehalf = (warp - kEpiWarp0) >> 2;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
+    // this warp's share of the BN token columns, in chunks of 16
+    constexpr int kChunksN = BN / 16;
+    const int cbeg = ehalf == 0 ? 0 : (kChunksN + 1) / 2, cend = ehalf == 0 ? (kChunksN + 1) / 2 : kChunksN;
     int tl = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tl) {
       const int acc = tl & 1;
@@ -344,24 +366,44 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
       float sc = p.wscale;
       if (!GROUPED) sc *= n_ok ? tl_load_scale(p.scales, p.scales_dtype, ncol) : 0.f;
       if (GROUPED) sc = 1.f;  // group scales (and the convention factor) went in at conversion
+      const bool fast = epi.fast != 0, approx = p.out_dtype != TL_F32;
+      const float sca = sc * epi.alpha;
+      const float bias = (fast && epi.fast_bias && n_ok) ? __ldg(epi.fast_bias + ncol) : 0.f;
+      const int esz = p.out_dtype == TL_F32 ? 4 : 2;
+      const int64_t row_bytes = p.n * esz;
       if (!mbar_wait(&tfull_bar[acc], (tl >> 1) & 1, &abort_flag)) {
         if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
         break;
       }
       tc_fence_after();
+      uint32_t vn[16];
+      if (cbeg < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + cbeg * 16), vn);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int ch = cbeg; ch < cend; ++ch) {
+        const int c0 = ch * 16;
         uint32_t v[16];
-        tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + c0), v);
         tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = vn[j];
+        if (ch + 1 < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + c0 + 16), vn);  // next chunk in flight
         const int64_t m0 = int64_t(m_tile) * BN + c0;
+        const int jmax = n_ok ? int(min(int64_t(16), p.m - m0)) : 0;
+        uint8_t* optr = reinterpret_cast<uint8_t*>(p.out) + m0 * row_bytes + ncol * esz;
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
-          const int64_t row = m0 + j;  // token
-          if (n_ok && row < p.m) {
-            const float o = tl_apply_epilogue(epi, __uint_as_float(v[j]) * sc, row, ncol, p.n);
-            tl_store_out(p.out, p.out_dtype, row * p.n + ncol, o);
+          if (j < jmax) {
+            float o;
+            if (fast) {
+              o = fmaf(__uint_as_float(v[j]), sca, bias);
+              if (epi.fast_unary) o = approx ? tl_unary_approx(epi.fast_unary, o) : tl_unary(epi.fast_unary, o);
+            } else {
+              o = tl_apply_epilogue(epi, __uint_as_float(v[j]) * sc, m0 + j, ncol, p.n);
+            }
+            if (p.out_dtype == TL_F32) *reinterpret_cast<float*>(optr) = o;
+            else if (p.out_dtype == TL_F16) *reinterpret_cast<__half*>(optr) = __float2half_rn(o);
+            else *reinterpret_cast<__nv_bfloat16*>(optr) = __float2bfloat16_rn(o);
           }
+          optr += row_bytes;
         }
       }
       tc_fence_before();
@@ -384,8 +426,8 @@ constexpr int kTc = 0, kSliced = 1;
 
 struct TcConfig { int bn, kstep, stages, ncw; };
 // the instantiated tile configurations (tl_variant p0..p3)
-const TcConfig kTcConfigs[] = {{192, 64, 4, 4}, {192, 64, 4, 8}, {128, 64, 6, 4}, {128, 64, 6, 8},
-                               {64, 128, 6, 8}, {32, 128, 7, 8}, {16, 128, 7, 8}};
+const TcConfig kTcConfigs[] = {{192, 64, 6, 4}, {192, 64, 6, 8}, {128, 64, 8, 4}, {128, 64, 8, 8},
+                               {64, 128, 6, 8}, {32, 128, 8, 8}, {16, 128, 8, 8}};
 
 bool tc_config_known(const tl_variant& v) {
   for (const auto& c : kTcConfigs)
@@ -397,7 +439,7 @@ template <typename AT, int BN, int KSTEP, int STAGES, int NCW>
 cudaError_t launch_tc(bool grouped, int grid, cudaStream_t s, const CUtensorMap& wmap, const CUtensorMap& amap,
                       const GemmArgs& p, const EpiParams& e) {
   constexpr size_t smem = size_t(STAGES) * (kTileRows * KSTEP + (KSTEP / 64) * BN * 128) + 1024;
-  constexpr int block = (NCW + 6) * 32;
+  constexpr int block = (NCW + 10) * 32;
   if (grouped) {
     auto kern = qgemm_tc_kernel<AT, BN, KSTEP, STAGES, NCW, true>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -416,13 +458,13 @@ cudaError_t launch_tc_cfg(const tl_variant& v, bool grouped, int grid, cudaStrea
 #define TL_TC_CASE(BN_, KS_, ST_, NCW_)                                             \
   if (v.p0 == BN_ && v.p1 == KS_ && v.p2 == ST_ && v.p3 == NCW_)                   \
     return launch_tc<AT, BN_, KS_, ST_, NCW_>(grouped, grid, s, wmap, amap, p, e);
-  TL_TC_CASE(192, 64, 4, 4)
-  TL_TC_CASE(192, 64, 4, 8)
-  TL_TC_CASE(128, 64, 6, 4)
-  TL_TC_CASE(128, 64, 6, 8)
+  TL_TC_CASE(192, 64, 6, 4)
+  TL_TC_CASE(192, 64, 6, 8)
+  TL_TC_CASE(128, 64, 8, 4)
+  TL_TC_CASE(128, 64, 8, 8)
   TL_TC_CASE(64, 128, 6, 8)
-  TL_TC_CASE(32, 128, 7, 8)
-  TL_TC_CASE(16, 128, 7, 8)
+  TL_TC_CASE(32, 128, 8, 8)
+  TL_TC_CASE(16, 128, 8, 8)
 #undef TL_TC_CASE
   return cudaErrorInvalidValue;
 }
@@ -445,14 +487,14 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
   v.family = TL_FAMILY_QGEMM;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kTc;
-    if (m <= 16) { v.p0 = 16; v.p1 = 128; v.p2 = 7; v.p3 = 8; }
-    else if (m <= 32) { v.p0 = 32; v.p1 = 128; v.p2 = 7; v.p3 = 8; }
+    if (m <= 16) { v.p0 = 16; v.p1 = 128; v.p2 = 8; v.p3 = 8; }
+    else if (m <= 32) { v.p0 = 32; v.p1 = 128; v.p2 = 8; v.p3 = 8; }
     else if (m <= 64) { v.p0 = 64; v.p1 = 128; v.p2 = 6; v.p3 = 8; }
     else {
       // fewest padded token rows; ties go to the wider tile
       const int64_t pad192 = (m + 191) / 192 * 192, pad128 = (m + 127) / 128 * 128;
-      if (pad192 <= pad128) { v.p0 = 192; v.p1 = 64; v.p2 = 4; v.p3 = 4; }
-      else { v.p0 = 128; v.p1 = 64; v.p2 = 6; v.p3 = 4; }
+      if (pad192 <= pad128) { v.p0 = 192; v.p1 = 64; v.p2 = 6; v.p3 = 8; }
+      else { v.p0 = 128; v.p1 = 64; v.p2 = 8; v.p3 = 8; }
     }
   } else {
     v.kernel = kSliced;  // f32 activations or odd K: sixteen-row slices through the small-batch kernels
@@ -530,7 +572,7 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   if (receipt) {
     receipt->choice = v;
     receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
-    receipt->block = (v.p3 + 6) * 32; receipt->split_k = 1;
+    receipt->block = (v.p3 + 10) * 32; receipt->split_k = 1;
     return TL_OK;
   }
   if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
