@@ -151,6 +151,21 @@ TL_API int32_t tl_qgemv_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const vo
                            int64_t k, const tl_quant_desc* qdesc, float alpha,
                            const tl_epilogue* epilogue);
 
+/* No counterpart in the reference.  Same operation and arguments as tl_qgemv_nt for
+ * hosts that must not allocate device memory at call time (a stream capture is open,
+ * all memory belongs to the host's own pool, or cudaMalloc's device-wide
+ * synchronisation cannot be tolerated): the kernel's partial-sum scratch is a fixed
+ * 4 MiB array inside the library image instead of a buffer grown with cudaMalloc, so
+ * the call makes no allocation.  Limits: f16/bf16 activations, K % 128 == 0,
+ * group_size % 64 == 0, and m*n*4 + ceil(n/256)*64 <= 4 MiB (else TL_ERR_UNSUPPORTED).
+ * All calls on a device share the array: calls ordered on one stream are safe, calls
+ * that overlap on the GPU race.  The first call on a device looks up the array's
+ * address; make it before any stream capture starts. */
+TL_API int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                                          const void* scales, void* out, int32_t out_dtype, int32_t m,
+                                          int64_t n, int64_t k, const tl_quant_desc* qdesc, float alpha,
+                                          const tl_epilogue* epilogue);
+
 /* Prefill GEMM with dequantization fused into the tile loads (tcgen05 / TMEM).
  * Replaces the reference's dispatchDequantizeInt8Grouped + dispatchMatmul pair
  * for m > 1 (src/backend/webgpu/ops/matmul-ops.ts:163-181).  a is f16 or bf16;

@@ -86,6 +86,7 @@ SIGNATURES = {
     "tl_f32_to_f16_bits": (C.c_uint32, [_F]),
     "tl_f16_bits_to_f32": (_F, [C.c_uint32]),
     "tl_qgemv_nt": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
+    "tl_qgemv_nt_static_scratch": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemm_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qmatmul_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_dequant_int8": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),

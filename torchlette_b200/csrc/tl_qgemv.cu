@@ -1466,3 +1466,127 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES] += launches;
   return TL_OK;
 }
+
+// ---------------------------------------------------------------------------
+// tl_qgemv_nt_static_scratch: the small-batch quantized matmul for callers that
+// must not allocate.
+//
+// tl_qgemv_nt may grow the context's partial-sum scratch with cudaMalloc the first
+// time a shape needs it.  That is unacceptable for a host that calls from inside a
+// region where device allocation is off limits: while a stream capture is open on
+// the device (cudaMalloc is not capturable and, in global capture mode, is an
+// error), inside a serving loop that has handed all device memory to its own pool,
+// or in a real-time path where the implicit device-wide synchronisation of
+// cudaMalloc/cudaFree would stall every other stream.  This entry point runs the
+// TMA-fed persistent kernel (variant "tma") with its partial-sum meeting point in a
+// fixed array that is part of the loaded module, so the call itself performs no
+// cudaMalloc, cudaFree or other allocating routine.
+//
+// The price is a fixed ceiling and a shared buffer:
+//   - m*n*4 + ceil(n/256)*64 bytes must fit in TL_STATIC_SCRATCH_BYTES (4 MiB); larger
+//     problems are rejected with TL_ERR_UNSUPPORTED before anything is launched;
+//   - every GPU that loads the library carries the 4 MiB until the process exits;
+//   - all calls on a device use the same array.  The part a call uses is cleared on
+//     the stream before the kernel runs (it keeps whatever the previous call left,
+//     including after an aborted kernel), so calls that are ordered on one stream are
+//     safe, but two calls that overlap on the GPU (different streams or contexts on
+//     the same device) race on it and must be serialised by the caller.
+// The array's device address is looked up with cudaGetSymbolAddress the first time
+// the entry point is called on a device (the name of a __device__ array is only a
+// host-side handle, never a pointer a kernel may be given).  That first call should
+// therefore be made before any stream capture begins.
+// ---------------------------------------------------------------------------
+#define TL_STATIC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char tl_static_scratch[TL_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+void* g_static_scratch_ptr[kStaticMaxDevices] = {nullptr};
+
+template <typename AT>
+void launch_tma_static(bool two, bool grouped, int grid, int block, size_t smem, cudaStream_t s, const CUtensorMap& wmap,
+                       const GemvArgs& p, const EpiParams& epi, const TmaArgs& ta) {
+#define TL_STATIC_LAUNCH(NT_, G_)                                                                    \
+  do {                                                                                              \
+    auto kern = qgemv_tma_kernel<AT, NT_, G_, 6>;                                                   \
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));             \
+    kern<<<grid, block, smem, s>>>(wmap, p, epi, ta);                                               \
+  } while (0)
+  if (two) { if (grouped) TL_STATIC_LAUNCH(2, true); else TL_STATIC_LAUNCH(2, false); }
+  else { if (grouped) TL_STATIC_LAUNCH(1, true); else TL_STATIC_LAUNCH(1, false); }
+#undef TL_STATIC_LAUNCH
+}
+}  // namespace
+
+extern "C" int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                                              const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n,
+                                              int64_t k, const tl_quant_desc* qdesc, float alpha,
+                                              const tl_epilogue* epilogue) {
+  TL_CHECK_CTX(ctx);
+  int32_t rc = tl_check_qargs(ctx, "tl_qgemv_nt_static_scratch", a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc);
+  if (rc != TL_OK) return rc;
+  if (m < 1 || m > 16)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_static_scratch: m=%d outside the GEMV range [1,16]", m);
+  if (n == 0) return TL_OK;
+  if ((a_dtype != TL_F16 && a_dtype != TL_BF16) || k % 128 != 0 || qdesc->group_size % 64 != 0)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                        "tl_qgemv_nt_static_scratch: needs f16/bf16 activations, K %% 128 == 0 and groupSize %% 64 == 0 "
+                        "(got %s, K=%lld, G=%d)", tl_dtype_name(a_dtype), (long long)k, qdesc->group_size);
+  if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_static_scratch: weight and activation pointers must be 16-byte aligned");
+  const int64_t bands = (n + kTmaBoxRows - 1) / kTmaBoxRows;
+  const size_t sbytes = size_t(m) * size_t(n) * sizeof(float);
+  const size_t need = sbytes + size_t(bands) * kTmaConsumerWarps * sizeof(unsigned);
+  if (need > TL_STATIC_SCRATCH_BYTES)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                        "tl_qgemv_nt_static_scratch: m=%d n=%lld needs %zu bytes of scratch, the built-in array holds %u; "
+                        "use tl_qgemv_nt", m, (long long)n, need, unsigned(TL_STATIC_SCRATCH_BYTES));
+  EpiParams epi;
+  bool has_ops = false;
+  rc = tl_make_epi(ctx, epilogue, alpha, &epi, &has_ops);
+  if (rc != TL_OK) return rc;
+  if (ctx->device < 0 || ctx->device >= kStaticMaxDevices)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_static_scratch: device ordinal %d not supported", ctx->device);
+  DeviceGuard guard(ctx->device);
+  if (!g_static_scratch_ptr[ctx->device]) {
+    // once per device, with that device current: the symbol's address on THIS device
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, tl_static_scratch);
+    if (e != cudaSuccess || !ptr) {
+      cudaGetLastError();
+      return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_nt_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    g_static_scratch_ptr[ctx->device] = ptr;
+  }
+  uint8_t* base = reinterpret_cast<uint8_t*>(g_static_scratch_ptr[ctx->device]);
+  // the array keeps the previous call's contents: zero the part this call accumulates into
+  TL_CUDA(ctx, cudaMemsetAsync(base, 0, need, ctx->stream));
+
+  GemvArgs p{};
+  p.a = a; p.packed = reinterpret_cast<const uint32_t*>(packed); p.scales = scales; p.out = out;
+  p.m = m; p.n = int32_t(n); p.k = int32_t(k);
+  p.group = qdesc->group_size; p.groups_per_row = int32_t(k / qdesc->group_size);
+  p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
+  p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+  p.row0 = 0; p.m_total = m;
+  TmaArgs ta{};
+  ta.scratch = reinterpret_cast<float*>(base);
+  ta.counters = reinterpret_cast<unsigned*>(base + sbytes);
+  ta.status = ctx->dev_status;
+  ta.spb = int32_t(k / kTmaBoxBytes);
+  ta.total_stages = int32_t(bands * ta.spb);
+  const int grid = int(std::min<int64_t>(ctx->sm_count, ta.total_stages));
+  const int block = (kTmaConsumerWarps + 1) * 32;
+  const size_t smem = size_t(6) * kTmaStageBytes + 1024;
+  CUtensorMap wmap;
+  if (!tl_encode_tmap_2d(&wmap, 1, packed, uint64_t(k), uint64_t(n), uint64_t(k), kTmaBoxBytes, kTmaBoxRows, 3))
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_nt_static_scratch: cuTensorMapEncodeTiled failed");
+  const bool grouped = qdesc->group_size != k;
+  if (a_dtype == TL_F16) launch_tma_static<__half>(m > 8, grouped, grid, block, smem, ctx->stream, wmap, p, epi, ta);
+  else launch_tma_static<__nv_bfloat16>(m > 8, grouped, grid, block, smem, ctx->stream, wmap, p, epi, ta);
+  TL_CUDA(ctx, cudaGetLastError());
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  ctx->counters[TL_COUNTER_QGEMV]++;
+  if (has_ops) ctx->counters[TL_COUNTER_QGEMV_EPILOGUE]++;
+  return TL_OK;
+}
