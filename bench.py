@@ -380,7 +380,7 @@ def run_gpu(args):
     achieved = alg / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None, "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
-                "kernel": "qgemv_mma_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
+                "kernel": "qgemv_ring_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
                 "avg_launch_us": ms_per_step * 1e3 / gemv_launches,
                 "note": "per rank; all 253 small-batch GEMV launches of one step, events on the launching stream"
                         + ("" if world == 1 else "; at N>1 the step time also holds the NCCL collectives")}

@@ -636,6 +636,8 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
   const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
   const uint32_t slot_bytes = uint32_t(nthreads) * 16u;  // one [blockDim] row of 16-byte words
 
+  // let the next kernel in the stream start its own weight prefetch as early as possible
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
   for (int s = 0; s < S; ++s) {
     if (s < nkb) {
@@ -644,6 +646,8 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
     }
     cp_async_commit();
   }
+  // weights never depend on the previous kernel; activations (its output) and our own stores do
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
   float total[NT][4];
 #pragma unroll
@@ -1160,10 +1164,23 @@ __global__ void __launch_bounds__(17 * 32, 1) qgemv_bulk_kernel(GemvArgs p, EpiP
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
+// Launched with programmatic stream serialisation: the kernel may start while its predecessor
+// in the stream is still draining, prefetches its weights (which depend on nothing), and only
+// then waits (griddepcontrol.wait) for the predecessor before it touches activations or writes.
 template <typename K>
 void launch_with_smem(K kernel, int grid, int block, size_t smem, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
   if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-  kernel<<<grid, block, smem, s>>>(p, e);
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p, e);
 }
 template <typename AT, int NT, bool GROUPED>
 void launch_ring_s(int depth, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
