@@ -299,9 +299,19 @@ def run_gpu(args):
         dist.broadcast_object_list(ident, src=0)
         idbuf = (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])
         B.check(ctx, lib.tl_comm_init(ctx, rank, world, idbuf))
+        if args.allreduce == "p2p":
+            # exchange buffers for the one-shot peer all-reduce: [batch, hidden] partial sums
+            hbuf = (C.c_char * 64)()
+            B.check(ctx, lib.tl_p2p_create(ctx, args.batch * 4096 * 4, hbuf))
+            handles = [None] * world
+            dist.all_gather_object(handles, bytes(hbuf))
+            allh = (C.c_char * (64 * world)).from_buffer_copy(b"".join(handles))
+            B.check(ctx, lib.tl_p2p_attach(ctx, allh))
+            dist.barrier()
 
     cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
-    stack = DecodeStack(be, cfg, rank, world, args.tp_mode)
+    stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if world > 1 else "nccl",
+                        fuse=not args.no_fuse)
     if args.autotune:
         shapes = sorted({(cfg.batch, p.n, p.k) for p in stack.layers[0]} | {(cfg.batch, stack.lm_head.n, stack.lm_head.k)})
         for (m, n, k) in shapes:
@@ -382,7 +392,7 @@ def run_gpu(args):
                 "traffic": None, "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
                 "kernel": "qgemv_ring_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
                 "avg_launch_us": ms_per_step * 1e3 / gemv_launches,
-                "note": "per rank; all 253 small-batch GEMV launches of one step, events on the launching stream"
+                "note": f"per rank; all {gemv_launches} small-batch GEMV launches of one step (253 projections), events on the launching stream"
                         + ("" if world == 1 else "; at N>1 the step time also holds the NCCL collectives")}
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
@@ -412,7 +422,9 @@ def run_gpu(args):
             "config": {"workload": "qwen3-8b-decode-matmul-stack", "batch": cfg.batch, "layers": cfg.layers,
                        "hidden": cfg.hidden, "intermediate": cfg.inter, "vocab": cfg.vocab,
                        "weights": "int8 per-channel, f32 scales, random init", "parallelism": f"tp{world}",
-                       "tp_mode": args.tp_mode if world > 1 else "none", "replay": "cuda graph",
+                       "tp_mode": args.tp_mode if world > 1 else "none",
+                       "allreduce": args.allreduce if world > 1 else "none", "replay": "cuda graph",
+                       "fusion": "none" if args.no_fuse else "q+k+v and gate+up share one launch each (same activations)",
                        "l2": "inputs larger than L2: 7.57 GB of weights per step, no flush needed",
                        "autotune": bool(args.autotune)},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -441,6 +453,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tp-mode", default="chained", choices=["chained", "gather"])
     ap.add_argument("--autotune", action="store_true")
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
+                    help="row-parallel sums: the library's one-shot peer-memory kernel, or NCCL")
+    ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no q/k/v and gate/up fusion)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-matrix GEMV / prefill GEMM figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")
     args = ap.parse_args()

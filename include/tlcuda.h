@@ -151,6 +151,24 @@ TL_API int32_t tl_qgemv_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const vo
                            int64_t k, const tl_quant_desc* qdesc, float alpha,
                            const tl_epilogue* epilogue);
 
+/* Horizontal fusion (no counterpart in the reference, which dispatches one GEMV per linear):
+ * up to 4 projections that read the SAME activations a[m,k] -- q/k/v, gate/up -- in ONE
+ * launch.  Each item has its own weight, scales, output [m, n_i], alpha and epilogue; m, k,
+ * dtypes and the packing descriptor are shared.  Results are identical to n_items
+ * tl_qgemv_nt calls (shapes the fused kernel does not take are run that way); the
+ * quant-GEMV counter moves by n_items. */
+typedef struct tl_qgemv_item {
+  const void* packed;
+  const void* scales;
+  void* out;
+  int64_t n;
+  float alpha;
+  const tl_epilogue* epilogue; /* may be NULL */
+} tl_qgemv_item;
+TL_API int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dtype, const tl_qgemv_item* items,
+                                   int32_t n_items, int32_t out_dtype, int32_t m, int64_t k,
+                                   const tl_quant_desc* qdesc);
+
 /* No counterpart in the reference.  Same operation and arguments as tl_qgemv_nt for
  * hosts that must not allocate device memory at call time (a stream capture is open,
  * all memory belongs to the host's own pool, or cudaMalloc's device-wide
@@ -281,6 +299,23 @@ TL_API int32_t tl_allgather_cols(tl_ctx* ctx, const void* local, void* out, int6
                                  int64_t n_local, int32_t dtype);
 /* Row-parallel reduction: in-place sum over ranks of buf[count]. */
 TL_API int32_t tl_allreduce_sum(tl_ctx* ctx, void* buf, int64_t count, int32_t dtype);
+
+
+/* One-shot all-reduce over peer memory (NVLink/NVSwitch P2P loads and stores, no NCCL on
+ * the data path) for the small, latency-bound sums of a row-parallel decode step
+ * ([m, hidden] partial outputs: tens of KB).  Every rank stages its partial in a buffer
+ * that its peers have mapped, raises a flag in every peer's memory, waits (bounded) for
+ * the peers' flags and sums all partials in rank order, so every rank computes
+ * bit-identical results.  No counterpart in the reference.
+ *   tl_p2p_create  allocates this rank's exchange buffer (max_bytes per message) and returns
+ *                  a 64-byte inter-process handle to hand to the other ranks;
+ *   tl_p2p_attach  maps the peers' buffers from the world*64 handle bytes (rank order);
+ *   tl_allreduce_sum_p2p  dst[count] = sum over ranks of src[count]; src may be dst.
+ * A wait that runs out sets the context's status word (TL_ERR_TIMEOUT at tl_sync). */
+#define TL_P2P_HANDLE_BYTES 64
+TL_API int32_t tl_p2p_create(tl_ctx* ctx, size_t max_bytes, void* out_handle64);
+TL_API int32_t tl_p2p_attach(tl_ctx* ctx, const void* handles_world_x64);
+TL_API int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype);
 
 #ifdef __cplusplus
 }

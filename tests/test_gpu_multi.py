@@ -1,0 +1,133 @@
+"""Two-GPU tests of the collectives (skipped on a single-GPU box): the one-shot
+peer-memory all-reduce against a locally computed sum, eager and replayed from a
+captured graph, and bit-identical across ranks; NCCL all-gather / all-reduce wrappers.
+Ranks are child processes (one per GPU); rendezvous over gloo on 127.0.0.1."""
+import ctypes as C
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _data(rank, call, count, dtype):
+    rng = np.random.default_rng(1000 * call + rank)
+    x = rng.standard_normal(count).astype(np.float32)
+    if dtype == "f16":
+        return x.astype(np.float16)
+    return x
+
+
+def _rank_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from torchlette_b200 import backend as tb
+    from torchlette_b200 import binding as B
+
+    try:
+        torch.cuda.set_device(rank)
+        B.preload_nccl()
+        be = tb.CudaBackend(rank)
+        lib, ctx = be._lib, be._ctx
+        ident = [None]
+        if rank == 0:
+            buf = (C.c_char * B.TL_COMM_ID_BYTES)()
+            B.check(None, lib.tl_comm_unique_id(buf))
+            ident[0] = bytes(buf)
+        dist.broadcast_object_list(ident, src=0)
+        B.check(ctx, lib.tl_comm_init(ctx, rank, world, (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])))
+        hbuf = (C.c_char * 64)()
+        B.check(ctx, lib.tl_p2p_create(ctx, 1 << 17, hbuf))
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(hbuf))
+        B.check(ctx, lib.tl_p2p_attach(ctx, (C.c_char * (64 * world)).from_buffer_copy(b"".join(handles))))
+        dist.barrier()
+        results = {}
+        call = 0
+        for dtype, count in [("f16", 8 * 4096), ("f32", 1001), ("f16", 4096), ("f32", 8 * 4096)]:
+            npdt = np.float16 if dtype == "f16" else np.float32
+            t = be.ops.empty([count], dtype)
+            for _ in range(4):  # back-to-back calls alternate the staging halves
+                mine = _data(rank, call, count, dtype)
+                be._upload(t.buffer, mine)
+                B.check(ctx, lib.tl_allreduce_sum_p2p(ctx, t.buffer, t.buffer, count, B.DTYPE_ID[dtype]))
+                got = be.ops.read(t)
+                expect = sum(_data(r, call, count, dtype).astype(np.float32) for r in range(world))
+                tol = 2e-3 if dtype == "f16" else 1e-6
+                assert np.allclose(got.astype(np.float32), expect, rtol=tol, atol=tol), (dtype, count, call)
+                results[call] = got.astype(npdt).tobytes()
+                call += 1
+            # NCCL wrapper on the same data
+            be._upload(t.buffer, _data(rank, call, count, dtype))
+            B.check(ctx, lib.tl_allreduce_sum(ctx, t.buffer, count, B.DTYPE_ID[dtype]))
+            expect = sum(_data(r, call, count, dtype).astype(np.float32) for r in range(world))
+            assert np.allclose(be.ops.read(t).astype(np.float32), expect, rtol=2e-3, atol=2e-3)
+            call += 1
+            t.destroy()
+        # replay: two all-reduces captured once, replayed three times with fresh inputs
+        count = 4096
+        a, b = be.ops.empty([count], "f32"), be.ops.empty([count], "f32")
+        B.check(ctx, lib.tl_allreduce_sum_p2p(ctx, a.buffer, a.buffer, count, B.TL_F32))  # an odd call first
+        be.beginCapture()
+        B.check(ctx, lib.tl_allreduce_sum_p2p(ctx, a.buffer, a.buffer, count, B.TL_F32))
+        B.check(ctx, lib.tl_allreduce_sum_p2p(ctx, b.buffer, b.buffer, count, B.TL_F32))
+        g = be.endCapture()
+        for rep in range(3):
+            be._upload(a.buffer, _data(rank, 500 + rep, count, "f32"))
+            be._upload(b.buffer, _data(rank, 600 + rep, count, "f32"))
+            be.replay(g)
+            ea = sum(_data(r, 500 + rep, count, "f32") for r in range(world))
+            eb = sum(_data(r, 600 + rep, count, "f32") for r in range(world))
+            assert np.allclose(be.ops.read(a), ea, atol=1e-6) and np.allclose(be.ops.read(b), eb, atol=1e-6)
+        be.destroyGraph(g)
+        # column gather
+        m, nl = 3, 40
+        loc = be.ops.tensorFromArray(np.full((m, nl), rank + 1, np.float32), [m, nl], "f32")
+        full = be.ops.empty([m, nl * world], "f32")
+        B.check(ctx, lib.tl_allgather_cols(ctx, loc.buffer, full.buffer, m, nl, B.TL_F32))
+        got = be.ops.read(full)
+        for r in range(world):
+            assert (got[:, r * nl:(r + 1) * nl] == r + 1).all()
+        be.sync()
+        allres = [None] * world
+        dist.all_gather_object(allres, results)
+        if rank == 0:
+            same = all(allres[0][k] == allres[r][k] for r in range(world) for k in allres[0])
+            q.put(("ok", same, be.getGpuUncapturedErrorCount()))
+        dist.barrier()
+        lib.tl_comm_destroy(ctx)
+        be.destroy()
+    except Exception as e:  # surfaced to the parent instead of a silent hang
+        if rank == 0:
+            q.put(("error", repr(e), -1))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_p2p_allreduce_and_nccl_wrappers_two_gpus():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    status, same, errs = q.get(timeout=300)
+    for p in procs:
+        p.join(timeout=120)
+    assert status == "ok", same
+    assert same is True, "ranks disagree bit-wise on an all-reduce result"
+    assert errs == 0
+    assert all(p.exitcode == 0 for p in procs)

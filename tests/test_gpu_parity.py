@@ -557,3 +557,50 @@ def test_tuned_winner_still_matches_oracle(backend):
         got, ref = _run_direct(be, cs, m, n, k, "f16", "f32")
         assert cases.rel_err(got, ref) <= TOL_F32
     be.clearPerShapeMatmulChoices()
+
+
+# ---------------------------------------------------------------------------
+# horizontal fusion: several projections over the same activations in one launch
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m,k,ns,act_dtype", [(1, 1024, (2048, 1024, 1024), "f16"), (8, 512, (304, 48), "bf16"),
+                                             (16, 256, (64, 64, 64, 64), "f16"), (3, 80, (32, 16), "f16")])
+def test_batched_gemv_matches_separate_calls_and_oracle(backend, m, k, ns, act_dtype):
+    be = backend
+    lib, ctx = be._lib, be._ctx
+    cs0 = cases.per_channel_case(8, k, m, seed=99, act_dtype=act_dtype)
+    x = be.ops.tensorFromArray(cs0["x_bits"], [m, k], act_dtype)
+    q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, k, B.TL_F32, B.TL_SCALE_DIRECT)
+    items = (B.QGemvItem * len(ns))()
+    held, refs, outs = [], [], []
+    for i, n in enumerate(ns):
+        cs = cases.per_channel_case(n, k, m, seed=200 + i, bias=True)
+        w = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, tb.perChannelFormat(k))
+        bias = be.ops.tensorFromArray(cs["bias"], [n], "f32")
+        out = be.ops.empty([m, n], "f32")
+        e = None
+        if i % 2 == 0:  # every other item carries its own epilogue
+            e = B.Epilogue()
+            e.n_ops, e.n_inputs = 2, 1
+            e.ops[0] = B.EpilogueOp(B.TL_EPI_BIAS, 0, 0, 0)
+            e.ops[1] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY["silu"], 0, 0)
+            e.inputs[0] = bias.buffer
+        alpha = 0.5 + 0.25 * i
+        items[i] = B.QGemvItem(w.buffer, w.scales.buffer, out.buffer, n, alpha, C.pointer(e) if e is not None else None)
+        held += [w, bias, e]
+        outs.append(out)
+        wref = orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k)
+        refs.append(orc.linear_reference(cs0["x"], wref, cs["bias"] if e is not None else None, "silu" if e is not None else None, alpha))
+    q0, l0 = be.getQuantGemvDispatchCount(), be.getKernelLaunchCount()
+    B.check(ctx, lib.tl_qgemv_nt_batched(ctx, x.buffer, B.DTYPE_ID[act_dtype], items, len(ns), B.TL_F32, m, k, C.byref(q)))
+    assert be.getQuantGemvDispatchCount() == q0 + len(ns)
+    if k % 64 == 0:
+        assert be.getKernelLaunchCount() == l0 + 1  # one launch for all items
+    for out, ref in zip(outs, refs):
+        assert cases.rel_err(be.ops.read(out), ref) <= TOL_F32
+    with pytest.raises(tb.TlError, match="items"):
+        B.check(ctx, lib.tl_qgemv_nt_batched(ctx, x.buffer, B.DTYPE_ID[act_dtype], items, 5, B.TL_F32, m, k, C.byref(q)))
+    for t in outs + [h for h in held if isinstance(h, tb.CudaTensor)] + [x]:
+        if t.scales is not None:
+            t.scales.destroy()
+        t.destroy()

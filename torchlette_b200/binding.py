@@ -46,6 +46,11 @@ class Epilogue(C.Structure):
                 ("inputs", C.c_void_p * TL_EPI_MAX_INPUTS)]
 
 
+class QGemvItem(C.Structure):
+    _fields_ = [("packed", C.c_void_p), ("scales", C.c_void_p), ("out", C.c_void_p), ("n", C.c_int64),
+                ("alpha", C.c_float), ("epilogue", C.POINTER(Epilogue))]
+
+
 class Variant(C.Structure):
     _fields_ = [("family", C.c_int32), ("kernel", C.c_int32), ("p0", C.c_int32), ("p1", C.c_int32),
                 ("p2", C.c_int32), ("p3", C.c_int32)]
@@ -87,6 +92,7 @@ SIGNATURES = {
     "tl_f16_bits_to_f32": (_F, [C.c_uint32]),
     "tl_qgemv_nt": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemv_nt_static_scratch": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
+    "tl_qgemv_nt_batched": (_I32, [_P, _P, _I32, C.POINTER(QGemvItem), _I32, _I32, _I32, _I64, C.POINTER(QuantDesc)]),
     "tl_qgemm_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qmatmul_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_dequant_int8": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),
@@ -119,6 +125,9 @@ SIGNATURES = {
     "tl_comm_destroy": (_I32, [_P]),
     "tl_allgather_cols": (_I32, [_P, _P, _P, _I64, _I64, _I32]),
     "tl_allreduce_sum": (_I32, [_P, _P, _I64, _I32]),
+    "tl_p2p_create": (_I32, [_P, _SZ, _P]),
+    "tl_p2p_attach": (_I32, [_P, _P]),
+    "tl_allreduce_sum_p2p": (_I32, [_P, _P, _P, _I64, _I32]),
 }
 
 

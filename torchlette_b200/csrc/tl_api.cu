@@ -119,6 +119,9 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->zscratch) cudaFree(ctx->zscratch);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  for (int r = 0; r < tl_ctx::kMaxPeers; ++r)
+    if (ctx->p2p_peer[r] && ctx->p2p_peer[r] != ctx->p2p_local) cudaIpcCloseMemHandle(ctx->p2p_peer[r]);
+  if (ctx->p2p_local) cudaFree(ctx->p2p_local);
   cudaStreamDestroy(ctx->stream);
   delete ctx;
   return TL_OK;

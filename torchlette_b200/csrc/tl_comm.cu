@@ -156,3 +156,246 @@ int32_t tl_allreduce_sum(tl_ctx* ctx, void* buf, int64_t count, int32_t dtype) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// One-shot all-reduce over peer-mapped memory (push model).
+//
+// Exchange buffer of a rank (cudaMalloc, exported with cudaIpcGetMemHandle):
+//   slots  [2 halves][kMaxPeers ranks][max_bytes]   slot (h, r) is WRITTEN BY RANK r
+//   flags  u32 [2][kMaxPeers][kP2PCtas]              likewise
+//   epochs u32 [kP2PCtas]                            owner-only per-CTA call counter; it lives on
+//                                                    the device so that a replayed graph keeps counting
+// CTA c of every rank owns slice c of the message.  It pushes its slice into slot (e&1, rank)
+// of EVERY rank with plain stores (posted writes over NVLink: one-way latency, no read round
+// trip), then one release-store per peer publishes epoch e in flags[e&1][rank][c].  It waits
+// (bounded) until all ranks' flags for (e&1, c) reach e and sums the world slots -- all local
+// memory now -- in rank order, so every rank computes the same bits.  Calls alternate halves:
+// a rank can be at most one call ahead of a peer, and then it writes the other half.
+// CTAs never wait on CTAs of the same GPU.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kP2PCtas = 8;
+constexpr int kP2PThreads = 512;
+constexpr int kP2PSpinLimit = 1 << 26;  // polls; seconds, not forever
+
+struct P2PArgs {
+  void* base[tl_ctx::kMaxPeers];  // every rank's exchange buffer as mapped HERE (own = local)
+  int rank, world;
+  size_t max_bytes;
+  int64_t count;
+  const void* src;
+  void* dst;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+template <typename T> __device__ __forceinline__ void add8(float (&acc)[8], const uint4& v);
+template <> __device__ __forceinline__ void add8<float>(float (&)[8], const uint4&) {}  // f32 takes the float4 path
+template <> __device__ __forceinline__ void add8<__half>(float (&acc)[8], const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    acc[2 * i] += f.x; acc[2 * i + 1] += f.y;
+  }
+}
+template <> __device__ __forceinline__ void add8<__nv_bfloat16>(float (&acc)[8], const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i] += __uint_as_float(w[i] << 16); acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+__device__ __forceinline__ uint8_t* p2p_slot(void* base, size_t max_bytes, int half, int r) {
+  return reinterpret_cast<uint8_t*>(base) + (size_t(half) * tl_ctx::kMaxPeers + r) * max_bytes;
+}
+__device__ __forceinline__ uint32_t* p2p_flags(void* base, size_t max_bytes) {
+  return reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(base) + 2 * size_t(tl_ctx::kMaxPeers) * max_bytes);
+}
+
+// T = element type (2 or 4 bytes); 16-byte vectors; f32 accumulation in rank order.
+template <typename T>
+__global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(P2PArgs a) {
+  __shared__ int ok_flag;
+  const int cta = blockIdx.x, tid = threadIdx.x;
+  // the next kernel in the stream (a GEMV that first prefetches weights) may start right away;
+  // this kernel itself must see its predecessor's output before it reads src
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  uint32_t* my_flags = p2p_flags(a.base[a.rank], a.max_bytes);
+  uint32_t* epochs = my_flags + 2 * tl_ctx::kMaxPeers * kP2PCtas;
+  const uint32_t epoch = epochs[cta] + 1;  // every thread reads it before thread 0 bumps it below
+  const int half = epoch & 1;
+  const size_t bytes = size_t(a.count) * sizeof(T);
+  const size_t vecs = (bytes + 15) / 16;  // slots are padded: whole 16-byte vectors
+  const size_t per = (vecs + kP2PCtas - 1) / kP2PCtas;
+  const size_t v0 = size_t(cta) * per, v1 = v0 + per < vecs ? v0 + per : vecs;
+  // 1. push this CTA's slice into slot (half, rank) of every rank
+  for (size_t i = v0 + tid; i < v1; i += blockDim.x) {
+    uint4 v;
+    if ((i + 1) * 16 <= bytes) v = reinterpret_cast<const uint4*>(a.src)[i];
+    else {  // ragged tail: zero padded
+      v = make_uint4(0, 0, 0, 0);
+      uint8_t* zb = reinterpret_cast<uint8_t*>(&v);
+      const uint8_t* sb = reinterpret_cast<const uint8_t*>(a.src) + i * 16;
+      for (size_t b = 0; b < bytes - i * 16; ++b) zb[b] = sb[b];
+    }
+    for (int r = 0; r < a.world; ++r) reinterpret_cast<uint4*>(p2p_slot(a.base[r], a.max_bytes, half, a.rank))[i] = v;
+  }
+  __syncthreads();  // all pushes of the CTA happen-before the release stores below
+  // 2. publish: one release store per rank (system scope, cumulative over the barrier)
+  if (tid == 0) { epochs[cta] = epoch; ok_flag = 1; }
+  if (tid < a.world)
+    st_release_sys(p2p_flags(a.base[tid], a.max_bytes) + (half * tl_ctx::kMaxPeers + a.rank) * kP2PCtas + cta, epoch);
+  __syncthreads();
+  // 3. wait (bounded) for every rank's slice to have landed here
+  if (tid < a.world) {
+    const uint32_t* f = my_flags + (half * tl_ctx::kMaxPeers + tid) * kP2PCtas + cta;
+    int spins = 0;
+    while (int32_t(ld_acquire_sys(f) - epoch) < 0) {
+      if (++spins > kP2PSpinLimit) { ok_flag = 0; atomicExch(a.status, TL_ERR_TIMEOUT); break; }
+    }
+  }
+  __syncthreads();
+  if (!ok_flag) return;
+  // 4. sum the world slots (local memory) in rank order: identical bits on every rank
+  uint4* d4 = reinterpret_cast<uint4*>(a.dst);
+  for (size_t i = v0 + tid; i < v1; i += blockDim.x) {
+    uint4 out;
+    if (sizeof(T) == 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int r = 0; r < a.world; ++r) {
+        const uint4 u = __ldcv(reinterpret_cast<const uint4*>(p2p_slot(a.base[a.rank], a.max_bytes, half, r)) + i);
+        const float4 v = *reinterpret_cast<const float4*>(&u);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+      out = *reinterpret_cast<uint4*>(&acc);
+    } else {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int r = 0; r < a.world; ++r)
+        add8<T>(acc, __ldcv(reinterpret_cast<const uint4*>(p2p_slot(a.base[a.rank], a.max_bytes, half, r)) + i));
+      uint32_t w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (DT<T>::id == TL_F16) {
+          const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        } else {
+          const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+          w[j] = *reinterpret_cast<const uint32_t*>(&h);
+        }
+      }
+      out = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    if ((i + 1) * 16 <= bytes) d4[i] = out;
+    else {  // the last vector extends past count: dst must not be overrun
+      const uint8_t* ob = reinterpret_cast<const uint8_t*>(&out);
+      uint8_t* db = reinterpret_cast<uint8_t*>(a.dst) + i * 16;
+      for (size_t b = 0; b < bytes - i * 16; ++b) db[b] = ob[b];
+    }
+  }
+}
+
+size_t p2p_total_bytes(size_t max_bytes) {
+  return 2 * size_t(tl_ctx::kMaxPeers) * max_bytes + sizeof(uint32_t) * (2 * tl_ctx::kMaxPeers * kP2PCtas + kP2PCtas);
+}
+}  // namespace
+
+extern "C" {
+
+int32_t tl_p2p_create(tl_ctx* ctx, size_t max_bytes, void* out_handle64) {
+  TL_CHECK_CTX(ctx);
+  if (!out_handle64 || max_bytes == 0) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_create: bad argument");
+  if (ctx->p2p_local) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_create: exchange buffer already exists");
+  static_assert(sizeof(cudaIpcMemHandle_t) == TL_P2P_HANDLE_BYTES, "IPC handle size");
+  DeviceGuard guard(ctx->device);
+  max_bytes = (max_bytes + 255) & ~size_t(255);
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, p2p_total_bytes(max_bytes));
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return tl_set_error(ctx, TL_ERR_OOM, "tl_p2p_create: %s", cudaGetErrorString(e));
+  }
+  TL_CUDA(ctx, cudaMemset(p, 0, p2p_total_bytes(max_bytes)));
+  cudaIpcMemHandle_t h;
+  e = cudaIpcGetMemHandle(&h, p);
+  if (e != cudaSuccess) {
+    cudaFree(p);
+    cudaGetLastError();
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_p2p_create: cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  }
+  std::memcpy(out_handle64, &h, sizeof(h));
+  ctx->p2p_local = p;
+  ctx->p2p_max_bytes = max_bytes;
+  return TL_OK;
+}
+
+int32_t tl_p2p_attach(tl_ctx* ctx, const void* handles) {
+  TL_CHECK_CTX(ctx);
+  if (!handles || !ctx->p2p_local) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach: call tl_p2p_create first");
+  if (ctx->world > tl_ctx::kMaxPeers) return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_p2p_attach: at most %d ranks", tl_ctx::kMaxPeers);
+  DeviceGuard guard(ctx->device);
+  for (int r = 0; r < ctx->world; ++r) {
+    if (r == ctx->rank) { ctx->p2p_peer[r] = ctx->p2p_local; continue; }
+    cudaIpcMemHandle_t h;
+    std::memcpy(&h, reinterpret_cast<const uint8_t*>(handles) + size_t(r) * TL_P2P_HANDLE_BYTES, sizeof(h));
+    void* p = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return tl_set_error(ctx, TL_ERR_CUDA, "tl_p2p_attach: cannot map rank %d's buffer: %s", r, cudaGetErrorString(e));
+    }
+    ctx->p2p_peer[r] = p;
+  }
+  ctx->p2p_attached = true;
+  return TL_OK;
+}
+
+int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype) {
+  TL_CHECK_CTX(ctx);
+  if (!src || !dst) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: null pointer");
+  if (count < 0 || !tl_dtype_valid(dtype)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: bad count or dtype");
+  if (count == 0) return TL_OK;
+  const size_t bytes = size_t(count) * tl_dtype_size(dtype);
+  if (ctx->world == 1) {
+    DeviceGuard guard(ctx->device);
+    if (src != dst) TL_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+    return TL_OK;
+  }
+  if (!ctx->p2p_attached) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: peers not attached");
+  if (((bytes + 15) & ~size_t(15)) > ctx->p2p_max_bytes)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_allreduce_sum_p2p: %zu bytes exceed the exchange buffer (%zu)", bytes, ctx->p2p_max_bytes);
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: pointers must be 16-byte aligned");
+  DeviceGuard guard(ctx->device);
+  P2PArgs a{};
+  for (int r = 0; r < ctx->world; ++r) a.base[r] = ctx->p2p_peer[r];
+  a.rank = ctx->rank; a.world = ctx->world; a.max_bytes = ctx->p2p_max_bytes; a.count = count;
+  a.src = src; a.dst = dst; a.status = ctx->dev_status;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(kP2PCtas);
+  cfg.blockDim = dim3(kP2PThreads);
+  cfg.stream = ctx->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (dtype == TL_F32) cudaLaunchKernelEx(&cfg, p2p_allreduce_kernel<float>, a);
+  else if (dtype == TL_F16) cudaLaunchKernelEx(&cfg, p2p_allreduce_kernel<__half>, a);
+  else cudaLaunchKernelEx(&cfg, p2p_allreduce_kernel<__nv_bfloat16>, a);
+  TL_CUDA(ctx, cudaGetLastError());
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  return TL_OK;
+}
+
+}  // extern "C"

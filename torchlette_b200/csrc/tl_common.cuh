@@ -60,6 +60,12 @@ struct tl_ctx {
   // multi-GPU
   void* nccl_comm = nullptr;
   int rank = 0, world = 1;
+  // one-shot peer all-reduce: this rank's exchange buffer and the peers' mappings
+  static constexpr int kMaxPeers = 8;
+  void* p2p_local = nullptr;
+  void* p2p_peer[kMaxPeers] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  size_t p2p_max_bytes = 0;
+  bool p2p_attached = false;
 };
 
 int32_t tl_set_error(tl_ctx* ctx, int32_t code, const char* fmt, ...);

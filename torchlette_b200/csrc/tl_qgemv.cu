@@ -609,15 +609,17 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// MAXT / MINB: launch bounds.  The 4-warp configuration asks for 12 resident CTAs per SM
+// (<= 42 registers) so that, under programmatic dependent launch, the CTAs of the NEXT kernel
+// fit beside the 6-7 CTAs per SM of the running one and prefetch their weights early.
 template <typename AT, int NT, bool GROUPED, int S>
-__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs p, EpiParams epi) {
-  extern __shared__ __align__(16) uint8_t ring_raw[];
+__device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& epi, int64_t tile_index, uint8_t* ring_raw) {
   uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [S][2][blockDim.x]
   const int nthreads = blockDim.x, tid = threadIdx.x;
   float* red = reinterpret_cast<float*>(ring_raw + size_t(S) * 2 * nthreads * 16);  // [warps][NT][4][32]
   const int warps = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int64_t tile_row = int64_t(blockIdx.x) * 16;
+  const int64_t tile_row = tile_index * 16;
   const int64_t r_lo = min(tile_row + g, int64_t(p.n) - 1);
   const int64_t r_hi = min(tile_row + g + 8, int64_t(p.n) - 1);
   const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
@@ -738,6 +740,31 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_kernel(GemvArgs 
       tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+
+template <typename AT, int NT, bool GROUPED, int S, int MAXT = kMmaMaxWarps * 32, int MINB = 1>
+__global__ void __launch_bounds__(MAXT, MINB) qgemv_ring_kernel(GemvArgs p, EpiParams epi) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  ring_tile<AT, NT, GROUPED, S>(p, epi, blockIdx.x, ring_smem);
+}
+
+// Horizontal fusion: up to four projections that read the SAME activations (q/k/v, gate/up) in
+// one launch.  CTA b works on tile b - tile_start[i] of item i; each item keeps its own weight,
+// scales, output, alpha and epilogue.
+constexpr int kMaxBatchItems = 4;
+struct RingBatchArgs {
+  GemvArgs p[kMaxBatchItems];
+  EpiParams e[kMaxBatchItems];
+  int32_t tile_start[kMaxBatchItems + 1];
+};
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_batched_kernel(const __grid_constant__ RingBatchArgs b) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int blk = int(blockIdx.x);
+  const int i = (blk >= b.tile_start[1]) + (blk >= b.tile_start[2]) + (blk >= b.tile_start[3]);
+  ring_tile<AT, NT, GROUPED, S>(b.p[i], b.e[i], blk - b.tile_start[i], ring_smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -1605,5 +1632,98 @@ extern "C" int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   ctx->counters[TL_COUNTER_QGEMV]++;
   if (has_ops) ctx->counters[TL_COUNTER_QGEMV_EPILOGUE]++;
+  return TL_OK;
+}
+
+
+// ---------------------------------------------------------------------------
+// tl_qgemv_nt_batched: several small-batch projections over the same activations in one launch.
+// ---------------------------------------------------------------------------
+namespace {
+template <typename AT, int NT, bool GROUPED, int S>
+void launch_ring_batched(int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
+  const size_t smem = size_t(S) * 2 * block * 16 + size_t(block / 32) * NT * 128 * 4;
+  auto kern = qgemv_ring_batched_kernel<AT, NT, GROUPED, S>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, b);
+}
+template <typename AT, int NT, bool GROUPED>
+void launch_ring_batched_s(int depth, int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
+  if (depth >= 4) launch_ring_batched<AT, NT, GROUPED, 4>(grid, block, s, b);
+  else launch_ring_batched<AT, NT, GROUPED, 2>(grid, block, s, b);
+}
+template <typename AT>
+void launch_ring_batched_at(bool two, bool grouped, int depth, int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
+  if (two) { if (grouped) launch_ring_batched_s<AT, 2, true>(depth, grid, block, s, b); else launch_ring_batched_s<AT, 2, false>(depth, grid, block, s, b); }
+  else { if (grouped) launch_ring_batched_s<AT, 1, true>(depth, grid, block, s, b); else launch_ring_batched_s<AT, 1, false>(depth, grid, block, s, b); }
+}
+}  // namespace
+
+extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dtype, const tl_qgemv_item* items,
+                                       int32_t n_items, int32_t out_dtype, int32_t m, int64_t k,
+                                       const tl_quant_desc* qdesc) {
+  TL_CHECK_CTX(ctx);
+  if (!items || n_items < 1 || n_items > kMaxBatchItems)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_batched: 1..%d items (got %d)", kMaxBatchItems, n_items);
+  if (m < 1 || m > 16) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_batched: m=%d outside the GEMV range [1,16]", m);
+  bool fused_ok = qdesc && (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && qdesc->group_size > 0 &&
+                  qdesc->group_size % 64 == 0 && !(reinterpret_cast<uintptr_t>(a) & 15);
+  for (int i = 0; i < n_items; ++i) {
+    int32_t rc = tl_check_qargs(ctx, "tl_qgemv_nt_batched", a, a_dtype, items[i].packed, items[i].scales, items[i].out,
+                                out_dtype, m, items[i].n, k, qdesc);
+    if (rc != TL_OK) return rc;
+    if (items[i].n == 0 || (reinterpret_cast<uintptr_t>(items[i].packed) & 15)) fused_ok = false;
+  }
+  if (!fused_ok) {
+    // shapes the fused kernel does not take: one ordinary call per item, same results
+    for (int i = 0; i < n_items; ++i) {
+      int32_t rc = tl_qgemv_nt(ctx, a, a_dtype, items[i].packed, items[i].scales, items[i].out, out_dtype, m, items[i].n, k,
+                               qdesc, items[i].alpha, items[i].epilogue);
+      if (rc != TL_OK) return rc;
+    }
+    return TL_OK;
+  }
+  RingBatchArgs b{};
+  int64_t tiles = 0;
+  int n_epi = 0;
+  for (int i = 0; i < kMaxBatchItems; ++i) {
+    b.tile_start[i] = int32_t(tiles);
+    if (i >= n_items) continue;
+    bool has_ops = false;
+    int32_t rc = tl_make_epi(ctx, items[i].epilogue, items[i].alpha, &b.e[i], &has_ops);
+    if (rc != TL_OK) return rc;
+    n_epi += has_ops ? 1 : 0;
+    GemvArgs& p = b.p[i];
+    p.a = a; p.packed = reinterpret_cast<const uint32_t*>(items[i].packed); p.scales = items[i].scales; p.out = items[i].out;
+    p.m = m; p.n = int32_t(items[i].n); p.k = int32_t(k);
+    p.group = qdesc->group_size; p.groups_per_row = int32_t(k / qdesc->group_size);
+    p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
+    p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+    p.row0 = 0; p.m_total = m;
+    tiles += (items[i].n + 15) / 16;
+  }
+  b.tile_start[kMaxBatchItems] = int32_t(tiles);
+  for (int i = n_items; i < kMaxBatchItems; ++i) b.tile_start[i] = int32_t(tiles);  // unused items are empty ranges
+  // same shape rule as the single-matrix default: few tiles -> many warps per tile
+  const int warps = tiles >= int64_t(ctx->sm_count) * 4 ? 4 : 16, depth = warps == 4 ? 4 : 2;
+  const int block = warps * 32, grid = int(tiles);
+  const bool grouped = qdesc->group_size != k;
+  DeviceGuard guard(ctx->device);
+  if (a_dtype == TL_F16) launch_ring_batched_at<__half>(m > 8, grouped, depth, grid, block, ctx->stream, b);
+  else launch_ring_batched_at<__nv_bfloat16>(m > 8, grouped, depth, grid, block, ctx->stream, b);
+  TL_CUDA(ctx, cudaGetLastError());
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  ctx->counters[TL_COUNTER_QGEMV] += n_items;
+  ctx->counters[TL_COUNTER_QGEMV_EPILOGUE] += n_epi;
   return TL_OK;
 }

@@ -77,9 +77,11 @@ class _Proj:
 
 class DecodeStack:
     def __init__(self, be: CudaBackend, cfg: StackConfig, rank: int = 0, world: int = 1, tp_mode: str = "chained",
-                 seed: int = 0):
-        assert tp_mode in ("chained", "gather")
+                 seed: int = 0, allreduce: str = "nccl", fuse: bool = True):
+        assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p")
         self.be, self.cfg, self.rank, self.world, self.tp_mode = be, cfg, rank, world, tp_mode
+        self.fuse = fuse  # q/k/v and gate/up as one launch each
+        self.allreduce = allreduce  # "p2p": the library's one-shot peer-memory all-reduce (peers must be attached)
         self.dev = torch.device("cuda", be.device)
         self.lib, self.ctx = be._lib, be._ctx
         self.tdt = torch.float16 if cfg.act_dtype == "f16" else torch.bfloat16
@@ -136,9 +138,34 @@ class DecodeStack:
             B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha,
             C.byref(e) if e is not None else None))
 
+    def _run_batched(self, projs, x: torch.Tensor, outs):
+        """Projections that read the same activations in one launch (tl_qgemv_nt_batched)."""
+        if self.cfg.batch > 16 or not self.fuse:
+            for p, o in zip(projs, outs):
+                self._run(p, x, o)
+            return
+        items = (B.QGemvItem * len(projs))()
+        keep = []
+        for i, (p, o) in enumerate(zip(projs, outs)):
+            e = None
+            if p.act:
+                e = B.Epilogue()
+                e.n_ops = 1
+                e.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY[p.act], 0, 0)
+                keep.append(e)
+            items[i] = B.QGemvItem(p.w.data_ptr(), p.s.data_ptr(), o.data_ptr(), p.n, p.alpha,
+                                   C.pointer(e) if e is not None else None)
+        q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, projs[0].k, B.TL_F32, B.TL_SCALE_DIRECT)
+        B.check(self.ctx, self.lib.tl_qgemv_nt_batched(self.ctx, x.data_ptr(), self.adt, items, len(projs),
+                                                       B.DTYPE_ID[projs[0].out_dtype], self.cfg.batch, projs[0].k,
+                                                       C.byref(q)))
+
     def _allreduce(self, t: torch.Tensor):
         if self.world > 1:
-            B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, t.data_ptr(), t.numel(), self.adt))
+            if self.allreduce == "p2p":
+                B.check(self.ctx, self.lib.tl_allreduce_sum_p2p(self.ctx, t.data_ptr(), t.data_ptr(), t.numel(), self.adt))
+            else:
+                B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, t.data_ptr(), t.numel(), self.adt))
 
     def _allgather(self, local: torch.Tensor, full: torch.Tensor, dtype_id: int):
         B.check(self.ctx, self.lib.tl_allgather_cols(self.ctx, local.data_ptr(), full.data_ptr(), local.shape[0],
@@ -156,9 +183,7 @@ class DecodeStack:
         gather = self.tp_mode == "gather" and self.world > 1
         for projs in self.layers:
             pq, pk, pv, po, pg, pu, pd = projs
-            self._run(pq, x, self.q)
-            self._run(pk, x, self.kk)
-            self._run(pv, x, self.v)
+            self._run_batched((pq, pk, pv), x, (self.q, self.kk, self.v))
             o_in = self.q
             if gather:
                 self._allgather(self.q, self.q_full, self.adt)
@@ -166,8 +191,7 @@ class DecodeStack:
                 o_in = self.q_slice
             self._run(po, o_in, self.h1)
             self._allreduce(self.h1)
-            self._run(pg, self.h1, self.g)
-            self._run(pu, self.h1, self.u)
+            self._run_batched((pg, pu), self.h1, (self.g, self.u))
             d_in = self.g
             if gather:
                 self._allgather(self.g, self.g_full, self.adt)
@@ -199,7 +223,8 @@ class DecodeStack:
             self.enqueue_step()
 
     def launches_per_step(self) -> int:
-        return 7 * self.cfg.layers + 1
+        fused = self.fuse and self.cfg.batch <= 16
+        return (4 if fused else 7) * self.cfg.layers + 1
 
     def destroy(self):
         if self.graph is not None:
