@@ -1211,8 +1211,9 @@ void launch_with_smem(K kernel, int grid, int block, size_t smem, cudaStream_t s
 }
 template <typename AT, int NT, bool GROUPED>
 void launch_ring_s(int depth, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
-  const size_t smem = size_t(depth >= 8 ? 8 : depth >= 4 ? 4 : 2) * 2 * block * 16 + size_t(block / 32) * NT * 128 * 4;
+  const size_t smem = size_t(depth >= 8 ? 8 : depth >= 6 ? 6 : depth >= 4 ? 4 : 2) * 2 * block * 16 + size_t(block / 32) * NT * 128 * 4;
   if (depth >= 8) launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 8>, grid, block, smem, s, p, e);
+  else if (depth >= 6) launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 6>, grid, block, smem, s, p, e);
   else if (depth >= 4) launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 4>, grid, block, smem, s, p, e);
   else launch_with_smem(qgemv_ring_kernel<AT, NT, GROUPED, 2>, grid, block, smem, s, p, e);
 }
@@ -1298,7 +1299,7 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
              (v.p0 == 4 || v.p0 == 5 || v.p0 == 6);
     case kRing:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
-             (v.p1 == 2 || v.p1 == 4 || v.p1 == 8);
+             (v.p1 == 2 || v.p1 == 4 || v.p1 == 6 || v.p1 == 8);
     case kSk:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 64 == 0 && v.p0 <= 8 &&
              (v.p1 == 2 || v.p1 == 4);
@@ -1315,8 +1316,16 @@ int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, i
     // few tiles: spread each tile's k range over many warps so everything is in flight at once
     const int64_t tiles = (n + 15) / 16;
     v.kernel = kRing;
-    if (tiles >= int64_t(ctx->sm_count) * 4) { v.p0 = 4; v.p1 = 4; }
-    else { v.p0 = 16; v.p1 = 2; }
+    if (tiles >= int64_t(ctx->sm_count) * 4) {
+      // 4-warp CTAs, all co-resident when they fit: the deepest prefetch ring whose shared memory
+      // still lets ceil(tiles / SMs) CTAs (at most 8, the register limit) live on one SM, so the
+      // bytes in flight per SM do not depend on how many tiles the matrix happens to have
+      const int64_t per_sm = std::min<int64_t>(8, (tiles + ctx->sm_count - 1) / ctx->sm_count);
+      int depth = 2;
+      for (int cand : {4, 6, 8})
+        if (per_sm * (int64_t(cand) * 4096 + 2048 + 1024) <= 224 * 1024) depth = cand;
+      v.p0 = 4; v.p1 = depth;
+    } else { v.p0 = 16; v.p1 = 2; }
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -1344,7 +1353,7 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
     for (int kb : {32, 64}) add(kBulk, w, kb);
   for (int st : {4, 6}) add(kTma, st, 0);
   for (int w : {2, 4, 8, 16})
-    for (int u : {2, 4, 8}) add(kRing, w, u);
+    for (int u : {2, 4, 6, 8}) add(kRing, w, u);
   for (int b : {2, 4, 8})
     for (int u : {2, 4}) add(kSk, b, u);
   for (int w : {4, 8, 16})
