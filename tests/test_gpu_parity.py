@@ -604,3 +604,32 @@ def test_batched_gemv_matches_separate_calls_and_oracle(backend, m, k, ns, act_d
         if t.scales is not None:
             t.scales.destroy()
         t.destroy()
+
+
+@pytest.mark.parametrize("variant", [(1, 3, 4, 4, 0, 0), (1, 5, 6, 0, 0, 0), (1, 6, 16, 32, 0, 0), (1, 4, 4, 6, 0, 0), (1, 2, 8, 4, 1, 0)])
+@pytest.mark.parametrize("group", [64, 128])
+def test_grouped_scales_on_every_fast_variant(backend, variant, group):
+    """Reference-native format (f16 group scales) forced through each tensor-core GEMV variant."""
+    be = backend
+    n, k, m = 520, 1024, 5
+    rng = np.random.default_rng(group + variant[1])
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    packed, scales = be.quantizeLinearWeight(w, group)
+    fmt = tb.resolveWeightFormat(f"int8-{group}")
+    wt = be.createQuantizedWeight(packed, scales, n, k, fmt)
+    xt = be.ops.tensorFromArray(x, [m, k], "f16")
+    ref = orc.matmul_nt(x.astype(np.float32), orc.dequantize_to_f32(packed, scales, k, group))
+    be.forceVariant(variant)
+    try:
+        if variant[1] == 3 and group == 64:
+            with pytest.raises(tb.TlError, match="forced variant"):  # its MMAs span 128 k: not applicable
+                be.linear(xt, wt)
+        else:
+            y = be.linear(xt, wt)
+            assert cases.rel_err(be.ops.read(y), ref) <= TOL_F32
+            y.destroy()
+    finally:
+        be.forceVariant(None)
+    for t in (xt, wt.scales, wt):
+        t.destroy()

@@ -23,7 +23,7 @@
 //              f16/bf16 activations, K % 128 == 0, G % 64 == 0.  p0 = stages.
 //   3 "sk"     persistent grid, the weight dealt out to warps in equal contiguous
 //              shares of 8-row x 128-byte units; partial tiles meet in an f32
-//              scratch.  f16/bf16 activations, K % 128 == 0, G % 64 == 0.
+//              scratch.  f16/bf16 activations, K % 128 == 0, G % 128 == 0.
 // Variant parameters: p0 = warps per CTA (sk: CTAs per SM), p1 = rows per warp
 // (simt) / k blocks in flight (mma, sk), p2, p3 = reserved.
 #include <algorithm>
@@ -1301,7 +1301,9 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
              (v.p1 == 2 || v.p1 == 4 || v.p1 == 6 || v.p1 == 8);
     case kSk:
-      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 64 == 0 && v.p0 <= 8 &&
+      // a thread's 32 contiguous weight bytes feed all of a unit's MMAs, so one MMA spans the whole
+      // 128-wide unit: a scale group must cover it
+      return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 128 == 0 && q.group_size % 128 == 0 && v.p0 <= 8 &&
              (v.p1 == 2 || v.p1 == 4);
     default: return false;
   }
