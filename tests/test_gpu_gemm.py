@@ -18,7 +18,7 @@ pytestmark = pytest.mark.gpu
 
 TC_CONFIGS = [(2, 0, 192, 64, 6, 4), (2, 0, 192, 64, 6, 8), (2, 0, 128, 64, 8, 4), (2, 0, 128, 64, 8, 8),
               (2, 0, 64, 128, 6, 8), (2, 0, 32, 128, 8, 8), (2, 0, 16, 128, 8, 8), (2, 0, 128, 128, 4, 8),
-              (2, 0, 192, 128, 3, 8)]
+              (2, 0, 192, 128, 3, 8), (2, 0, 128, 128, 4, 16), (2, 0, 192, 128, 3, 16)]
 
 
 def _gemm_case(be, m, n, k, act_dtype, out_dtype, variant=None, bias=False, act=None, seed=0, rows=None):

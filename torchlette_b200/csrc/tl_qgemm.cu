@@ -26,9 +26,17 @@
 // Every wait is bounded; a wait that runs out raises a status word, all roles
 // drain, TMEM is released and the kernel returns.
 #include <algorithm>
+#include <type_traits>
 
 #include "tl_common.cuh"
 #include "tl_tma.cuh"
+
+#ifdef TL_TRACE
+__device__ long long g_tl_trace[4][64][6];
+#define TL_TR(role, it, ev) do { if (blockIdx.x == 0 && (it) < 64) g_tl_trace[role][it][ev] = clock64(); } while (0)
+#else
+#define TL_TR(role, it, ev) do {} while (0)
+#endif
 
 namespace {
 
@@ -171,7 +179,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
                 EpiParams epi) {
   static_assert(KSTEP == 64 || KSTEP == 128, "one weight box row is 64 or 128 bytes");
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
-  static_assert(NCW == 4 || NCW == 8, "converter warps");
+  static_assert(NCW == 4 || NCW == 8 || NCW == 16, "converter warps");
   constexpr int kWBytes = kTileRows * KSTEP;        // int8 weight box
   constexpr int kABox = BN * 128;                   // one [BN x 64] activation box
   constexpr int kABoxes = KSTEP / 64;
@@ -187,7 +195,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
   constexpr int kParts = NCW / 4;                   // converter threads per weight row
   constexpr int kChunks = KSTEP / 16 / kParts;      // 16-byte chunks per converter thread and stage
   constexpr int kEpiWarp0 = NCW, kEpiWarps = 8, kProducerWarp = NCW + 8, kMmaWarp = NCW + 9;
-  constexpr uint32_t kIdesc = (1u << 4) | (Cvt<AT>::kFmt << 7) | (Cvt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
+  // Both operands carry the activation type: kind::f16 with an f16 weight operand against
+  // bf16 activations raised "illegal instruction" on B200, so the cheaper f16 bit trick cannot
+  // be used for bf16 problems.
+  using WT = AT;
+  constexpr uint32_t kIdesc = (1u << 4) | (Cvt<WT>::kFmt << 7) | (Cvt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
                               (uint32_t(kTileRows >> 4) << 24);
 
   extern __shared__ uint8_t gemm_smem_raw[];
@@ -237,12 +249,14 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
             if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_EMPTY); }
             break;
           }
+          TL_TR(0, it, 0);
           uint8_t* st = stages + size_t(s) * kStageBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
           tma_load_2d(st, &wmap, ks * KSTEP, n_tile * kTileRows, &full_bar[s]);
 #pragma unroll
           for (int b = 0; b < kABoxes; ++b)
             tma_load_2d(st + kWBytes + b * kABox, &amap, ks * KSTEP + b * 64, m_tile * BN, &full_bar[s]);
+          TL_TR(0, it, 1);
         }
       }
     }
@@ -261,8 +275,11 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
         bool ok = true;
         for (int ks = 0; ks < p.ksteps && ok; ++ks, ++it) {
           const int s = it % STAGES, sl = it % TS;
-          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag) &&
-               mbar_wait(&aready_bar[sl], (it / TS) & 1, &abort_flag);
+          TL_TR(1, it, 0);
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag);
+          TL_TR(1, it, 1);
+          ok = ok && mbar_wait(&aready_bar[sl], (it / TS) & 1, &abort_flag);
+          TL_TR(1, it, 2);
           if (!ok) {
             if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
             break;
@@ -277,6 +294,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
           }
           tc_commit(&empty_bar[s]);      // the shared-memory stage is free once these MMAs have run
           tc_commit(&slotfree_bar[sl]);  // and so is the TMEM operand slot
+          TL_TR(1, it, 3);
         }
         if (!ok) break;
         tc_commit(&tfull_bar[acc]);
@@ -298,7 +316,9 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     auto convert = [&](int it) -> bool {
       const int s = it % STAGES;
       const int tl = it / p.ksteps, ks = it - tl * p.ksteps;
+      if (warp == 0 && lane == 0) TL_TR(2, it, 0);
       if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag)) return false;
+      if (warp == 0 && lane == 0) TL_TR(2, it, 1);
       const uint32_t wb = smem_u32(stages + size_t(s) * kStageBytes) + row_off;
       uint4 raw[kChunks];
 #pragma unroll
@@ -328,10 +348,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
             v[i][2 * j + 1] = Cvt<AT>::pack(f2, f3);
           }
         } else {
-          Cvt<AT>::word(raw[i].x, v[i][0], v[i][1]);
-          Cvt<AT>::word(raw[i].y, v[i][2], v[i][3]);
-          Cvt<AT>::word(raw[i].z, v[i][4], v[i][5]);
-          Cvt<AT>::word(raw[i].w, v[i][6], v[i][7]);
+          Cvt<WT>::word(raw[i].x, v[i][0], v[i][1]);
+          Cvt<WT>::word(raw[i].y, v[i][2], v[i][3]);
+          Cvt<WT>::word(raw[i].z, v[i][4], v[i][5]);
+          Cvt<WT>::word(raw[i].w, v[i][6], v[i][7]);
         }
       }
       return true;
@@ -339,13 +359,17 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     bool ok = total_it > 0 && convert(0);
     for (int it = 0; it < total_it && ok; ++it) {
       const int sl = it % TS;
+      if (warp == 0 && lane == 0) TL_TR(2, it, 2);
       if (it >= TS && !mbar_wait(&slotfree_bar[sl], ((it / TS) - 1) & 1, &abort_flag)) { ok = false; break; }
+      if (warp == 0 && lane == 0) TL_TR(2, it, 3);
       tc_fence_after();
       const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + sl * kSlotCols);
 #pragma unroll
       for (int i = 0; i < kChunks; ++i) tmem_st8(slot + (part * kChunks + i) * 8, v[i]);
       if (it + 1 < total_it) ok = convert(it + 1);  // overlaps the stores above
+      if (warp == 0 && lane == 0) TL_TR(2, it, 4);
       tmem_st_wait();      // this thread's TMEM stores are complete
+      if (warp == 0 && lane == 0) TL_TR(2, it, 5);
       tc_fence_before();
       __syncwarp();        // ... and so are those of the other 31 lanes
       if (lane == 0) mbar_arrive(&aready_bar[sl]);  // one arrival per warp keeps the barrier cheap
@@ -430,7 +454,7 @@ struct TcConfig { int bn, kstep, stages, ncw; };
 // the instantiated tile configurations (tl_variant p0..p3)
 const TcConfig kTcConfigs[] = {{192, 64, 6, 4}, {192, 64, 6, 8}, {128, 64, 8, 4}, {128, 64, 8, 8},
                                {64, 128, 6, 8}, {32, 128, 8, 8}, {16, 128, 8, 8},
-                               {128, 128, 4, 8}, {192, 128, 3, 8}};
+                               {128, 128, 4, 8}, {192, 128, 3, 8}, {128, 128, 4, 16}, {192, 128, 3, 16}};
 
 bool tc_config_known(const tl_variant& v) {
   for (const auto& c : kTcConfigs)
@@ -470,6 +494,8 @@ cudaError_t launch_tc_cfg(const tl_variant& v, bool grouped, int grid, cudaStrea
   TL_TC_CASE(16, 128, 8, 8)
   TL_TC_CASE(128, 128, 4, 8)
   TL_TC_CASE(192, 128, 3, 8)
+  TL_TC_CASE(128, 128, 4, 16)
+  TL_TC_CASE(192, 128, 3, 16)
 #undef TL_TC_CASE
   return cudaErrorInvalidValue;
 }
@@ -599,3 +625,9 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   return TL_OK;
 }
+
+#ifdef TL_TRACE
+extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_trace(void* dst, size_t bytes) {
+  return cudaMemcpyFromSymbol(dst, g_tl_trace, bytes) == cudaSuccess ? 0 : -1;
+}
+#endif
