@@ -68,6 +68,31 @@ def test_qgemm_many_tiles_per_cta_exercises_both_accumulators(backend):
     assert cases.rel_err(got, ref) <= 1e-3
 
 
+def test_qgemm_partial_wave_is_cut_along_k_and_is_repeatable(backend):
+    """Tiles beyond the last whole wave are split along K; partials are summed in part order,
+    so two runs agree bit for bit, and the election counters are left clear for the next launch."""
+    sms = backend.smCount()
+    fmt = tb.perChannelFormat(1024).packing
+    # a whole number of waves: nothing to cut
+    plan = backend.planQuantizedMatmul(512, sms * 32, 1024, "bf16", "bf16", fmt)
+    assert plan["family"] == "gemm" and plan["splitK"] == 1
+    # 8 tiles on a machine of `sms` CTAs: cut four ways
+    plan = backend.planQuantizedMatmul(256, 512, 1024, "bf16", "bf16", fmt)
+    assert plan["splitK"] == 4 and plan["grid"][0] == 32
+    runs = []
+    for _ in range(3):
+        got, ref = _gemm_case(backend, 256, 512, 1024, "bf16", "f32", None, bias=True, act="gelu", seed=21)
+        assert cases.rel_err(got, ref) <= 1e-3
+        runs.append(got.copy())
+    assert np.array_equal(runs[0], runs[1]) and np.array_equal(runs[0], runs[2])
+    # whole waves followed by a cut remainder (2 * sms + 4 tiles of 128 x 128)
+    n = 128 * (sms + 2)
+    got, ref = _gemm_case(backend, 256, n, 256, "f16", "f32", (2, 0, 128, 128, 4, 8), seed=22,
+                          rows=[0, 127, 128, 255])
+    assert cases.rel_err(got, ref) <= 1e-3
+    assert backend.getGpuUncapturedErrorCount() == 0
+
+
 @pytest.mark.parametrize("group", [64, 128])
 @pytest.mark.parametrize("act_dtype", ["f16", "bf16"])
 def test_qgemm_grouped_reference_native_format(backend, group, act_dtype):

@@ -155,6 +155,27 @@ template <> struct Cvt<__nv_bfloat16> {
   }
 };
 
+// One unary op over sixteen accumulators.  The op and the precision are resolved once, so
+// each case is a straight run of sixteen independent chains.
+template <int OP, bool APPROX>
+__device__ __forceinline__ void unary16_case(float (&o)[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) o[j] = APPROX ? tl_unary_approx(OP, o[j]) : tl_unary(OP, o[j]);
+}
+__device__ __forceinline__ void unary16(int op, bool approx, float (&o)[16]) {
+#define TL_U16(OP) case OP: if (approx) unary16_case<OP, true>(o); else unary16_case<OP, false>(o); break;
+  switch (op) {
+    TL_U16(TL_UNARY_RELU)
+    TL_U16(TL_UNARY_SILU)
+    TL_U16(TL_UNARY_SIGMOID)
+    TL_U16(TL_UNARY_TANH)
+    TL_U16(TL_UNARY_GELU_TANH)
+    TL_U16(TL_UNARY_GELU_ERF)
+    default: break;
+  }
+#undef TL_U16
+}
+
 struct GemmArgs {
   const void* scales;
   void* out;
@@ -163,7 +184,37 @@ struct GemmArgs {
   float wscale;
   int* status;
   int32_t n_tiles, m_tiles, ksteps;
+  // Work decomposition: tiles [0, full_tiles) are whole-K items; each of the rem_tiles after
+  // them is cut into `splits` K ranges of ks_per_split steps so that the last, partial wave
+  // still fills the machine.  Split partials meet in `slabs`; `counters` (zero between
+  // launches) elects the finishing CTA of each cut tile.
+  int32_t full_tiles, rem_tiles, splits, ks_per_split;
+  float* slabs;
+  int* counters;
 };
+
+struct WorkItem { int tile, ks0, nks, slot, part; };
+
+// The i-th work item of this CTA (items are dealt round-robin over the grid).
+__device__ __forceinline__ bool get_work(const GemmArgs& p, int i, WorkItem& w) {
+  const int idx = int(blockIdx.x) + i * int(gridDim.x);
+  if (idx < p.full_tiles) {
+    w.tile = idx; w.ks0 = 0; w.nks = p.ksteps; w.slot = -1; w.part = 0;
+    return true;
+  }
+  const int j = idx - p.full_tiles;
+  if (j >= p.rem_tiles * p.splits) return false;
+  if (p.splits == 1) {
+    w.tile = p.full_tiles + j; w.ks0 = 0; w.nks = p.ksteps; w.slot = -1; w.part = 0;
+    return true;
+  }
+  w.slot = j / p.splits;
+  w.part = j - w.slot * p.splits;
+  w.tile = p.full_tiles + w.slot;
+  w.ks0 = w.part * p.ks_per_split;
+  w.nks = min(p.ks_per_split, p.ksteps - w.ks0);
+  return true;
+}
 
 constexpr int kTileRows = 128;  // weight rows per CTA tile = TMEM lanes
 
@@ -203,7 +254,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
                               (uint32_t(kTileRows >> 4) << 24);
 
   extern __shared__ uint8_t gemm_smem_raw[];
-  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], aready_bar[TS], slotfree_bar[TS], tfull_bar[2], tempty_bar[2];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], aready_bar[TS], slotfree_bar[TS], tfull_bar[2], tempty_bar[2], esync_bar[2];
+  __shared__ int split_last;
   __shared__ uint32_t tmem_base_smem;
   __shared__ int abort_flag;
   uint8_t* stages = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(gemm_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -221,6 +273,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tfull_bar[b], 1);
       mbar_init(&tempty_bar[b], kEpiWarps);
+      mbar_init(&esync_bar[b], kEpiWarps);
     }
     abort_flag = 0;
     mbar_fence_init();
@@ -233,7 +286,6 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_base_smem;
-  const int total_tiles = p.n_tiles * p.m_tiles;
 
   if (warp == kProducerWarp) {
     // ------------------------------ TMA producer ------------------------------
@@ -241,9 +293,10 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
       tma_prefetch_desc(&wmap);
       tma_prefetch_desc(&amap);
       int it = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x) {
-        const int n_tile = tile / p.m_tiles, m_tile = tile - n_tile * p.m_tiles;
-        for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
+      WorkItem w;
+      for (int wi = 0; get_work(p, wi, w) && !abort_flag; ++wi) {
+        const int n_tile = w.tile / p.m_tiles, m_tile = w.tile - n_tile * p.m_tiles;
+        for (int ks = w.ks0; ks < w.ks0 + w.nks; ++ks, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, &abort_flag)) {
             if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_EMPTY); }
@@ -264,7 +317,8 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       int it = 0, tl = 0;
-      for (int tile = blockIdx.x; tile < total_tiles && !abort_flag; tile += gridDim.x, ++tl) {
+      WorkItem w;
+      for (; get_work(p, tl, w) && !abort_flag; ++tl) {
         const int acc = tl & 1;
         if (tl >= 2 && !mbar_wait(&tempty_bar[acc], ((tl >> 1) - 1) & 1, &abort_flag)) {
           if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
@@ -273,7 +327,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
         bool ok = true;
-        for (int ks = 0; ks < p.ksteps && ok; ++ks, ++it) {
+        for (int ks = w.ks0; ks < w.ks0 + w.nks && ok; ++ks, ++it) {
           const int s = it % STAGES, sl = it % TS;
           TL_TR(1, it, 0);
           ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag);
@@ -290,7 +344,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
 #pragma unroll
           for (int kk = 0; kk < KSTEP / 16; ++kk) {
             const uint64_t bdesc = make_b_desc(a_base + (kk >> 2) * kABox + (kk & 3) * 32);
-            tc_mma_ts(d_tmem, a_tmem + kk * 8, bdesc, kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+            tc_mma_ts(d_tmem, a_tmem + kk * 8, bdesc, kIdesc, (ks > w.ks0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[s]);      // the shared-memory stage is free once these MMAs have run
           tc_commit(&slotfree_bar[sl]);  // and so is the TMEM operand slot
@@ -307,15 +361,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     const uint32_t swz = KSTEP == 128 ? uint32_t(r & 7) : uint32_t((r >> 1) & 3);
     const uint32_t row_off = uint32_t(r) * KSTEP;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
-    // Flat walk over (tile, k-step).  The loop is software pipelined: the bytes of step i+1 are
-    // read and converted into registers while the TMEM stores of step i are still landing, and
-    // only then does the thread wait for those stores and signal the MMA issuer.
-    const int my_tiles = (total_tiles - int(blockIdx.x) + int(gridDim.x) - 1) / int(gridDim.x);
-    const int total_it = my_tiles * p.ksteps;
+    // Per k-step: wait for the stage, read this thread's bytes of its row, convert in registers,
+    // wait for a free TMEM operand slot, store, and signal the MMA issuer right away.  (Overlapping
+    // the next step's conversion with these stores measured slower: it delays the signal, and the
+    // short shared-memory ring makes the loop latency bound, not throughput bound.)
     uint32_t v[kChunks][8];
-    auto convert = [&](int it) -> bool {
+    auto convert = [&](int it, int ks, int n_tile) -> bool {
       const int s = it % STAGES;
-      const int tl = it / p.ksteps, ks = it - tl * p.ksteps;
       if (warp == 0 && lane == 0) TL_TR(2, it, 0);
       if (!mbar_wait(&full_bar[s], (it / STAGES) & 1, &abort_flag)) return false;
       if (warp == 0 && lane == 0) TL_TR(2, it, 1);
@@ -324,10 +376,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
 #pragma unroll
       for (int i = 0; i < kChunks; ++i) raw[i] = lds128(wb + ((uint32_t(part * kChunks + i) ^ swz) << 4));
       int64_t grow = 0;
-      if (GROUPED) {
-        const int n_tile = (int(blockIdx.x) + tl * int(gridDim.x)) / p.m_tiles;
-        grow = min(int64_t(n_tile) * kTileRows + r, p.n - 1);
-      }
+      if (GROUPED) grow = min(int64_t(n_tile) * kTileRows + r, p.n - 1);
 #pragma unroll
       for (int i = 0; i < kChunks; ++i) {
         const int c = part * kChunks + i;
@@ -356,23 +405,28 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
       }
       return true;
     };
-    bool ok = total_it > 0 && convert(0);
-    for (int it = 0; it < total_it && ok; ++it) {
-      const int sl = it % TS;
-      if (warp == 0 && lane == 0) TL_TR(2, it, 2);
-      if (it >= TS && !mbar_wait(&slotfree_bar[sl], ((it / TS) - 1) & 1, &abort_flag)) { ok = false; break; }
-      if (warp == 0 && lane == 0) TL_TR(2, it, 3);
-      tc_fence_after();
-      const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + sl * kSlotCols);
+    bool ok = true;
+    int it = 0;
+    WorkItem w;
+    for (int wi = 0; ok && get_work(p, wi, w); ++wi) {
+      const int n_tile = w.tile / p.m_tiles;
+      for (int ks = w.ks0; ks < w.ks0 + w.nks; ++ks, ++it) {
+        const int sl = it % TS;
+        if (!convert(it, ks, n_tile)) { ok = false; break; }
+        if (warp == 0 && lane == 0) TL_TR(2, it, 2);
+        if (it >= TS && !mbar_wait(&slotfree_bar[sl], ((it / TS) - 1) & 1, &abort_flag)) { ok = false; break; }
+        if (warp == 0 && lane == 0) TL_TR(2, it, 3);
+        tc_fence_after();
+        const uint32_t slot = tmem_base + lane_addr + uint32_t(2 * BN + sl * kSlotCols);
 #pragma unroll
-      for (int i = 0; i < kChunks; ++i) tmem_st8(slot + (part * kChunks + i) * 8, v[i]);
-      if (it + 1 < total_it) ok = convert(it + 1);  // overlaps the stores above
-      if (warp == 0 && lane == 0) TL_TR(2, it, 4);
-      tmem_st_wait();      // this thread's TMEM stores are complete
-      if (warp == 0 && lane == 0) TL_TR(2, it, 5);
-      tc_fence_before();
-      __syncwarp();        // ... and so are those of the other 31 lanes
-      if (lane == 0) mbar_arrive(&aready_bar[sl]);  // one arrival per warp keeps the barrier cheap
+        for (int i = 0; i < kChunks; ++i) tmem_st8(slot + (part * kChunks + i) * 8, v[i]);
+        if (warp == 0 && lane == 0) TL_TR(2, it, 4);
+        tmem_st_wait();      // this thread's TMEM stores are complete
+        if (warp == 0 && lane == 0) TL_TR(2, it, 5);
+        tc_fence_before();
+        __syncwarp();        // ... and so are those of the other 31 lanes
+        if (lane == 0) mbar_arrive(&aready_bar[sl]);  // one arrival per warp keeps the barrier cheap
+      }
     }
     if (!ok && lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_FULL); }
   } else {
@@ -382,11 +436,13 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
     // this warp's share of the BN token columns, in chunks of 16
     constexpr int kChunksN = BN / 16;
     const int cbeg = ehalf == 0 ? 0 : (kChunksN + 1) / 2, cend = ehalf == 0 ? (kChunksN + 1) / 2 : kChunksN;
-    int tl = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++tl) {
+    int tl = 0, esync = 0;
+    WorkItem w;
+    for (; get_work(p, tl, w); ++tl) {
       const int acc = tl & 1;
-      const int n_tile = tile / p.m_tiles, m_tile = tile - n_tile * p.m_tiles;
-      const int64_t ncol = int64_t(n_tile) * kTileRows + quad * 32 + lane;  // this thread's output column
+      const int n_tile = w.tile / p.m_tiles, m_tile = w.tile - n_tile * p.m_tiles;
+      const int r = quad * 32 + lane;
+      const int64_t ncol = int64_t(n_tile) * kTileRows + r;  // this thread's output column
       const bool n_ok = ncol < p.n;
       float sc = p.wscale;
       if (!GROUPED) sc *= n_ok ? tl_load_scale(p.scales, p.scales_dtype, ncol) : 0.f;
@@ -396,11 +452,48 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
       const float bias = (fast && epi.fast_bias && n_ok) ? __ldg(epi.fast_bias + ncol) : 0.f;
       const int esz = p.out_dtype == TL_F32 ? 4 : 2;
       const int64_t row_bytes = p.n * esz;
+      // sixteen accumulators of this thread's column (token rows m0 .. m0+15): epilogue + store
+      auto emit16 = [&](int c0, const uint32_t (&v)[16]) {
+        const int64_t m0 = int64_t(m_tile) * BN + c0;
+        const int jmax = n_ok ? int(min(int64_t(16), p.m - m0)) : 0;
+        uint8_t* optr = reinterpret_cast<uint8_t*>(p.out) + m0 * row_bytes + ncol * esz;
+        if (fast) {
+          // sixteen independent chains with the op decided once per chunk, not per element
+          float o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = fmaf(__uint_as_float(v[j]), sca, bias);
+          if (epi.fast_unary) unary16(epi.fast_unary, approx, o);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < jmax) {
+              if (p.out_dtype == TL_F32) *reinterpret_cast<float*>(optr) = o[j];
+              else if (p.out_dtype == TL_F16) *reinterpret_cast<__half*>(optr) = __float2half_rn(o[j]);
+              else *reinterpret_cast<__nv_bfloat16*>(optr) = __float2bfloat16_rn(o[j]);
+            }
+            optr += row_bytes;
+          }
+        } else {
+          // general op chain (binary operands, casts, several ops): rolled, one element at a time
+          float vv[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) vv[j] = __uint_as_float(v[j]);
+#pragma unroll 1
+          for (int j = 0; j < jmax; ++j) {
+            const float o = tl_apply_epilogue(epi, vv[j] * sc, m0 + j, ncol, p.n);
+            if (p.out_dtype == TL_F32) *reinterpret_cast<float*>(optr) = o;
+            else if (p.out_dtype == TL_F16) *reinterpret_cast<__half*>(optr) = __float2half_rn(o);
+            else *reinterpret_cast<__nv_bfloat16*>(optr) = __float2bfloat16_rn(o);
+            optr += row_bytes;
+          }
+        }
+      };
       if (!mbar_wait(&tfull_bar[acc], (tl >> 1) & 1, &abort_flag)) {
         if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
         break;
       }
       tc_fence_after();
+      const bool split = w.slot >= 0;
+      float* my_slab = split ? p.slabs + (size_t(w.slot) * p.splits + w.part) * size_t(kTileRows * BN) : nullptr;
       uint32_t vn[16];
       if (cbeg < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + cbeg * 16), vn);
 #pragma unroll 1
@@ -411,29 +504,59 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
 #pragma unroll
         for (int j = 0; j < 16; ++j) v[j] = vn[j];
         if (ch + 1 < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + c0 + 16), vn);  // next chunk in flight
-        const int64_t m0 = int64_t(m_tile) * BN + c0;
-        const int jmax = n_ok ? int(min(int64_t(16), p.m - m0)) : 0;
-        uint8_t* optr = reinterpret_cast<uint8_t*>(p.out) + m0 * row_bytes + ncol * esz;
+        if (!split) {
+          emit16(c0, v);
+        } else {
+          // a K range of a cut tile: park the partial sums, token-major so that lanes coalesce
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          if (j < jmax) {
-            float o;
-            if (fast) {
-              o = fmaf(__uint_as_float(v[j]), sca, bias);
-              if (epi.fast_unary) o = approx ? tl_unary_approx(epi.fast_unary, o) : tl_unary(epi.fast_unary, o);
-            } else {
-              o = tl_apply_epilogue(epi, __uint_as_float(v[j]) * sc, m0 + j, ncol, p.n);
-            }
-            if (p.out_dtype == TL_F32) *reinterpret_cast<float*>(optr) = o;
-            else if (p.out_dtype == TL_F16) *reinterpret_cast<__half*>(optr) = __float2half_rn(o);
-            else *reinterpret_cast<__nv_bfloat16*>(optr) = __float2bfloat16_rn(o);
-          }
-          optr += row_bytes;
+          for (int j = 0; j < 16; ++j) my_slab[(c0 + j) * kTileRows + r] = __uint_as_float(v[j]);
         }
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[acc]);
+      if (split) {
+        // Elect the CTA that finishes this tile: the one whose partial arrives last.  The
+        // epilogue warps meet on mbarriers (bounded waits), never on bar.sync, so a warp that
+        // gave up cannot strand the others.
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&esync_bar[0]);
+        bool ok = mbar_wait(&esync_bar[0], esync & 1, &abort_flag);
+        if (ok && warp == kEpiWarp0 && lane == 0) {
+          const int prev = atomicAdd(p.counters + w.slot, 1);
+          split_last = prev == p.splits - 1;
+          if (split_last) p.counters[w.slot] = 0;  // every part has arrived: leave the counter clear
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&esync_bar[1]);
+        ok = ok && mbar_wait(&esync_bar[1], esync & 1, &abort_flag);
+        ++esync;
+        if (!ok) {
+          if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
+          break;
+        }
+        if (split_last) {
+          __threadfence();
+          const float* slab0 = p.slabs + size_t(w.slot) * p.splits * size_t(kTileRows * BN);
+#pragma unroll 1
+          for (int ch = cbeg; ch < cend; ++ch) {
+            const int c0 = ch * 16;
+            float sum[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[j] = 0.f;
+            for (int part = 0; part < p.splits; ++part) {  // fixed order: the result does not depend on arrival order
+              const float* sp = slab0 + size_t(part) * size_t(kTileRows * BN) + size_t(c0) * kTileRows + r;
+#pragma unroll
+              for (int j = 0; j < 16; ++j) sum[j] += __ldcg(sp + j * kTileRows);
+            }
+            uint32_t v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(sum[j]);
+            emit16(c0, v);
+          }
+        }
+      }
     }
   }
 
@@ -522,10 +645,10 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
     else if (m <= 32) { v.p0 = 32; v.p1 = 128; v.p2 = 8; v.p3 = 8; }
     else if (m <= 64) { v.p0 = 64; v.p1 = 128; v.p2 = 6; v.p3 = 8; }
     else {
-      // 128 tokens x 128 k per step measured best overall; the 192-token tile wins only when it
-      // pads the token count noticeably less
+      // 192 tokens x 128 k per step measured ~1.3x the throughput of the 128-token tile per padded
+      // token, so it wins unless it pads the token count by more than that
       const int64_t pad192 = (m + 191) / 192 * 192, pad128 = (m + 127) / 128 * 128;
-      if (pad192 * 10 < pad128 * 9) { v.p0 = 192; v.p1 = 64; v.p2 = 6; v.p3 = 8; }
+      if (pad192 * 3 <= pad128 * 4) { v.p0 = 192; v.p1 = 128; v.p2 = 3; v.p3 = 8; }
       else { v.p0 = 128; v.p1 = 128; v.p2 = 4; v.p3 = 8; }
     }
   } else {
@@ -600,12 +723,35 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   p.m_tiles = int32_t((m + bn - 1) / bn);
   p.ksteps = int32_t((k + kstep - 1) / kstep);
   const int64_t tiles = int64_t(p.n_tiles) * p.m_tiles;
-  const int grid = int(std::min<int64_t>(ctx->sm_count, tiles));
+  // Whole waves run one tile per CTA; the tiles of the last, partial wave are cut along K
+  // (at most kMaxSplits ways) so that it still occupies most of the machine.
+  constexpr int kMaxSplits = 4;
+  const int sms = ctx->sm_count;
+  p.full_tiles = int32_t(tiles / sms * sms);
+  p.rem_tiles = int32_t(tiles - p.full_tiles);
+  p.splits = 1;
+  if (p.rem_tiles > 0) {
+    int s = std::min<int>({sms / p.rem_tiles, kMaxSplits, p.ksteps});
+    while (s > 1 && (s - 1) * ((p.ksteps + s - 1) / s) >= p.ksteps) --s;  // every part gets at least one step
+    p.splits = std::max(1, s);
+  }
+  p.ks_per_split = (p.ksteps + p.splits - 1) / p.splits;
+  const int64_t items = int64_t(p.full_tiles) + int64_t(p.rem_tiles) * p.splits;
+  const int grid = int(std::min<int64_t>(sms, items));
   if (receipt) {
     receipt->choice = v;
     receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
-    receipt->block = (v.p3 + 10) * 32; receipt->split_k = 1;
+    receipt->block = (v.p3 + 10) * 32; receipt->split_k = p.splits;
     return TL_OK;
+  }
+  if (p.splits > 1) {
+    void* slabs = nullptr;
+    void* counters = nullptr;
+    int32_t rc = tl_ensure_scratch(ctx, size_t(p.rem_tiles) * p.splits * kTileRows * bn * sizeof(float), &slabs);
+    if (rc == TL_OK) rc = tl_ensure_zeroed_scratch(ctx, size_t(p.rem_tiles) * sizeof(int), &counters);
+    if (rc != TL_OK) return rc;
+    p.slabs = static_cast<float*>(slabs);
+    p.counters = static_cast<int*>(counters);
   }
   if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "qgemm: weight and activation pointers must be 16-byte aligned");
