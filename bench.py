@@ -311,11 +311,19 @@ def run_gpu(args):
 
     cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
     stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if world > 1 else "nccl",
-                        fuse=not args.no_fuse)
+                        fuse=not args.no_fuse, chain=args.step_launch == "chain")
+    chained = stack.uses_chain()
     if args.autotune:
         shapes = sorted({(cfg.batch, p.n, p.k) for p in stack.layers[0]} | {(cfg.batch, stack.lm_head.n, stack.lm_head.k)})
         for (m, n, k) in shapes:
             be.pretuneMatmulShapes([(m, n, k)], cfg.act_dtype, cfg.act_dtype, tb.QuantPacking("int8-grouped", k, "f32", "direct"))
+    if chained and args.chain_shape:
+        w, d = (int(v) for v in args.chain_shape.split(","))
+        be.forceVariant((B.TL_FAMILY_QGEMV, 7, w, d, 0, 0))
+        try:
+            stack.build_chain()
+        finally:
+            be.forceVariant(None)
     stack.capture()
 
     def barrier():
@@ -390,9 +398,11 @@ def run_gpu(args):
     achieved = alg / (ms_per_step * 1e-3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak,
                 "traffic": None, "peak_source": f"{which} (MEASURED_PEAKS.json hbm_gbs)" if which == "measured" else "fallback 6650 GB/s",
-                "kernel": "qgemv_ring_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
+                "kernel": "qgemv_chain_kernel" if chained else "qgemv_ring_kernel", "algorithmic_bytes_per_launch": alg / gemv_launches,
                 "avg_launch_us": ms_per_step * 1e3 / gemv_launches,
-                "note": f"per rank; all {gemv_launches} small-batch GEMV launches of one step (253 projections), events on the launching stream"
+                "note": ("per rank; one persistent launch runs all 253 projections of a step (145 phases), events on the launching stream"
+                         if chained else
+                         f"per rank; all {gemv_launches} small-batch GEMV launches of one step (253 projections), events on the launching stream")
                         + ("" if world == 1 else "; at N>1 the step time also holds the NCCL collectives")}
     tpath = os.path.join(ROOT, "profiles", "traffic.json")
     if os.path.exists(tpath):
@@ -423,8 +433,10 @@ def run_gpu(args):
                        "hidden": cfg.hidden, "intermediate": cfg.inter, "vocab": cfg.vocab,
                        "weights": "int8 per-channel, f32 scales, random init", "parallelism": f"tp{world}",
                        "tp_mode": args.tp_mode if world > 1 else "none",
-                       "allreduce": args.allreduce if world > 1 else "none", "replay": "cuda graph",
-                       "fusion": "none" if args.no_fuse else "q+k+v and gate+up share one launch each (same activations)",
+                       "allreduce": args.allreduce if world > 1 else "none",
+                       "replay": "one persistent cooperative launch per step (tl_qgemv_chain)" if chained else "cuda graph",
+                       "fusion": ("vertical: all 253 projections in one launch, weight prefetch runs across phase boundaries" if chained
+                                  else "none" if args.no_fuse else "q+k+v and gate+up share one launch each (same activations)"),
                        "l2": "inputs larger than L2: 7.57 GB of weights per step, no flush needed",
                        "autotune": bool(args.autotune)},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -455,6 +467,10 @@ def main():
     ap.add_argument("--autotune", action="store_true")
     ap.add_argument("--allreduce", default="p2p", choices=["p2p", "nccl"],
                     help="row-parallel sums: the library's one-shot peer-memory kernel, or NCCL")
+    ap.add_argument("--step-launch", default="graph", choices=["chain", "graph"],
+                    help="graph: a replayed CUDA graph of per-projection launches (the measured-faster default); "
+                         "chain: the whole step as one persistent cooperative launch (one GPU, batch <= 16)")
+    ap.add_argument("--chain-shape", default="", help="warps,depth of the chain kernel's CTAs (default: the library's)")
     ap.add_argument("--no-fuse", action="store_true", help="one launch per projection (no q/k/v and gate/up fusion)")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-matrix GEMV / prefill GEMM figures")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline sample")

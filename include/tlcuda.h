@@ -169,6 +169,36 @@ TL_API int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dtype, 
                                    int32_t n_items, int32_t out_dtype, int32_t m, int64_t k,
                                    const tl_quant_desc* qdesc);
 
+/* Vertical fusion (no counterpart in the reference, whose executor replays one dispatch per
+ * node of a compiled plan, src/executor/lazy-executor.ts): a whole SEQUENCE of dependent
+ * small-batch products -- the matmuls of a decode step -- in one persistent cooperative
+ * launch.  A phase is 1..4 projections that read the same activations a[m, k] (the items of
+ * tl_qgemv_nt_batched); phases run in order, and the activations of a phase may be outputs of
+ * any earlier phase.  The weight stream runs ahead across phase boundaries.  Experimental:
+ * results are exact, but on the decode stack it measured slower than a replayed graph of
+ * tl_qgemv_nt launches, which stays the recommended path.  Results equal those of tl_qgemv_nt on the
+ * same operands (same summation order as its "ring" kernel with 8 warps).
+ * Limits: m in [1,16]; f16/bf16 activations, 16-byte aligned; every K % 64 == 0; group_size
+ * % 64 == 0 and dividing K (group_size == k: one scale per output channel); an item's out
+ * must not alias its phase's activations.  Pointers (weights, scales, outputs, activations,
+ * epilogue inputs) are captured at creation and must stay valid until the chain is destroyed.
+ * tl_qgemv_chain_launch enqueues a 4-byte-per-phase memset and the kernel on the context's
+ * stream; it moves the quant-GEMV counter by the number of items and the launch counter by 1. */
+typedef struct tl_chain tl_chain;
+typedef struct tl_chain_phase {
+  const void* a;      /* activations [m, k] */
+  int64_t k;
+  int32_t group_size; /* as tl_quant_desc.group_size, for this phase's K */
+  int32_t out_dtype;  /* of this phase's outputs [m, n_i] */
+  int32_t n_items;
+  int32_t reserved;
+  tl_qgemv_item items[4];
+} tl_chain_phase;
+TL_API int32_t tl_qgemv_chain_create(tl_ctx* ctx, const tl_chain_phase* phases, int32_t n_phases, int32_t a_dtype,
+                                     int32_t m, int32_t scales_dtype, int32_t scale_convention, tl_chain** out);
+TL_API int32_t tl_qgemv_chain_launch(tl_ctx* ctx, tl_chain* chain);
+TL_API int32_t tl_qgemv_chain_destroy(tl_ctx* ctx, tl_chain* chain);
+
 /* No counterpart in the reference.  Same operation and arguments as tl_qgemv_nt for
  * hosts that must not allocate device memory at call time (a stream capture is open,
  * all memory belongs to the host's own pool, or cudaMalloc's device-wide

@@ -377,6 +377,47 @@ class CudaBackend:
             outBuffer.buffer, B.DTYPE_ID[outputDtype], m, n, k, C.byref(q), alpha,
             C.byref(e) if e is not None else None))
 
+    def createQuantizedGemvChain(self, phases: Sequence[dict], m: int, scaleConvention: str = "direct"):
+        """Vertical fusion (no counterpart in the reference): describe a sequence of dependent
+        small-batch quantized products once, then run it as ONE persistent launch with
+        ``runQuantizedGemvChain``.  Each phase is a dict
+        ``{"a": CudaTensor [m,k], "k": int, "groupSize": int, "outputDtype": str, "items": [...]}``
+        whose items are dicts ``{"packed", "scales", "out", "n", "alpha", "epilogue", "epilogueInputs"}``
+        with the meaning of ``dispatchQuantizedGemvNT``'s arguments (1..4 items share the
+        phase's activations)."""
+        arr = (B.ChainPhase * len(phases))()
+        keep = []
+        scales_dtype = None
+        for pi, ph in enumerate(phases):
+            c = arr[pi]
+            c.a, c.k, c.group_size = ph["a"].buffer, ph["k"], ph["groupSize"]
+            c.out_dtype, c.n_items = B.DTYPE_ID[ph.get("outputDtype", "f32")], len(ph["items"])
+            if len(ph["items"]) > 4:
+                raise TlError(B.TL_ERR_INVALID_ARG, "chain: at most 4 items per phase")
+            for ii, it in enumerate(ph["items"]):
+                e = self._epilogue(it.get("epilogue"), it.get("epilogueInputs", ()))
+                if e is not None:
+                    keep.append(e)
+                sd = "f16" if it["scales"].dtype == "u16" else "f32"
+                if scales_dtype not in (None, sd):
+                    raise TlError(B.TL_ERR_INVALID_ARG, "chain: all scales must share one dtype")
+                scales_dtype = sd
+                c.items[ii] = B.QGemvItem(it["packed"].buffer, it["scales"].buffer, it["out"].buffer, it["n"],
+                                          it.get("alpha", 1.0), C.pointer(e) if e is not None else None)
+        convention = B.TL_SCALE_SNORM127 if scaleConvention == "snorm127" else B.TL_SCALE_DIRECT
+        handle = C.c_void_p()
+        a_dtype = B.DTYPE_ID[phases[0]["a"].dtype]
+        B.check(self._ctx, self._lib.tl_qgemv_chain_create(self._ctx, arr, len(phases), a_dtype, m,
+                                                           B.DTYPE_ID[scales_dtype or "f32"], convention,
+                                                           C.byref(handle)))
+        return handle
+
+    def runQuantizedGemvChain(self, chain):
+        B.check(self._ctx, self._lib.tl_qgemv_chain_launch(self._ctx, chain))
+
+    def destroyQuantizedGemvChain(self, chain):
+        B.check(self._ctx, self._lib.tl_qgemv_chain_destroy(self._ctx, chain))
+
     def dispatchDequantizeInt8Grouped(self, packedWeight: CudaTensor, scales: CudaTensor, outBuffer: CudaTensor,
                                       n: int, k: int, groupSize: int, *, packing: Optional[QuantPacking] = None):
         """dispatch.ts:949-1037: explicit dequant to [N,K] of outBuffer.dtype."""

@@ -51,6 +51,11 @@ class QGemvItem(C.Structure):
                 ("alpha", C.c_float), ("epilogue", C.POINTER(Epilogue))]
 
 
+class ChainPhase(C.Structure):
+    _fields_ = [("a", C.c_void_p), ("k", C.c_int64), ("group_size", C.c_int32), ("out_dtype", C.c_int32),
+                ("n_items", C.c_int32), ("reserved", C.c_int32), ("items", QGemvItem * 4)]
+
+
 class Variant(C.Structure):
     _fields_ = [("family", C.c_int32), ("kernel", C.c_int32), ("p0", C.c_int32), ("p1", C.c_int32),
                 ("p2", C.c_int32), ("p3", C.c_int32)]
@@ -93,6 +98,9 @@ SIGNATURES = {
     "tl_qgemv_nt": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemv_nt_static_scratch": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemv_nt_batched": (_I32, [_P, _P, _I32, C.POINTER(QGemvItem), _I32, _I32, _I32, _I64, C.POINTER(QuantDesc)]),
+    "tl_qgemv_chain_create": (_I32, [_P, C.POINTER(ChainPhase), _I32, _I32, _I32, _I32, _I32, C.POINTER(C.c_void_p)]),
+    "tl_qgemv_chain_launch": (_I32, [_P, _P]),
+    "tl_qgemv_chain_destroy": (_I32, [_P, _P]),
     "tl_qgemm_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qmatmul_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_dequant_int8": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),

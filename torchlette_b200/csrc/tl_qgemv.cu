@@ -33,7 +33,7 @@
 
 namespace {
 
-constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4, kTma = 5, kBulk = 6;
+constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4, kTma = 5, kBulk = 6, kChain = 7;
 
 // geometry of the "bulk" kernel for a given k: tiles per stage, stage bytes, stages, warps per tile
 struct BulkGeom { int rt, nstages, p; uint32_t stage_bytes; size_t smem; bool ok; };
@@ -1311,7 +1311,6 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
 
 int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q, tl_variant* out) {
-  (void)m;
   tl_variant v{};
   v.family = TL_FAMILY_QGEMV;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
@@ -1326,8 +1325,12 @@ int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, i
       int depth = 2;
       for (int cand : {4, 6, 8})
         if (per_sm * (int64_t(cand) * 4096 + 2048 + 1024) <= 224 * 1024) depth = cand;
+      // two token tiles (m > 8) double the accumulators: the registers then cap the resident
+      // CTAs, and rings deeper than 4 measured 1.5x slower
+      if (m > 8) depth = std::min(depth, 4);
       v.p0 = 4; v.p1 = depth;
-    } else { v.p0 = 16; v.p1 = 2; }
+    } else if (m > 8) { v.p0 = 8; v.p1 = 4; }
+    else { v.p0 = 16; v.p1 = 4; }
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -1738,3 +1741,591 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
   ctx->counters[TL_COUNTER_QGEMV_EPILOGUE] += n_epi;
   return TL_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Persistent chain ("vertical fusion"): a whole sequence of dependent small-batch
+// products -- the decode step of a layer stack -- in ONE cooperative launch.
+//
+// Launch boundaries are what a stream of single GEMVs loses most of its time to: every
+// kernel ramps its loads up from nothing and drains them at the end (about 4 us per launch
+// against 2.7-16 us of streaming for the decode projections).  Here the weight stream never
+// stops.  Every CTA owns a flat sequence of 16-row tiles that runs through ALL phases
+// (phase = up to four projections that read the same activations), and every thread keeps
+// S 16-byte cp.async copies per row in flight along that sequence -- the prefetch cursor
+// simply walks on into the next tile, and the next phase, because weight addresses never
+// depend on results.  Only the consumer side is phase-ordered: before a CTA reads the
+// activations of phase p it waits until all CTAs with tiles in phase p-1 have stored theirs
+// (one arrival counter per phase in global memory, release/acquire at GPU scope).  While it
+// waits, its prefetched next-phase weights keep landing, so HBM stays busy across the barrier.
+//
+// The sequence of a CTA is a table the host writes once (ChainTile records, in execution
+// order, everything a tile needs in 80 bytes): walking it is one broadcast load per tile,
+// issued a tile ahead, never a chain of dependent descriptor loads.  (A first version walked
+// phase descriptors on the device; their cold-miss latency, 3-6 us per tile, sat inside the
+// k loop and made the chain slower than separate launches.)
+//
+// The tile arithmetic (fragment mapping, W warps interleaved over 64-wide k blocks, summation
+// order) is the ring kernel's, so a chain gives the same bits as ring launches with W warps.
+// Shape: W = 8 warps per tile and S = 12 k blocks in flight per thread, two CTAs per SM, so
+// that a CTA's ring (W*S KB = 96 KB) holds more than one 16 x 4096 tile.
+//
+// Standing: correct (bit-identical to ring launches) but NOT yet faster than a replayed graph
+// of ring launches on the Qwen3-8B stack (2.3-2.6 ms against 1.8-2.0 ms per step).  Device
+// traces show why: the weight wait is zero (the prefetch does run ahead), but one k-block
+// iteration of a warp takes 0.3 us at batch 1 and 0.6 us at batch 8 -- with one or two tiles
+// per CTA and phase every activation line is touched about once per SM, so the activation
+// loads miss L1 and cost an L2 round trip per iteration that a short register queue cannot
+// hide, and 16-24 warps per SM are too few to cover it; phases whose tile count is not a
+// multiple of the grid add a 5-6 us wait at the next gate.  It is kept as an explicit entry
+// point and is not what tl_qgemv_nt or the benchmark's default path run.
+// Tiles of a phase are dealt round-robin starting at a rotating CTA, which balances the
+// cumulative load.  All CTAs are co-resident (cooperative launch).  Every spin is bounded; a
+// wait that runs out raises the status word and a global abort word that ends everybody's.
+// ---------------------------------------------------------------------------
+namespace {
+
+constexpr int kChainMaxItems = 4;
+constexpr unsigned kChainSpinLimit = 1u << 20;
+
+struct alignas(16) ChainTile {
+  const uint8_t* w;      // first weight row of the tile
+  const void* a;         // activations [m, k] of the phase
+  const void* scales;    // the item's scales
+  void* out;             // the item's output [m, n]
+  const EpiParams* epi;  // the item's epilogue
+  uint64_t pad_;
+  int32_t k, n, tile_row, phase;             // k == 0 ends the list
+  int32_t group, out_dtype, wait_for, arrive;  // wait_for: arrivals of phase-1 to see first (0: none);
+                                               // arrive: this is the CTA's last tile of its phase
+};
+static_assert(sizeof(ChainTile) == 80, "record layout");
+
+struct ChainArgs {
+  const ChainTile* sched;  // [grid][stride]
+  unsigned* bar;           // [n_phases] arrival counters, then one abort word; all zero at launch
+  int* status;
+  int32_t stride, n_phases, m, scales_dtype;
+  float wscale;
+};
+
+__device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_act128(const void* p) {
+  // Activations are written by other CTAs of this same launch, so never the non-coherent path
+  // (ld.global.nc / __ldg).  An ordinary cached load is correct here: it is ordered after the
+  // acquire on the phase counter (thread 0) and the CTA barrier that follows it, exactly the
+  // pattern of a grid-wide barrier, and L1 reuse across the CTAs of an SM is what keeps the
+  // activation traffic off L2.
+  uint4 v;
+  asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+
+// The part of a record the prefetch cursor needs.
+struct ChainFetchRec {
+  const uint8_t* w;
+  int32_t k, n, tile_row;
+};
+// Schedule records are read with volatile asm loads: an ordinary load may be sunk by the compiler
+// to its first use, a whole tile later, which puts the miss latency back on the critical path.
+__device__ __forceinline__ int4 ld_sched128(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint64_t ptr_of(int lo, int hi) { return (uint64_t(uint32_t(hi)) << 32) | uint32_t(lo); }
+__device__ __forceinline__ ChainFetchRec chain_load_fetch(const ChainTile* t) {
+  ChainFetchRec r;
+  const int4 p0 = ld_sched128(&t->w);  // w, a
+  const int4 v = ld_sched128(&t->k);
+  r.w = reinterpret_cast<const uint8_t*>(ptr_of(p0.x, p0.y));
+  r.k = v.x; r.n = v.y; r.tile_row = v.z;
+  return r;
+}
+
+#ifdef TL_TRACE
+__device__ unsigned long long g_chain_trace[2][256][6];
+__device__ __forceinline__ unsigned long long chain_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TL_CTR(ph, ev) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == 200) && (ph) < 256) g_chain_trace[blockIdx.x ? 1 : 0][ph][ev] = chain_now(); } while (0)
+__device__ unsigned long long g_chain_iter[4][32][4];
+#define TL_CIT(ph, it, ev) do { if (threadIdx.x == 0 && blockIdx.x == 0 && (ph) >= 4 && (ph) < 8 && (it) < 32) g_chain_iter[(ph) - 4][it][ev] = chain_now(); } while (0)
+#else
+#define TL_CTR(ph, ev) do {} while (0)
+#define TL_CIT(ph, it, ev) do {} while (0)
+#endif
+
+// A whole record, for the consumer side (five 16-byte broadcast loads).
+struct ChainRec {
+  const void* a;
+  const void* scales;
+  void* out;
+  const EpiParams* epi;
+  int32_t k, n, tile_row, phase, group, out_dtype, wait_for, arrive;
+};
+__device__ __forceinline__ ChainRec chain_load_rec(const ChainTile* t) {
+  const int4 p0 = ld_sched128(&t->w);       // w, a
+  const int4 p1 = ld_sched128(&t->scales);  // scales, out
+  const int4 p2 = ld_sched128(&t->epi);     // epi, pad
+  const int4 i0 = ld_sched128(&t->k);
+  const int4 i1 = ld_sched128(&t->group);
+  ChainRec r;
+  r.a = reinterpret_cast<const void*>(ptr_of(p0.z, p0.w));
+  r.scales = reinterpret_cast<const void*>(ptr_of(p1.x, p1.y));
+  r.out = reinterpret_cast<void*>(ptr_of(p1.z, p1.w));
+  r.epi = reinterpret_cast<const EpiParams*>(ptr_of(p2.x, p2.y));
+  r.k = i0.x; r.n = i0.y; r.tile_row = i0.z; r.phase = i0.w;
+  r.group = i1.x; r.out_dtype = i1.y; r.wait_for = i1.z; r.arrive = i1.w;
+  return r;
+}
+
+template <typename AT, int NT, bool GROUPED, int W, int S, int MINB>
+__global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainArgs c) {
+  constexpr int kThreads = W * 32;
+  extern __shared__ __align__(16) uint8_t chain_smem[];
+  uint4* ring = reinterpret_cast<uint4*>(chain_smem);                               // [S][2][threads]
+  float* red = reinterpret_cast<float*>(chain_smem + size_t(S) * 2 * kThreads * 16);  // [W][NT][4][32]
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
+  constexpr uint32_t kSlotBytes = kThreads * 16u;
+  const ChainTile* my = c.sched + size_t(blockIdx.x) * size_t(c.stride);
+  unsigned* abort_word = c.bar + c.n_phases;
+  if (tid == 0) s_abort = 0;
+
+  // ---- prefetch cursor: S k blocks ahead of the consumer, along the same flat sequence ----
+  int fj = 0, left = 0;
+  bool fend = false;
+  const uint8_t *w_lo = nullptr, *w_hi = nullptr;
+  ChainFetchRec fcur = chain_load_fetch(my), fnxt = chain_load_fetch(my + 1);
+  auto fetch_open = [&]() {
+    // settle on the next record that has k blocks for this warp, or on the end of the list
+    while (true) {
+      if (fcur.k == 0) { fend = true; left = 0; return; }
+      left = ((fcur.k >> 6) - warp + W - 1) / W;
+      if (left > 0) break;
+      fcur = fnxt;
+      ++fj;
+      fnxt = chain_load_fetch(my + fj + 1);
+    }
+    const int last = fcur.n - 1 - fcur.tile_row;  // last valid row of the tile (clamped like the ring kernel)
+    w_lo = fcur.w + int64_t(min(g, last)) * fcur.k + 16 * t + warp * 64;
+    w_hi = fcur.w + int64_t(min(g + 8, last)) * fcur.k + 16 * t + warp * 64;
+  };
+  fetch_open();
+  auto fetch_into = [&](int slot) {
+    if (!fend) {
+      cp_async16(ring_base + uint32_t(2 * slot) * kSlotBytes, w_lo);
+      cp_async16(ring_base + uint32_t(2 * slot + 1) * kSlotBytes, w_hi);
+      w_lo += W * 64;
+      w_hi += W * 64;
+      if (--left == 0) {
+        fcur = fnxt;
+        ++fj;
+        fnxt = chain_load_fetch(my + fj + 1);  // needed a whole tile from now
+        fetch_open();
+      }
+    }
+    cp_async_commit();  // one group per step, empty or not, keeps wait_group's count uniform
+  };
+#pragma unroll 1
+  for (int s = 0; s < S; ++s) fetch_into(s);
+  __syncthreads();
+
+  int slot = 0, cj = 0;
+  ChainRec cur = chain_load_rec(my);
+  while (cur.k != 0) {
+    const ChainRec nxt = chain_load_rec(my + cj + 1);  // used at the end of this tile
+    // ---- gate: the activations of this phase are the stores of the phases before it ----
+    TL_CTR(cur.phase, 0);
+    if (cur.wait_for > 0) {
+      if (tid == 0) {
+        const unsigned want = unsigned(cur.wait_for);
+        unsigned spins = 0;
+        while (ld_acquire_gpu(c.bar + (cur.phase - 1)) < want) {
+          if (++spins > kChainSpinLimit || ld_acquire_gpu(abort_word) != 0u) {
+            if (spins > kChainSpinLimit) { atomicExch(c.status, TL_DEV_TIMEOUT_FULL); atomicExch(abort_word, 1u); }
+            s_abort = 1;
+            break;
+          }
+          __nanosleep(20);
+        }
+      }
+      __syncthreads();
+      if (s_abort) break;
+      __threadfence();
+    }
+    TL_CTR(cur.phase, 1);
+    const int k = cur.k, n = cur.n;
+    const int64_t tile_row = cur.tile_row;
+    const AT* a = reinterpret_cast<const AT*>(cur.a);
+    const AT* a_col[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) a_col[nt] = a + int64_t(min(g + 8 * nt, c.m - 1)) * k + 16 * t + warp * 64;
+    const int nkb = ((k >> 6) - warp + W - 1) / W;
+    const void* scales = cur.scales;
+    const int group = GROUPED ? cur.group : 0, gpr = GROUPED ? k / cur.group : 0;
+    const int64_t r_lo = min(tile_row + g, int64_t(n) - 1), r_hi = min(tile_row + g + 8, int64_t(n) - 1);
+
+    // What the epilogue will need comes from global memory: ask for it now, so that the latency
+    // hides behind the k loop instead of following it.
+    constexpr int kOutPerThread = (NT * 128 + kThreads - 1) / kThreads;
+    float pre_scale[kOutPerThread], pre_bias[kOutPerThread];
+    const EpiParams& epi = *cur.epi;
+    const int epi_fast = __ldg(&epi.fast), epi_unary = __ldg(&epi.fast_unary);
+    const float epi_alpha = __ldg(&epi.alpha);
+    const float* epi_bias = reinterpret_cast<const float*>(__ldg(reinterpret_cast<const unsigned long long*>(&epi.fast_bias)));
+#pragma unroll
+    for (int u = 0; u < kOutPerThread; ++u) {
+      const int o = tid + u * kThreads;
+      const int64_t row = tile_row + ((o & 31) >> 2) + (((o >> 5) & 2) ? 8 : 0);
+      const bool live = o < NT * 128 && row < n;
+      pre_scale[u] = (!GROUPED && live) ? tl_load_scale(scales, c.scales_dtype, row) : 1.f;
+      pre_bias[u] = (live && epi_fast && epi_bias) ? __ldg(epi_bias + row) : 0.f;
+    }
+
+    float total[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
+
+    // Activations are loaded PD k blocks ahead into a register queue.  With one or two tiles per
+    // CTA and phase, every activation line is touched about once per SM, so these loads mostly
+    // miss L1: an L2 round trip (~0.4 us) per k block unless it is issued well ahead.  The queue
+    // is indexed statically (the loop is unrolled PD-fold): shifting it with moves would make
+    // every move wait for the load still in flight to its source register.
+    constexpr int PD = (W * 32 * MINB > 512) ? (NT == 1 ? 2 : 1) : (NT == 1 ? 3 : 2);
+    uint4 bq[PD][NT][2];
+#pragma unroll
+    for (int d = 0; d < PD; ++d)
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const AT* src = a_col[nt] + int64_t(d) * (W * 64);
+        bq[d][nt][0] = d < nkb ? ld_act128(src) : make_uint4(0, 0, 0, 0);
+        bq[d][nt][1] = d < nkb ? ld_act128(src + 8) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll 1
+    for (int i0 = 0; i0 < nkb; i0 += PD) {
+#pragma unroll
+      for (int d = 0; d < PD; ++d) {
+        const int i = i0 + d;
+        if (i >= nkb) break;
+        uint4 bx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          bx[nt][0] = bq[d][nt][0];
+          bx[nt][1] = bq[d][nt][1];
+          if (i + PD < nkb) {
+            const AT* src = a_col[nt] + int64_t(i + PD) * (W * 64);
+            bq[d][nt][0] = ld_act128(src);
+            bq[d][nt][1] = ld_act128(src + 8);
+          }
+        }
+        TL_CIT(cur.phase, i, 0);
+        cp_async_wait<S - 1>();
+        TL_CIT(cur.phase, i, 1);
+        const uint4 wl = ring[(2 * slot) * kThreads + tid];
+        const uint4 wh = ring[(2 * slot + 1) * kThreads + tid];
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) acc[nt][e] = GROUPED ? 0.f : total[nt][e];
+        const uint32_t wlo[4] = {wl.x, wl.y, wl.z, wl.w};
+        const uint32_t whi[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t a0, a1, a2, a3;
+          MmaOps<AT>::cvt(wlo[j], a0, a2);
+          MmaOps<AT>::cvt(whi[j], a1, a3);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            const uint4 v = bx[nt][j >> 1];
+            const uint32_t b0 = (j & 1) ? v.z : v.x, b1 = (j & 1) ? v.w : v.y;
+            MmaOps<AT>::mma(acc[nt], a0, a1, a2, a3, b0, b1);
+          }
+        }
+        TL_CIT(cur.phase, i, 2);
+        fetch_into(slot);  // the slot's words are in registers and consumed: refill it
+        TL_CIT(cur.phase, i, 3);
+        slot = slot + 1 == S ? 0 : slot + 1;
+        if (GROUPED) {
+          const int gi = ((warp + i * W) * 64) / group;
+          const float s_lo = tl_load_scale(scales, c.scales_dtype, r_lo * gpr + gi);
+          const float s_hi = tl_load_scale(scales, c.scales_dtype, r_hi * gpr + gi);
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            total[nt][0] = fmaf(s_lo, acc[nt][0], total[nt][0]);
+            total[nt][1] = fmaf(s_lo, acc[nt][1], total[nt][1]);
+            total[nt][2] = fmaf(s_hi, acc[nt][2], total[nt][2]);
+            total[nt][3] = fmaf(s_hi, acc[nt][3], total[nt][3]);
+          }
+        } else {
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) total[nt][e] = acc[nt][e];
+        }
+      }
+    }
+
+    // ---- the W warps' partial tiles meet in shared memory; scale, epilogue, store ----
+    TL_CTR(cur.phase, 2);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[((warp * NT + nt) * 4 + i) * 32 + lane] = total[nt][i];
+    __syncthreads();
+#pragma unroll
+    for (int u = 0; u < kOutPerThread; ++u) {
+      const int o = tid + u * kThreads;
+      if (o >= NT * 128) break;
+      const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < W; ++w) v += red[((w * NT + nt) * 4 + i) * 32 + ln];
+      const int gg = ln >> 2, tt = ln & 3;
+      const int64_t row = tile_row + gg + ((i & 2) ? 8 : 0);
+      const int col = 8 * nt + 2 * tt + (i & 1);
+      if (row < n && col < c.m) {
+        const float vs = v * (c.wscale * pre_scale[u]);
+        float r;
+        if (epi_fast) {
+          // [bias][unary] chain, evaluated in the op interpreter's order and rounding
+          r = __fmul_rn(vs, epi_alpha);
+          if (epi_bias) r = __fadd_rn(r, pre_bias[u]);
+          if (epi_unary) r = tl_unary(epi_unary, r);
+        } else {
+          r = tl_apply_epilogue(epi, vs, col, row, n);
+        }
+        tl_store_out(cur.out, cur.out_dtype, int64_t(col) * n + row, r);
+      }
+    }
+    __syncthreads();  // the stores above are done, and `red` may be overwritten
+    TL_CTR(cur.phase, 3);
+    // ---- leaving a phase = one arrival on its counter ----
+    if (cur.arrive && tid == 0) {
+      __threadfence();
+      TL_CTR(cur.phase, 4);
+      atomicAdd(c.bar + cur.phase, 1u);
+      TL_CTR(cur.phase, 5);
+    }
+    cur = nxt;
+    ++cj;
+  }
+  cp_async_wait<0>();  // nothing of ours may still be landing when the CTA leaves
+}
+
+}  // namespace
+
+struct tl_chain {
+  ChainTile* d_sched = nullptr;
+  EpiParams* d_epi = nullptr;
+  unsigned* d_bar = nullptr;
+  int32_t n_phases = 0, m = 0, a_dtype = 0, scales_dtype = 0, stride = 0;
+  float wscale = 1.f;
+  bool grouped = false;
+  int32_t n_items = 0, n_epi = 0;
+  int grid = 0, threads = 0, warps = 0, depth = 0;
+  size_t smem = 0;
+  const void* kernel = nullptr;
+};
+
+namespace {
+// CTA shapes of the chain kernel: warps per tile x prefetch depth (k blocks in flight per thread),
+// with the resident CTAs per SM the launch bounds ask for.
+template <typename AT, int NT, bool GROUPED, int W, int S, int MINB>
+void chain_set(tl_chain* ch) {
+  ch->kernel = reinterpret_cast<const void*>(&qgemv_chain_kernel<AT, NT, GROUPED, W, S, MINB>);
+  ch->threads = W * 32;
+  ch->smem = size_t(S) * 2 * (W * 32) * 16 + size_t(W) * NT * 128 * sizeof(float);
+}
+template <typename AT, int NT, bool GROUPED>
+bool chain_pick_shape(tl_chain* ch, int warps, int depth) {
+  if (warps == 8 && depth == 12) { chain_set<AT, NT, GROUPED, 8, 12, 2>(ch); return true; }
+  if (warps == 8 && depth == 8) { chain_set<AT, NT, GROUPED, 8, 8, 3>(ch); return true; }
+  if (warps == 4 && depth == 12) { chain_set<AT, NT, GROUPED, 4, 12, 6>(ch); return true; }
+  if (warps == 16 && depth == 12) { chain_set<AT, NT, GROUPED, 16, 12, 1>(ch); return true; }
+  return false;
+}
+template <typename AT>
+bool chain_pick_at(tl_chain* ch, int warps, int depth) {
+  if (ch->m > 8) return ch->grouped ? chain_pick_shape<AT, 2, true>(ch, warps, depth) : chain_pick_shape<AT, 2, false>(ch, warps, depth);
+  return ch->grouped ? chain_pick_shape<AT, 1, true>(ch, warps, depth) : chain_pick_shape<AT, 1, false>(ch, warps, depth);
+}
+}  // namespace
+
+extern "C" int32_t tl_qgemv_chain_destroy(tl_ctx* ctx, tl_chain* chain) {
+  TL_CHECK_CTX(ctx);
+  if (!chain) return TL_OK;
+  DeviceGuard guard(ctx->device);
+  cudaStreamSynchronize(ctx->stream);
+  if (chain->d_sched) cudaFree(chain->d_sched);
+  if (chain->d_epi) cudaFree(chain->d_epi);
+  if (chain->d_bar) cudaFree(chain->d_bar);
+  delete chain;
+  return TL_OK;
+}
+
+extern "C" int32_t tl_qgemv_chain_create(tl_ctx* ctx, const tl_chain_phase* phases, int32_t n_phases, int32_t a_dtype,
+                                         int32_t m, int32_t scales_dtype, int32_t scale_convention, tl_chain** out) {
+  TL_CHECK_CTX(ctx);
+  if (!out) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_chain_create: null output");
+  *out = nullptr;
+  if (!phases || n_phases < 1 || n_phases > 4096)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_chain_create: 1..4096 phases (got %d)", n_phases);
+  if (m < 1 || m > 16) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_chain_create: m=%d outside the GEMV range [1,16]", m);
+  if (a_dtype != TL_F16 && a_dtype != TL_BF16)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_chain_create: activations must be f16 or bf16");
+  DeviceGuard guard(ctx->device);
+  tl_chain* ch = new tl_chain();
+  ch->n_phases = n_phases; ch->m = m; ch->a_dtype = a_dtype; ch->scales_dtype = scales_dtype;
+  ch->wscale = scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+
+  // ---- validate, flatten the epilogues ----
+  std::vector<EpiParams> epis;
+  for (int p = 0; p < n_phases; ++p) {
+    const tl_chain_phase& src = phases[p];
+    if (src.n_items < 1 || src.n_items > kChainMaxItems || src.k < 64 || src.k % 64 != 0 || src.k > (int64_t(1) << 30) ||
+        src.group_size < 64 || src.group_size % 64 != 0 || src.k % src.group_size != 0 ||
+        (reinterpret_cast<uintptr_t>(src.a) & 15)) {
+      delete ch;
+      return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                          "tl_qgemv_chain_create: phase %d: needs 1..4 items, K %% 64 == 0, group %% 64 == 0 dividing K, "
+                          "16-byte aligned activations", p);
+    }
+    tl_quant_desc q{TL_SCHEME_INT8_GROUPED, src.group_size, scales_dtype, scale_convention};
+    if (src.group_size != src.k) ch->grouped = true;
+    for (int i = 0; i < src.n_items; ++i) {
+      const tl_qgemv_item& si = src.items[i];
+      int32_t rc = tl_check_qargs(ctx, "tl_qgemv_chain_create", src.a, a_dtype, si.packed, si.scales, si.out, src.out_dtype,
+                                  m, si.n, src.k, &q);
+      bool has_ops = false;
+      EpiParams e{};
+      if (rc == TL_OK) rc = tl_make_epi(ctx, si.epilogue, si.alpha, &e, &has_ops);
+      if (rc == TL_OK && (si.n < 1 || si.n > (int64_t(1) << 30) || (reinterpret_cast<uintptr_t>(si.packed) & 15) || si.out == src.a))
+        rc = tl_set_error(ctx, TL_ERR_INVALID_ARG,
+                          "tl_qgemv_chain_create: phase %d item %d: n >= 1, 16-byte aligned weights, out != a", p, i);
+      if (rc != TL_OK) { delete ch; return rc; }
+      epis.push_back(e);
+      ch->n_items++;
+      ch->n_epi += has_ops ? 1 : 0;
+    }
+  }
+
+  // ---- kernel shape and grid ----
+  // a forced variant {TL_FAMILY_QGEMV, kernel 7 "chain", warps, depth} overrides the default shape
+  ch->warps = 8; ch->depth = 12;
+  if (ctx->has_forced && ctx->forced.family == TL_FAMILY_QGEMV && ctx->forced.kernel == kChain) {
+    ch->warps = ctx->forced.p0; ch->depth = ctx->forced.p1;
+  }
+  if (!(a_dtype == TL_F16 ? chain_pick_at<__half>(ch, ch->warps, ch->depth) : chain_pick_at<__nv_bfloat16>(ch, ch->warps, ch->depth))) {
+    const int w = ch->warps, d = ch->depth;
+    delete ch;
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_chain_create: no chain kernel with %d warps x depth %d", w, d);
+  }
+  cudaError_t e = cudaFuncSetAttribute(ch->kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(ch->smem));
+  int per_sm = 0;
+  if (e == cudaSuccess) e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ch->kernel, ch->threads, ch->smem);
+  if (e != cudaSuccess || per_sm < 1) {
+    delete ch;
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_chain_create: occupancy query failed: %s", cudaGetErrorString(e));
+  }
+  ch->grid = ctx->sm_count * per_sm;  // all of them co-resident: the launch is cooperative
+  e = cudaMalloc(&ch->d_epi, epis.size() * sizeof(EpiParams));
+  if (e == cudaSuccess) e = cudaMemcpy(ch->d_epi, epis.data(), epis.size() * sizeof(EpiParams), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    tl_qgemv_chain_destroy(ctx, ch);
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_chain_create: %s", cudaGetErrorString(e));
+  }
+
+  // ---- the schedule: tiles of successive phases dealt round-robin, each phase starting at the
+  // CTA after the one the previous phase stopped at; one list of records per CTA ----
+  std::vector<std::vector<ChainTile>> lists;
+  lists.resize(size_t(ch->grid));
+  int64_t start = 0;
+  int64_t prev_tiles = 0;
+  size_t epi_index = 0;
+  for (int p = 0; p < n_phases; ++p) {
+    const tl_chain_phase& src = phases[p];
+    const int32_t wait_for = p == 0 ? 0 : int32_t(std::min<int64_t>(ch->grid, prev_tiles));
+    std::vector<size_t> first_of_cta(size_t(ch->grid), size_t(-1));
+    int64_t t = 0;
+    for (int i = 0; i < src.n_items; ++i, ++epi_index) {
+      const tl_qgemv_item& si = src.items[i];
+      for (int64_t row = 0; row < si.n; row += 16, ++t) {
+        const size_t cta = size_t((start + t) % ch->grid);
+        ChainTile rec{};
+        rec.w = reinterpret_cast<const uint8_t*>(si.packed) + row * src.k;
+        rec.a = src.a; rec.scales = si.scales; rec.out = si.out; rec.epi = ch->d_epi + epi_index;
+        rec.k = int32_t(src.k); rec.n = int32_t(si.n); rec.tile_row = int32_t(row); rec.phase = p;
+        rec.group = src.group_size; rec.out_dtype = src.out_dtype;
+        rec.wait_for = 0; rec.arrive = 0;
+        auto& list = lists[cta];
+        if (first_of_cta[cta] == size_t(-1)) {
+          first_of_cta[cta] = list.size();
+          rec.wait_for = wait_for;
+        }
+        list.push_back(rec);
+      }
+    }
+    for (size_t cta = 0; cta < lists.size(); ++cta)
+      if (first_of_cta[cta] != size_t(-1)) lists[cta].back().arrive = 1;  // its last tile of this phase
+    start += t;
+    prev_tiles = t;
+  }
+  size_t longest = 0;
+  for (const auto& l : lists) longest = std::max(longest, l.size());
+  ch->stride = int32_t(longest + 2);  // the list ends with an all-zero record, and the walk reads one past it
+  std::vector<ChainTile> flat;
+  flat.resize(lists.size() * size_t(ch->stride));
+  for (size_t cta = 0; cta < lists.size(); ++cta)
+    std::copy(lists[cta].begin(), lists[cta].end(), flat.begin() + cta * size_t(ch->stride));
+  e = cudaMalloc(&ch->d_sched, flat.size() * sizeof(ChainTile));
+  if (e == cudaSuccess) e = cudaMalloc(&ch->d_bar, size_t(n_phases + 1) * sizeof(unsigned));
+  if (e == cudaSuccess) e = cudaMemcpy(ch->d_sched, flat.data(), flat.size() * sizeof(ChainTile), cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) {
+    tl_qgemv_chain_destroy(ctx, ch);
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_chain_create: %s", cudaGetErrorString(e));
+  }
+  *out = ch;
+  return TL_OK;
+}
+
+extern "C" int32_t tl_qgemv_chain_launch(tl_ctx* ctx, tl_chain* chain) {
+  TL_CHECK_CTX(ctx);
+  if (!chain) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_chain_launch: null chain");
+  DeviceGuard guard(ctx->device);
+  TL_CUDA(ctx, cudaMemsetAsync(chain->d_bar, 0, size_t(chain->n_phases + 1) * sizeof(unsigned), ctx->stream));
+  ChainArgs args{};
+  args.sched = chain->d_sched; args.bar = chain->d_bar; args.status = ctx->dev_status;
+  args.stride = chain->stride; args.n_phases = chain->n_phases; args.m = chain->m;
+  args.scales_dtype = chain->scales_dtype; args.wscale = chain->wscale;
+  void* kargs[] = {&args};
+  cudaError_t e = cudaLaunchCooperativeKernel(chain->kernel, dim3(unsigned(chain->grid)), dim3(unsigned(chain->threads)), kargs,
+                                              chain->smem, ctx->stream);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_chain_launch: %s", cudaGetErrorString(e));
+  }
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  ctx->counters[TL_COUNTER_QGEMV] += chain->n_items;
+  ctx->counters[TL_COUNTER_QGEMV_EPILOGUE] += chain->n_epi;
+  return TL_OK;
+}
+
+#ifdef TL_TRACE
+extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_trace(void* dst, size_t bytes) {
+  return cudaMemcpyFromSymbol(dst, g_chain_trace, bytes) == cudaSuccess ? 0 : -1;
+}
+extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_iter(void* dst, size_t bytes) {
+  return cudaMemcpyFromSymbol(dst, g_chain_iter, bytes) == cudaSuccess ? 0 : -1;
+}
+#endif

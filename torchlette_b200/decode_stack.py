@@ -77,8 +77,13 @@ class _Proj:
 
 class DecodeStack:
     def __init__(self, be: CudaBackend, cfg: StackConfig, rank: int = 0, world: int = 1, tp_mode: str = "chained",
-                 seed: int = 0, allreduce: str = "nccl", fuse: bool = True):
+                 seed: int = 0, allreduce: str = "nccl", fuse: bool = True, chain: bool = False):
         assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p")
+        # chain: the whole step as ONE persistent cooperative launch (tl_qgemv_chain_*); single rank,
+        # batch <= 16 only -- elsewhere the step stays a graph of per-projection launches
+        self.chain_requested = chain
+        self._chain = None
+        self._chain_keep = []
         self.be, self.cfg, self.rank, self.world, self.tp_mode = be, cfg, rank, world, tp_mode
         self.fuse = fuse  # q/k/v and gate/up as one launch each
         self.allreduce = allreduce  # "p2p": the library's one-shot peer-memory all-reduce (peers must be attached)
@@ -177,8 +182,50 @@ class DecodeStack:
         B.check(self.ctx, self.lib.tl_copy2d(self.ctx, out.data_ptr(), w * esz, full.data_ptr() + self.rank * w * esz,
                                              full.shape[1] * esz, w * esz, out.shape[0]))
 
+    # -- the whole step as one persistent launch --------------------------------
+    def _phase(self, x: torch.Tensor, projs, outs) -> "B.ChainPhase":
+        ph = B.ChainPhase()
+        ph.a, ph.k, ph.group_size = x.data_ptr(), projs[0].k, projs[0].k
+        ph.out_dtype, ph.n_items = B.DTYPE_ID[projs[0].out_dtype], len(projs)
+        for i, (p, o) in enumerate(zip(projs, outs)):
+            e = None
+            if p.act:
+                e = B.Epilogue()
+                e.n_ops = 1
+                e.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY[p.act], 0, 0)
+                self._chain_keep.append(e)
+            ph.items[i] = B.QGemvItem(p.w.data_ptr(), p.s.data_ptr(), o.data_ptr(), p.n, p.alpha,
+                                      C.pointer(e) if e is not None else None)
+        return ph
+
+    def uses_chain(self) -> bool:
+        return self.chain_requested and self.world == 1 and self.cfg.batch <= 16
+
+    def build_chain(self):
+        """Describe the step to the library once: 4 phases per layer (q+k+v, o, gate+up, down) + lm_head."""
+        phases = []
+        x = self.x
+        for pq, pk, pv, po, pg, pu, pd in self.layers:
+            phases.append(self._phase(x, (pq, pk, pv), (self.q, self.kk, self.v)))
+            phases.append(self._phase(self.q, (po,), (self.h1,)))
+            phases.append(self._phase(self.h1, (pg, pu), (self.g, self.u)))
+            phases.append(self._phase(self.g, (pd,), (self.h2,)))
+            x = self.h2
+        phases.append(self._phase(x, (self.lm_head,), (self.logits_local,)))
+        arr = (B.ChainPhase * len(phases))(*phases)
+        handle = C.c_void_p()
+        B.check(self.ctx, self.lib.tl_qgemv_chain_create(self.ctx, arr, len(phases), self.adt, self.cfg.batch,
+                                                         B.TL_F32, B.TL_SCALE_DIRECT, C.byref(handle)))
+        self._chain = handle
+        return handle
+
     def enqueue_step(self):
         """Enqueue one pass over the whole stack on the library's stream."""
+        if self.uses_chain():
+            if self._chain is None:
+                self.build_chain()
+            B.check(self.ctx, self.lib.tl_qgemv_chain_launch(self.ctx, self._chain))
+            return
         x = self.x
         gather = self.tp_mode == "gather" and self.world > 1
         for projs in self.layers:
@@ -209,6 +256,8 @@ class DecodeStack:
         as a replayable graph — the analogue of the reference's compiled plans."""
         self.enqueue_step()
         self.be.sync()
+        if self.uses_chain():
+            return None  # already a single launch: nothing for a graph to save
         self.be.beginCapture()
         try:
             self.enqueue_step()
@@ -223,10 +272,15 @@ class DecodeStack:
             self.enqueue_step()
 
     def launches_per_step(self) -> int:
+        if self.uses_chain():
+            return 1
         fused = self.fuse and self.cfg.batch <= 16
         return (4 if fused else 7) * self.cfg.layers + 1
 
     def destroy(self):
+        if self._chain is not None:
+            self.lib.tl_qgemv_chain_destroy(self.ctx, self._chain)
+            self._chain = None
         if self.graph is not None:
             self.be.destroyGraph(self.graph)
             self.graph = None
