@@ -479,6 +479,14 @@ static TuneKey make_key(int64_t m, int64_t n, int64_t k, int32_t a_dtype, const 
   return TuneKey{m, n, k, a_dtype, q.group_size, q.scales_dtype, q.scale_convention};
 }
 
+// The tuned winner recorded for a shape, if any (the batched launch keys on the summed N).
+bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, tl_variant* v) {
+  auto it = ctx->tuned.find(make_key(m, n, k, a_dtype, q));
+  if (it == ctx->tuned.end()) return false;
+  *v = it->second;
+  return true;
+}
+
 // Order of precedence follows selectMatmulChoice
 // (src/backend/webgpu/matmul/dispatch.ts:171-192): explicit (forced) variant ->
 // per-shape tuned winner (re-gated on applicability) -> heuristic default.

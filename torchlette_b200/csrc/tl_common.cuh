@@ -56,6 +56,7 @@ struct tl_ctx {
   bool autotune_enabled = false;
   int64_t tune_runs = 0;
   std::map<TuneKey, tl_variant> tuned;
+  std::map<int, int> ring_occupancy;  // resident CTAs per SM of each ring kernel shape (queried once)
   bool capturing = false;
   // multi-GPU
   void* nccl_comm = nullptr;
@@ -125,6 +126,8 @@ struct EpiParams {
 // Validates an epilogue description and flattens it; returns TL_OK or an error
 // (with the message set on ctx).
 int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* out, bool* has_ops);
+
+bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, tl_variant* v);
 
 // Common argument validation of the quantized entry points.
 int32_t tl_check_qargs(tl_ctx* ctx, const char* who, const void* a, int32_t a_dtype,

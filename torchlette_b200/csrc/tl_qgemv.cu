@@ -79,7 +79,27 @@ struct GemvArgs {
   float wscale;    // 1/127 for the snorm convention, 1 for direct
   int32_t row0;    // first batch row of this launch (epilogue binary inputs index absolute rows)
   int32_t m_total;
+#ifdef TL_TRACE
+  int32_t trace_id;  // launch number, for the device-side timeline of traced builds
+#endif
 };
+
+#ifdef TL_TRACE
+// per launch: min/max CTA start, min/max time the dependency wait was passed, min/max CTA end,
+// max time the first weight block had landed
+__device__ unsigned long long g_ring_trace[512][8];
+__device__ __forceinline__ unsigned long long ring_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define TL_RT_MIN(id, ev) do { if (threadIdx.x == 0 && (id) < 512) atomicMin(&g_ring_trace[id][ev], ring_now()); } while (0)
+#define TL_RT_MAX(id, ev) do { if (threadIdx.x == 0 && (id) < 512) atomicMax(&g_ring_trace[id][ev], ring_now()); } while (0)
+int g_ring_trace_next = 0;
+#else
+#define TL_RT_MIN(id, ev) do {} while (0)
+#define TL_RT_MAX(id, ev) do {} while (0)
+#endif
 
 // ---------------------------------------------------------------------------
 // 0: scalar fallback.  One warp per output row; lane l walks words l, l+32, ...
@@ -638,6 +658,11 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
   const uint32_t slot_bytes = uint32_t(nthreads) * 16u;  // one [blockDim] row of 16-byte words
 
+#ifdef TL_TRACE
+  const int trace_id = p.trace_id;
+#endif
+  TL_RT_MIN(trace_id, 0);
+  TL_RT_MAX(trace_id, 1);
   // let the next kernel in the stream start its own weight prefetch as early as possible
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
@@ -650,6 +675,8 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   }
   // weights never depend on the previous kernel; activations (its output) and our own stores do
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  TL_RT_MIN(trace_id, 2);
+  TL_RT_MAX(trace_id, 3);
 
   float total[NT][4];
 #pragma unroll
@@ -720,6 +747,7 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
     }
   }
   cp_async_wait<0>();
+  TL_RT_MAX(trace_id, 6);
 
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -740,6 +768,8 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
     }
   }
+  TL_RT_MIN(trace_id, 4);
+  TL_RT_MAX(trace_id, 5);
 }
 
 // ---------------------------------------------------------------------------
@@ -1229,6 +1259,79 @@ void launch_ring(bool two, bool grouped, int depth, int grid, int block, cudaStr
   }
 }
 
+// ---------------------------------------------------------------------------
+// Shape of a ring launch: W warps per 16-row tile, S k blocks in flight per thread.
+// A launch whose CTAs are all resident at once has no tail wave, and a tail wave of a few
+// CTAs runs at one thread's latency-bound pace: on the decode stack the gate+up launch
+// (1536 tiles) took 27 us with 10 resident CTAs per SM (44 registers, 56 CTAs left over) and
+// 19 us with 12 (40 registers).  So: the widest CTA (shortest k loop per warp) whose launch
+// fits in one wave, and for it the deepest ring that still fits -- asked of the occupancy
+// calculator, which knows the registers of each instantiation.  Matrices too large for one
+// wave take 4-warp CTAs with the ring sized by shared memory.
+// ---------------------------------------------------------------------------
+template <typename AT, int NT, bool GROUPED>
+const void* ring_kernel_ptr_d(bool batched, int depth) {
+  switch (depth) {
+    case 8: return batched ? reinterpret_cast<const void*>(&qgemv_ring_batched_kernel<AT, NT, GROUPED, 8>)
+                           : reinterpret_cast<const void*>(&qgemv_ring_kernel<AT, NT, GROUPED, 8>);
+    case 6: return batched ? reinterpret_cast<const void*>(&qgemv_ring_batched_kernel<AT, NT, GROUPED, 6>)
+                           : reinterpret_cast<const void*>(&qgemv_ring_kernel<AT, NT, GROUPED, 6>);
+    case 4: return batched ? reinterpret_cast<const void*>(&qgemv_ring_batched_kernel<AT, NT, GROUPED, 4>)
+                           : reinterpret_cast<const void*>(&qgemv_ring_kernel<AT, NT, GROUPED, 4>);
+    default: return batched ? reinterpret_cast<const void*>(&qgemv_ring_batched_kernel<AT, NT, GROUPED, 2>)
+                            : reinterpret_cast<const void*>(&qgemv_ring_kernel<AT, NT, GROUPED, 2>);
+  }
+}
+template <typename AT>
+const void* ring_kernel_ptr_at(bool batched, bool two, bool grouped, int depth) {
+  if (two) return grouped ? ring_kernel_ptr_d<AT, 2, true>(batched, depth) : ring_kernel_ptr_d<AT, 2, false>(batched, depth);
+  return grouped ? ring_kernel_ptr_d<AT, 1, true>(batched, depth) : ring_kernel_ptr_d<AT, 1, false>(batched, depth);
+}
+inline size_t ring_smem_bytes(int warps, int depth, bool two) {
+  return size_t(depth) * 2 * warps * 32 * 16 + size_t(warps) * (two ? 2 : 1) * 128 * 4;
+}
+int ring_occupancy(tl_ctx* ctx, bool batched, int a_dtype, bool two, bool grouped, int warps, int depth) {
+  const int key = (batched ? 1 : 0) | (a_dtype == TL_F16 ? 2 : 0) | (two ? 4 : 0) | (grouped ? 8 : 0) | (warps << 4) | (depth << 10);
+  auto it = ctx->ring_occupancy.find(key);
+  if (it != ctx->ring_occupancy.end()) return it->second;
+  const void* kern = a_dtype == TL_F16 ? ring_kernel_ptr_at<__half>(batched, two, grouped, depth)
+                                       : ring_kernel_ptr_at<__nv_bfloat16>(batched, two, grouped, depth);
+  const size_t smem = ring_smem_bytes(warps, depth, two);
+  int occ = 0;
+  if (smem <= 227 * 1024) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, warps * 32, smem) != cudaSuccess) {
+      cudaGetLastError();
+      occ = 0;
+    }
+  }
+  ctx->ring_occupancy[key] = occ;
+  return occ;
+}
+void ring_pick_shape(tl_ctx* ctx, bool batched, int a_dtype, int m, bool grouped, int64_t tiles, int64_t k, int* warps,
+                     int* depth) {
+  const bool two = m > 8;
+  const int kblocks = int(k >> 6);
+  for (int w : {16, 8, 4}) {
+    const int nkb = (kblocks + w - 1) / w;  // k blocks of one warp
+    for (int s : {8, 6, 4, 2}) {
+      if (s > 2 && s - 2 >= nkb) continue;  // a shallower ring already holds all of them
+      const int occ = ring_occupancy(ctx, batched, a_dtype, two, grouped, w, s);
+      if (int64_t(occ) * ctx->sm_count >= tiles) { *warps = w; *depth = s; return; }
+    }
+  }
+  // several waves: 4-warp CTAs; the deepest ring whose shared memory still lets
+  // ceil(tiles / SMs) CTAs (at most 8) live on one SM
+  const int64_t per_sm = std::min<int64_t>(8, (tiles + ctx->sm_count - 1) / ctx->sm_count);
+  int d = 2;
+  for (int cand : {4, 6, 8})
+    if (per_sm * (int64_t(cand) * 4096 + 2048 + 1024) <= 224 * 1024) d = cand;
+  // two token tiles (m > 8) double the accumulators: the registers then cap the resident
+  // CTAs, and rings deeper than 4 measured 1.5x slower
+  if (two) d = std::min(d, 4);
+  *warps = 4; *depth = d;
+}
+
 template <typename AT, bool M16, bool GROUPED>
 void launch_sk_d(int depth, int grid, cudaStream_t s, const GemvArgs& p, const EpiParams& e, const SkArgs& sk) {
   if (depth >= 4) qgemv_sk_kernel<AT, M16, GROUPED, 4><<<grid, 256, 0, s>>>(p, e, sk);
@@ -1314,23 +1417,11 @@ int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, i
   tl_variant v{};
   v.family = TL_FAMILY_QGEMV;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
-    // few tiles: spread each tile's k range over many warps so everything is in flight at once
     const int64_t tiles = (n + 15) / 16;
     v.kernel = kRing;
-    if (tiles >= int64_t(ctx->sm_count) * 4) {
-      // 4-warp CTAs, all co-resident when they fit: the deepest prefetch ring whose shared memory
-      // still lets ceil(tiles / SMs) CTAs (at most 8, the register limit) live on one SM, so the
-      // bytes in flight per SM do not depend on how many tiles the matrix happens to have
-      const int64_t per_sm = std::min<int64_t>(8, (tiles + ctx->sm_count - 1) / ctx->sm_count);
-      int depth = 2;
-      for (int cand : {4, 6, 8})
-        if (per_sm * (int64_t(cand) * 4096 + 2048 + 1024) <= 224 * 1024) depth = cand;
-      // two token tiles (m > 8) double the accumulators: the registers then cap the resident
-      // CTAs, and rings deeper than 4 measured 1.5x slower
-      if (m > 8) depth = std::min(depth, 4);
-      v.p0 = 4; v.p1 = depth;
-    } else if (m > 8) { v.p0 = 8; v.p1 = 4; }
-    else { v.p0 = 16; v.p1 = 4; }
+    int w = 4, d = 2;
+    ring_pick_shape(ctx, false, a_dtype, m, q.group_size != k, tiles, k, &w, &d);
+    v.p0 = w; v.p1 = d;
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -1382,6 +1473,9 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   p.scales_dtype = q.scales_dtype; p.out_dtype = out_dtype;
   p.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
   p.row0 = 0; p.m_total = m;
+#ifdef TL_TRACE
+  p.trace_id = g_ring_trace_next++;
+#endif
   const bool grouped = q.group_size != k;
   int block = v.p0 * 32;
   int grid = 0, launches = 1;
@@ -1627,6 +1721,9 @@ extern "C" int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_
   p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
   p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
   p.row0 = 0; p.m_total = m;
+#ifdef TL_TRACE
+  p.trace_id = g_ring_trace_next++;
+#endif
   TmaArgs ta{};
   ta.scratch = reinterpret_cast<float*>(base);
   ta.counters = reinterpret_cast<unsigned*>(base + sbytes);
@@ -1673,7 +1770,9 @@ void launch_ring_batched(int grid, int block, cudaStream_t s, const RingBatchArg
 }
 template <typename AT, int NT, bool GROUPED>
 void launch_ring_batched_s(int depth, int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
-  if (depth >= 4) launch_ring_batched<AT, NT, GROUPED, 4>(grid, block, s, b);
+  if (depth >= 8) launch_ring_batched<AT, NT, GROUPED, 8>(grid, block, s, b);
+  else if (depth >= 6) launch_ring_batched<AT, NT, GROUPED, 6>(grid, block, s, b);
+  else if (depth >= 4) launch_ring_batched<AT, NT, GROUPED, 4>(grid, block, s, b);
   else launch_ring_batched<AT, NT, GROUPED, 2>(grid, block, s, b);
 }
 template <typename AT>
@@ -1724,15 +1823,36 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
     p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
     p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
     p.row0 = 0; p.m_total = m;
+#ifdef TL_TRACE
+    p.trace_id = g_ring_trace_next;
+#endif
+#ifdef TL_TRACE
+  p.trace_id = g_ring_trace_next++;
+#endif
     tiles += (items[i].n + 15) / 16;
   }
   b.tile_start[kMaxBatchItems] = int32_t(tiles);
+#ifdef TL_TRACE
+  g_ring_trace_next++;
+#endif
   for (int i = n_items; i < kMaxBatchItems; ++i) b.tile_start[i] = int32_t(tiles);  // unused items are empty ranges
-  // same shape rule as the single-matrix default: few tiles -> many warps per tile
-  const int warps = tiles >= int64_t(ctx->sm_count) * 4 ? 4 : 16, depth = warps == 4 ? 4 : 2;
+  // the single-matrix shape rule (one wave if possible); a forced or tuned ring variant (keyed on
+  // the summed N) overrides it
+  int64_t n_total = 0;
+  for (int i = 0; i < n_items; ++i) n_total += items[i].n;
+  DeviceGuard guard(ctx->device);
+  int warps = 4, depth = 2;
+  ring_pick_shape(ctx, true, a_dtype, m, qdesc->group_size != k, tiles, k, &warps, &depth);
+  tl_variant tv{};
+  if (ctx->has_forced && ctx->forced.family == TL_FAMILY_QGEMV && ctx->forced.kernel == kRing) {
+    warps = ctx->forced.p0; depth = ctx->forced.p1;
+  } else if (tl_lookup_tuned(ctx, m, n_total, k, a_dtype, *qdesc, &tv) && tv.family == TL_FAMILY_QGEMV && tv.kernel == kRing) {
+    warps = tv.p0; depth = tv.p1;
+  }
+  if (warps != 2 && warps != 4 && warps != 8 && warps != 16)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_batched: ring variant with %d warps", warps);
   const int block = warps * 32, grid = int(tiles);
   const bool grouped = qdesc->group_size != k;
-  DeviceGuard guard(ctx->device);
   if (a_dtype == TL_F16) launch_ring_batched_at<__half>(m > 8, grouped, depth, grid, block, ctx->stream, b);
   else launch_ring_batched_at<__nv_bfloat16>(m > 8, grouped, depth, grid, block, ctx->stream, b);
   TL_CUDA(ctx, cudaGetLastError());
@@ -2324,6 +2444,16 @@ extern "C" int32_t tl_qgemv_chain_launch(tl_ctx* ctx, tl_chain* chain) {
 #ifdef TL_TRACE
 extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_trace(void* dst, size_t bytes) {
   return cudaMemcpyFromSymbol(dst, g_chain_trace, bytes) == cudaSuccess ? 0 : -1;
+}
+extern "C" __attribute__((visibility("default"))) int32_t tl_debug_ring_trace(void* dst, size_t bytes, int32_t reset) {
+  if (reset) {
+    std::vector<unsigned long long> init(512 * 8);
+    for (int i = 0; i < 512; ++i)
+      for (int e = 0; e < 8; ++e) init[size_t(i) * 8 + e] = (e == 0 || e == 2 || e == 4) ? ~0ull : 0ull;
+    if (reset == 1) g_ring_trace_next = 0;
+    return cudaMemcpyToSymbol(g_ring_trace, init.data(), init.size() * 8) == cudaSuccess ? 0 : -1;
+  }
+  return cudaMemcpyFromSymbol(dst, g_ring_trace, bytes) == cudaSuccess ? 0 : -1;
 }
 extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_iter(void* dst, size_t bytes) {
   return cudaMemcpyFromSymbol(dst, g_chain_iter, bytes) == cudaSuccess ? 0 : -1;
