@@ -633,3 +633,22 @@ def test_grouped_scales_on_every_fast_variant(backend, variant, group):
         be.forceVariant(None)
     for t in (xt, wt.scales, wt):
         t.destroy()
+
+
+def test_ring_launch_shape_fits_one_wave_when_it_can(backend):
+    """The default ring shape comes from the occupancy calculator: if any of the 16-, 8- or
+    4-warp shapes lets the whole launch be resident at once, the launch is a single wave
+    (grid <= resident CTAs), and few-tile matrices get the widest CTA."""
+    be = backend
+    sms = be.smCount()
+    for (n, k) in [(4096, 4096), (4096, 12288), (6144, 4096), (14336, 4096), (1024, 4096)]:
+        plan = be.planQuantizedMatmul(8, n, k, "f16", "f16", tb.perChannelFormat(k).packing)
+        assert ".ring" in plan["variant"]
+        warps, depth = plan["choice"][2], plan["choice"][3]
+        assert warps in (4, 8, 16) and depth in (2, 4, 6, 8)
+        assert plan["grid"][0] == (n + 15) // 16 and plan["block"] == warps * 32
+        # one wave: at most 2048 threads and 64K registers per SM bound the resident CTAs
+        assert plan["grid"][0] <= sms * (2048 // plan["block"])
+    assert be.planQuantizedMatmul(8, 1024, 4096, "f16", "f16", tb.perChannelFormat(4096).packing)["choice"][2] == 16
+    # far more tiles than one wave holds: 4-warp CTAs
+    assert be.planQuantizedMatmul(8, 151936, 4096, "f16", "f16", tb.perChannelFormat(4096).packing)["choice"][2] == 4
