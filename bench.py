@@ -300,17 +300,36 @@ def run_gpu(args):
         idbuf = (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])
         B.check(ctx, lib.tl_comm_init(ctx, rank, world, idbuf))
         if args.allreduce == "p2p":
-            # exchange buffers for the one-shot peer all-reduce: [batch, hidden] partial sums
-            hbuf = (C.c_char * 64)()
-            B.check(ctx, lib.tl_p2p_create(ctx, args.batch * 4096 * 4, hbuf))
+            # exchange buffers for the one-shot peer all-reduce: [batch, hidden] partial sums.
+            # If any rank cannot map its peers (no peer access between some pair of GPUs), every
+            # rank switches to the NCCL all-reduce and the JSON line says so.
+            ok = 1
+            try:
+                hbuf = (C.c_char * 64)()
+                B.check(ctx, lib.tl_p2p_create(ctx, args.batch * 4096 * 4, hbuf))
+                mine = bytes(hbuf)
+            except tb.TlError as ex:
+                ok, mine = 0, bytes(64)
+                sys.stderr.write(f"rank {rank}: peer all-reduce unavailable ({ex})\n")
             handles = [None] * world
-            dist.all_gather_object(handles, bytes(hbuf))
-            allh = (C.c_char * (64 * world)).from_buffer_copy(b"".join(handles))
-            B.check(ctx, lib.tl_p2p_attach(ctx, allh))
+            dist.all_gather_object(handles, (ok, mine))
+            if all(h[0] for h in handles):
+                try:
+                    allh = (C.c_char * (64 * world)).from_buffer_copy(b"".join(h[1] for h in handles))
+                    B.check(ctx, lib.tl_p2p_attach(ctx, allh))
+                except tb.TlError as ex:
+                    ok = 0
+                    sys.stderr.write(f"rank {rank}: peer all-reduce unavailable ({ex})\n")
+            else:
+                ok = 0
+            flags = [None] * world
+            dist.all_gather_object(flags, ok)
+            if not all(flags):
+                args.allreduce = "nccl (peer buffers could not be mapped)"
             dist.barrier()
 
     cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
-    stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if world > 1 else "nccl",
+    stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce="p2p" if (world > 1 and args.allreduce == "p2p") else "nccl",
                         fuse=not args.no_fuse, chain=args.step_launch == "chain")
     chained = stack.uses_chain()
     if args.autotune:
