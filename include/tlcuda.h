@@ -347,6 +347,21 @@ TL_API int32_t tl_p2p_create(tl_ctx* ctx, size_t max_bytes, void* out_handle64);
 TL_API int32_t tl_p2p_attach(tl_ctx* ctx, const void* handles_world_x64);
 TL_API int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype);
 
+/* Row-parallel projection fused with its all-reduce (tensor parallelism; no counterpart in
+ * the reference): out[m, n] = sum over ranks of alpha * a_r[m, k_r] . W_r[n, k_r]^T in ONE
+ * kernel.  Every CTA computes a 16-row tile of the local partial product, stores it --
+ * rounded to out_dtype, exactly what tl_qgemv_nt would have written -- into all ranks'
+ * exchange buffers over NVLink, waits (bounded) for the other ranks' versions of the same
+ * tile and writes their sum in rank order, so the result has the bits of tl_qgemv_nt
+ * followed by tl_allreduce_sum_p2p.  Needs tl_p2p_create / tl_p2p_attach with max_bytes >=
+ * m*n*sizeof(out element); m in [1,16]; f16/bf16 activations; K % 64 == 0; n <= 16384 and
+ * the same n for every fused call on a context; no epilogue ops (alpha only: anything
+ * non-linear would have to follow the sum).  Collective: every rank must call it in the same
+ * order.  With one rank it is tl_qgemv_nt. */
+TL_API int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                                     const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n,
+                                     int64_t k, const tl_quant_desc* qdesc, float alpha);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,6 +1,7 @@
 """Two-GPU tests of the collectives (skipped on a single-GPU box): the one-shot
 peer-memory all-reduce against a locally computed sum, eager and replayed from a
-captured graph, and bit-identical across ranks; NCCL all-gather / all-reduce wrappers.
+captured graph, and bit-identical across ranks; the row-parallel GEMV fused with its
+all-reduce against the unfused pair (bit for bit); NCCL all-gather / all-reduce wrappers.
 Ranks are child processes (one per GPU); rendezvous over gloo on 127.0.0.1."""
 import ctypes as C
 import os
@@ -91,6 +92,58 @@ def _rank_main(rank, world, port, q):
             eb = sum(_data(r, 600 + rep, count, "f32") for r in range(world))
             assert np.allclose(be.ops.read(a), ea, atol=1e-6) and np.allclose(be.ops.read(b), eb, atol=1e-6)
         be.destroyGraph(g)
+        # fused row-parallel GEMV + all-reduce: same bits as tl_qgemv_nt followed by the peer all-reduce
+        m, n, kfull = 5, 300, 256 * world
+        rng = np.random.default_rng(77)
+        qw = rng.integers(-127, 128, size=(n, kfull), dtype=np.int8)
+        sc = rng.uniform(0.001, 0.01, size=(n, 1)).astype(np.float32)
+        kr = kfull // world
+        wq = np.ascontiguousarray(qw[:, rank * kr:(rank + 1) * kr])
+        fmt = tb.perChannelFormat(kr)
+        wt = be.createQuantizedWeight(wq.view(np.uint32).reshape(n, kr // 4), sc, n, kr, fmt)
+        qd = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, kr, B.TL_F32, B.TL_SCALE_DIRECT)
+        y_unfused, y_fused = be.ops.empty([m, n], "f16"), be.ops.empty([m, n], "f16")
+        xt = be.ops.empty([m, kr], "f16")
+        alpha = 0.37
+
+        def fused_inputs(rep):
+            xf = np.random.default_rng(900 + rep).standard_normal((m, kfull)).astype(np.float16)
+            be._upload(xt.buffer, np.ascontiguousarray(xf[:, rank * kr:(rank + 1) * kr]))
+            return xf
+
+        def run_unfused():
+            be.forceVariant((1, 4, 16, 4, 0, 0))  # the fused kernel's tile shape: same summation order
+            try:
+                B.check(ctx, lib.tl_qgemv_nt(ctx, xt.buffer, B.TL_F16, wt.buffer, wt.scales.buffer, y_unfused.buffer, B.TL_F16,
+                                             m, n, kr, C.byref(qd), alpha, None))
+            finally:
+                be.forceVariant(None)
+            B.check(ctx, lib.tl_allreduce_sum_p2p(ctx, y_unfused.buffer, y_unfused.buffer, m * n, B.TL_F16))
+
+        def run_fused():
+            B.check(ctx, lib.tl_qgemv_nt_allreduce(ctx, xt.buffer, B.TL_F16, wt.buffer, wt.scales.buffer, y_fused.buffer,
+                                                   B.TL_F16, m, n, kr, C.byref(qd), alpha))
+
+        for rep in range(3):  # successive calls alternate the halves of the exchange buffer
+            xf = fused_inputs(rep)
+            run_unfused()
+            run_fused()
+            got_u, got_f = be.ops.read(y_unfused).copy(), be.ops.read(y_fused).copy()
+            assert np.array_equal(got_u.view(np.uint16), got_f.view(np.uint16)), rep
+            ref = alpha * (xf.astype(np.float32) @ (qw.astype(np.float32) * sc).T)
+            assert np.allclose(got_f.astype(np.float32).reshape(m, n), ref, rtol=2e-2, atol=2e-2), rep
+            results[1000 + rep] = got_f.tobytes()
+        be.beginCapture()
+        run_fused()
+        gf = be.endCapture()
+        for rep in range(3, 6):
+            xf = fused_inputs(rep)
+            be.replay(gf)
+            ref = alpha * (xf.astype(np.float32) @ (qw.astype(np.float32) * sc).T)
+            got_f = be.ops.read(y_fused).copy()
+            assert np.allclose(got_f.astype(np.float32).reshape(m, n), ref, rtol=2e-2, atol=2e-2), rep
+            results[1000 + rep] = got_f.tobytes()
+        be.destroyGraph(gf)
         # column gather
         m, nl = 3, 40
         loc = be.ops.tensorFromArray(np.full((m, nl), rank + 1, np.float32), [m, nl], "f32")

@@ -98,6 +98,7 @@ SIGNATURES = {
     "tl_qgemv_nt": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemv_nt_static_scratch": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qgemv_nt_batched": (_I32, [_P, _P, _I32, C.POINTER(QGemvItem), _I32, _I32, _I32, _I64, C.POINTER(QuantDesc)]),
+    "tl_qgemv_nt_allreduce": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F]),
     "tl_qgemv_chain_create": (_I32, [_P, C.POINTER(ChainPhase), _I32, _I32, _I32, _I32, _I32, C.POINTER(C.c_void_p)]),
     "tl_qgemv_chain_launch": (_I32, [_P, _P]),
     "tl_qgemv_chain_destroy": (_I32, [_P, _P]),

@@ -305,9 +305,8 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(P2PArgs a) {
   }
 }
 
-size_t p2p_total_bytes(size_t max_bytes) {
-  return 2 * size_t(tl_ctx::kMaxPeers) * max_bytes + sizeof(uint32_t) * (2 * tl_ctx::kMaxPeers * kP2PCtas + kP2PCtas);
-}
+static_assert(kP2PCtas == 8, "tl_p2p_fused_offset assumes 8 CTAs' worth of flags and epochs");
+size_t p2p_total_bytes(size_t max_bytes) { return tl_p2p_total_bytes(max_bytes); }
 }  // namespace
 
 extern "C" {

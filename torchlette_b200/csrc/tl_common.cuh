@@ -67,6 +67,7 @@ struct tl_ctx {
   void* p2p_peer[kMaxPeers] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
   size_t p2p_max_bytes = 0;
   bool p2p_attached = false;
+  int64_t fused_tiles = 0;  // tiles of the fused GEMV + all-reduce calls made on this context (0: none yet)
 };
 
 int32_t tl_set_error(tl_ctx* ctx, int32_t code, const char* fmt, ...);
@@ -126,6 +127,29 @@ struct EpiParams {
 // Validates an epilogue description and flattens it; returns TL_OK or an error
 // (with the message set on ctx).
 int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* out, bool* has_ops);
+
+// Layout of a rank's peer-exchange buffer (tl_p2p_create): slots [2 halves][kMaxPeers][max_bytes],
+// then the flags and per-CTA epochs of the stand-alone all-reduce kernel, then -- from a 256-byte
+// boundary -- the words of the fused GEMV + all-reduce: tile epochs u32 [kP2PFusedMaxTiles] and
+// arrival counters u32 [2 halves][kP2PFusedMaxTiles], and the fused kernel's OWN slots
+// [2 halves][kMaxPeers][max_bytes] (separate from the stand-alone kernel's, so that the two may
+// be mixed freely on one stream).
+constexpr int kP2PFusedMaxTiles = 1024;
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline size_t tl_p2p_fused_offset(size_t max_bytes) {
+  return (2 * size_t(tl_ctx::kMaxPeers) * max_bytes + sizeof(uint32_t) * (2 * tl_ctx::kMaxPeers * 8 + 8) + 255) & ~size_t(255);
+}
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline size_t tl_p2p_fused_slots_offset(size_t max_bytes) {
+  return tl_p2p_fused_offset(max_bytes) + ((sizeof(uint32_t) * 3 * kP2PFusedMaxTiles + 255) & ~size_t(255));
+}
+inline size_t tl_p2p_total_bytes(size_t max_bytes) {
+  return tl_p2p_fused_slots_offset(max_bytes) + 2 * size_t(tl_ctx::kMaxPeers) * max_bytes;
+}
 
 bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, tl_variant* v);
 

@@ -629,11 +629,37 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Arguments of the fused row-parallel GEMV + all-reduce (see qgemv_ring_allreduce_kernel).
+struct PushArgs {
+  uint8_t* base[tl_ctx::kMaxPeers];  // every rank's exchange buffer as mapped on this GPU (own = local)
+  int32_t rank, world;
+  uint64_t max_bytes;                // size of one slot
+  void* dst;                         // [m, n] sum over ranks, in the output type
+  int* status;
+};
+constexpr int kPushSpinLimit = 1 << 22;  // polls of one thread; seconds, not forever
+__device__ __forceinline__ uint32_t push_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void push_red_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ float push_load(const void* base, int dtype, int64_t idx) {
+  // written by other GPUs: volatile loads, never a cached copy
+  if (dtype == TL_F32) return __ldcv(reinterpret_cast<const float*>(base) + idx);
+  const unsigned short bits = __ldcv(reinterpret_cast<const unsigned short*>(base) + idx);
+  if (dtype == TL_F16) return __half2float(__ushort_as_half(bits));
+  return __uint_as_float(uint32_t(bits) << 16);
+}
+
 // MAXT / MINB: launch bounds.  The 4-warp configuration asks for 12 resident CTAs per SM
 // (<= 42 registers) so that, under programmatic dependent launch, the CTAs of the NEXT kernel
 // fit beside the 6-7 CTAs per SM of the running one and prefetch their weights early.
-template <typename AT, int NT, bool GROUPED, int S>
-__device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& epi, int64_t tile_index, uint8_t* ring_raw) {
+template <typename AT, int NT, bool GROUPED, int S, bool PUSH = false>
+__device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& epi, int64_t tile_index, uint8_t* ring_raw,
+                                          const PushArgs* q = nullptr) {
   uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [S][2][blockDim.x]
   const int nthreads = blockDim.x, tid = threadIdx.x;
   float* red = reinterpret_cast<float*>(ring_raw + size_t(S) * 2 * nthreads * 16);  // [warps][NT][4][32]
@@ -754,6 +780,15 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
 #pragma unroll
     for (int i = 0; i < 4; ++i) red[((warp * NT + nt) * 4 + i) * 32 + lane] = total[nt][i];
   __syncthreads();
+  // Fused all-reduce (PUSH): this tile's partial sums go, rounded to the output type, straight
+  // into slot (half, rank) of EVERY rank's exchange buffer instead of into p.out.
+  uint32_t push_epoch = 0;
+  uint32_t* push_words = nullptr;
+  if (PUSH) {
+    push_words = reinterpret_cast<uint32_t*>(q->base[q->rank] + tl_p2p_fused_offset(q->max_bytes));
+    push_epoch = push_words[tile_index];  // owner-only counter; every thread reads it before thread 0 bumps it
+  }
+  const int push_half = int(push_epoch & 1u);
   for (int o = tid; o < NT * 128; o += nthreads) {
     const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
     float v = 0.f;
@@ -765,7 +800,55 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       float s = p.wscale;
       if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
       const float r = tl_apply_epilogue(epi, v * s, p.row0 + col, row, p.n);
-      tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+      if (PUSH) {
+        for (int rr = 0; rr < q->world; ++rr)
+          tl_store_out(q->base[rr] + tl_p2p_fused_slots_offset(q->max_bytes) + (size_t(push_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes, p.out_dtype,
+                       int64_t(col) * p.n + row, r);
+      } else {
+        tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+      }
+    }
+  }
+  if (PUSH) {
+    // One arrival per rank on the tile's counter (release at system scope, cumulative over the
+    // barrier, so the pushes above are visible first); then wait -- bounded -- until all ranks'
+    // versions of THIS tile have arrived here, and sum them in rank order: every rank computes
+    // the same bits, the ones the stand-alone all-reduce gives.  A CTA waits only for the same
+    // tile of the other GPUs, never for a CTA of its own GPU.  Halves alternate per use of a
+    // tile, so a rank that is one call ahead writes the other half.
+    __shared__ int push_ok;
+    __syncthreads();
+    uint32_t* arrive_local = push_words + kP2PFusedMaxTiles + push_half * kP2PFusedMaxTiles + tile_index;
+    if (tid == 0) {
+      push_words[tile_index] = push_epoch + 1;
+      push_ok = 1;
+    }
+    if (tid < q->world) {
+      uint32_t* peer_words = reinterpret_cast<uint32_t*>(q->base[tid] + tl_p2p_fused_offset(q->max_bytes));
+      push_red_release_sys(peer_words + kP2PFusedMaxTiles + push_half * kP2PFusedMaxTiles + tile_index, 1u);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t want = uint32_t(q->world) * (push_epoch / 2 + 1);  // every use of (half, tile) adds `world` arrivals
+      int spins = 0;
+      while (int32_t(push_ld_acquire_sys(arrive_local) - want) < 0) {
+        if (++spins > kPushSpinLimit) { push_ok = 0; atomicExch(q->status, TL_ERR_TIMEOUT); break; }
+      }
+    }
+    __syncthreads();
+    if (push_ok) {
+      for (int o = tid; o < NT * 128; o += nthreads) {
+        const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+        const int64_t row = tile_row + (ln >> 2) + ((i & 2) ? 8 : 0);
+        const int col = 8 * nt + 2 * (ln & 3) + (i & 1);
+        if (row < p.n && col < p.m) {
+          const int64_t idx = int64_t(col) * p.n + row;
+          float sum = 0.f;
+          for (int rr = 0; rr < q->world; ++rr)
+            sum += push_load(q->base[q->rank] + tl_p2p_fused_slots_offset(q->max_bytes) + (size_t(push_half) * tl_ctx::kMaxPeers + rr) * q->max_bytes, p.out_dtype, idx);
+          tl_store_out(q->dst, p.out_dtype, idx, sum);
+        }
+      }
     }
   }
   TL_RT_MIN(trace_id, 4);
@@ -778,6 +861,17 @@ template <typename AT, int NT, bool GROUPED, int S, int MAXT = kMmaMaxWarps * 32
 __global__ void __launch_bounds__(MAXT, MINB) qgemv_ring_kernel(GemvArgs p, EpiParams epi) {
   extern __shared__ __align__(16) uint8_t ring_smem[];
   ring_tile<AT, NT, GROUPED, S>(p, epi, blockIdx.x, ring_smem);
+}
+
+// Row-parallel projection fused with its all-reduce (tensor parallelism, o / down): every CTA
+// computes its 16-row tile of the local partial product, pushes it into all ranks' exchange
+// buffers over NVLink (plain peer stores), signals, waits for the other ranks' versions of the
+// same tile and writes the summed tile -- one kernel where a GEMV and an all-reduce kernel ran.
+// Two resident CTAs of 512 threads per SM (64 registers) keep the 256-tile projections in one wave.
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32, 2) qgemv_ring_allreduce_kernel(GemvArgs p, EpiParams epi, PushArgs q) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  ring_tile<AT, NT, GROUPED, S, true>(p, epi, blockIdx.x, ring_smem, &q);
 }
 
 // Horizontal fusion: up to four projections that read the SAME activations (q/k/v, gate/up) in
@@ -2459,3 +2553,90 @@ extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_it
   return cudaMemcpyFromSymbol(dst, g_chain_iter, bytes) == cudaSuccess ? 0 : -1;
 }
 #endif
+
+// ---------------------------------------------------------------------------
+// Fused row-parallel GEMV + all-reduce (host side)
+// ---------------------------------------------------------------------------
+namespace {
+template <typename AT, int NT, bool GROUPED>
+cudaError_t launch_ring_allreduce(int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e, const PushArgs& q) {
+  constexpr int S = 4;
+  const size_t smem = size_t(S) * 2 * block * 16 + size_t(block / 32) * NT * 128 * 4;
+  auto kern = qgemv_ring_allreduce_kernel<AT, NT, GROUPED, S>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, p, e, q);
+}
+template <typename AT>
+cudaError_t launch_ring_allreduce_at(bool two, bool grouped, int grid, int block, cudaStream_t s, const GemvArgs& p,
+                                     const EpiParams& e, const PushArgs& q) {
+  if (two) return grouped ? launch_ring_allreduce<AT, 2, true>(grid, block, s, p, e, q) : launch_ring_allreduce<AT, 2, false>(grid, block, s, p, e, q);
+  return grouped ? launch_ring_allreduce<AT, 1, true>(grid, block, s, p, e, q) : launch_ring_allreduce<AT, 1, false>(grid, block, s, p, e, q);
+}
+}  // namespace
+
+extern "C" int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed, const void* scales,
+                                         void* out, int32_t out_dtype, int32_t m, int64_t n, int64_t k,
+                                         const tl_quant_desc* qdesc, float alpha) {
+  TL_CHECK_CTX(ctx);
+  if (ctx->world <= 1)  // nothing to sum: the plain product
+    return tl_qgemv_nt(ctx, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc, alpha, nullptr);
+  int32_t rc = tl_check_qargs(ctx, "tl_qgemv_nt_allreduce", a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc);
+  if (rc != TL_OK) return rc;
+  if (m < 1 || m > 16) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_allreduce: m=%d outside the GEMV range [1,16]", m);
+  if (!ctx->p2p_attached) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_allreduce: peers not attached (tl_p2p_create / tl_p2p_attach)");
+  if (!(a_dtype == TL_F16 || a_dtype == TL_BF16) || k % 64 != 0 || qdesc->group_size % 64 != 0 ||
+      (reinterpret_cast<uintptr_t>(a) & 15) || (reinterpret_cast<uintptr_t>(packed) & 15))
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                        "tl_qgemv_nt_allreduce: needs f16/bf16 activations, K %% 64 == 0, group %% 64 == 0, 16-byte aligned operands");
+  const int64_t tiles = (n + 15) / 16;
+  if (n < 1 || tiles > kP2PFusedMaxTiles)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_allreduce: n=%lld outside [1, %d]", (long long)n, 16 * kP2PFusedMaxTiles);
+  if (size_t(m) * size_t(n) * tl_dtype_size(out_dtype) > ctx->p2p_max_bytes)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_allreduce: %zu bytes exceed the exchange buffer (%zu)",
+                        size_t(m) * size_t(n) * tl_dtype_size(out_dtype), ctx->p2p_max_bytes);
+  // The tile counters count uses, so every fused call on a context must cover the same tiles.
+  if (ctx->fused_tiles != 0 && ctx->fused_tiles != tiles)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_allreduce: every call on a context must have the same n (first call: %lld rows)",
+                        (long long)ctx->fused_tiles * 16);
+  EpiParams epi;
+  bool has_ops = false;
+  rc = tl_make_epi(ctx, nullptr, alpha, &epi, &has_ops);
+  if (rc != TL_OK) return rc;
+  DeviceGuard guard(ctx->device);
+  GemvArgs p{};
+  p.a = a; p.packed = reinterpret_cast<const uint32_t*>(packed); p.scales = scales; p.out = out;
+  p.m = m; p.n = int32_t(n); p.k = int32_t(k);
+  p.group = qdesc->group_size; p.groups_per_row = int32_t(k / qdesc->group_size);
+  p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
+  p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+  p.row0 = 0; p.m_total = m;
+  PushArgs q{};
+  for (int r = 0; r < ctx->world; ++r) q.base[r] = static_cast<uint8_t*>(ctx->p2p_peer[r]);
+  q.rank = ctx->rank; q.world = ctx->world; q.max_bytes = ctx->p2p_max_bytes; q.dst = out; q.status = ctx->dev_status;
+  // widest CTA that keeps the launch in one wave at two resident CTAs per SM
+  int warps = 4;
+  for (int w : {16, 8})
+    if (tiles <= int64_t(ctx->sm_count) * (1024 / (w * 32))) { warps = w; break; }
+  const int block = warps * 32, grid = int(tiles);
+  const bool grouped = qdesc->group_size != k;
+  cudaError_t e = a_dtype == TL_F16 ? launch_ring_allreduce_at<__half>(m > 8, grouped, grid, block, ctx->stream, p, epi, q)
+                                    : launch_ring_allreduce_at<__nv_bfloat16>(m > 8, grouped, grid, block, ctx->stream, p, epi, q);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_nt_allreduce: launch failed: %s", cudaGetErrorString(e));
+  }
+  ctx->fused_tiles = tiles;
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  ctx->counters[TL_COUNTER_QGEMV]++;
+  return TL_OK;
+}

@@ -78,7 +78,7 @@ class _Proj:
 class DecodeStack:
     def __init__(self, be: CudaBackend, cfg: StackConfig, rank: int = 0, world: int = 1, tp_mode: str = "chained",
                  seed: int = 0, allreduce: str = "nccl", fuse: bool = True, chain: bool = False):
-        assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p")
+        assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p", "fused")
         # chain: the whole step as ONE persistent cooperative launch (tl_qgemv_chain_*); single rank,
         # batch <= 16 only -- elsewhere the step stays a graph of per-projection launches
         self.chain_requested = chain
@@ -86,7 +86,9 @@ class DecodeStack:
         self._chain_keep = []
         self.be, self.cfg, self.rank, self.world, self.tp_mode = be, cfg, rank, world, tp_mode
         self.fuse = fuse  # q/k/v and gate/up as one launch each
-        self.allreduce = allreduce  # "p2p": the library's one-shot peer-memory all-reduce (peers must be attached)
+        # "p2p": the library's one-shot peer-memory all-reduce (peers must be attached);
+        # "fused": the row-parallel projections do their own all-reduce (tl_qgemv_nt_allreduce)
+        self.allreduce = allreduce
         self.dev = torch.device("cuda", be.device)
         self.lib, self.ctx = be._lib, be._ctx
         self.tdt = torch.float16 if cfg.act_dtype == "f16" else torch.bfloat16
@@ -165,9 +167,20 @@ class DecodeStack:
                                                        B.DTYPE_ID[projs[0].out_dtype], self.cfg.batch, projs[0].k,
                                                        C.byref(q)))
 
+    def _run_row_parallel(self, p: _Proj, x: torch.Tensor, out: torch.Tensor):
+        """o / down: the partial product and its sum over ranks."""
+        if self.world > 1 and self.allreduce == "fused" and self.cfg.batch <= 16 and not p.act:
+            q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, p.k, B.TL_F32, B.TL_SCALE_DIRECT)
+            B.check(self.ctx, self.lib.tl_qgemv_nt_allreduce(
+                self.ctx, x.data_ptr(), self.adt, p.w.data_ptr(), p.s.data_ptr(), out.data_ptr(),
+                B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha))
+            return
+        self._run(p, x, out)
+        self._allreduce(out)
+
     def _allreduce(self, t: torch.Tensor):
         if self.world > 1:
-            if self.allreduce == "p2p":
+            if self.allreduce in ("p2p", "fused"):
                 B.check(self.ctx, self.lib.tl_allreduce_sum_p2p(self.ctx, t.data_ptr(), t.data_ptr(), t.numel(), self.adt))
             else:
                 B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, t.data_ptr(), t.numel(), self.adt))
@@ -236,16 +249,14 @@ class DecodeStack:
                 self._allgather(self.q, self.q_full, self.adt)
                 self._slice_cols(self.q_full, self.q_slice)
                 o_in = self.q_slice
-            self._run(po, o_in, self.h1)
-            self._allreduce(self.h1)
+            self._run_row_parallel(po, o_in, self.h1)
             self._run_batched((pg, pu), self.h1, (self.g, self.u))
             d_in = self.g
             if gather:
                 self._allgather(self.g, self.g_full, self.adt)
                 self._slice_cols(self.g_full, self.g_slice)
                 d_in = self.g_slice
-            self._run(pd, d_in, self.h2)
-            self._allreduce(self.h2)
+            self._run_row_parallel(pd, d_in, self.h2)
             x = self.h2
         self._run(self.lm_head, x, self.logits_local)
         if self.world > 1:
