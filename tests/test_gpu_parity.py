@@ -652,3 +652,62 @@ def test_ring_launch_shape_fits_one_wave_when_it_can(backend):
     assert be.planQuantizedMatmul(8, 1024, 4096, "f16", "f16", tb.perChannelFormat(4096).packing)["choice"][2] == 16
     # far more tiles than one wave holds: 4-warp CTAs
     assert be.planQuantizedMatmul(8, 151936, 4096, "f16", "f16", tb.perChannelFormat(4096).packing)["choice"][2] == 4
+
+
+@pytest.mark.parametrize("m,act_dtype", [(1, "f16"), (8, "f16"), (8, "bf16"), (13, "f16"), (16, "bf16")])
+@pytest.mark.parametrize("warps,depth", [(4, 2), (8, 4), (16, 2)])
+def test_wide_ring_tiles_give_the_same_bits(backend, m, act_dtype, warps, depth):
+    """32-row ring tiles (variant p2 = 2: one activation fragment feeds two MMA row tiles) against the
+    16-row tiles of the same warp count: same summation order, so the same bits; ragged N and K."""
+    be = backend
+    n, k = 1000, 832   # 31 full 32-row tiles + 8 rows; 13 k blocks over 4 / 8 / 16 warps
+    cs = cases.per_channel_case(n, k, m, seed=50 + m, act_dtype=act_dtype, bias=True)
+    w = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, tb.perChannelFormat(k))
+    x = be.ops.tensorFromArray(cs["x_bits"], [m, k], act_dtype)
+    b = be.ops.tensorFromArray(cs["bias"], [n], "f32")
+    outs = []
+    for wide in (0, 2):
+        be.forceVariant((1, 4, warps, depth, wide, 0))
+        try:
+            y = be.linear(x, w, b, "silu", "f32")
+        finally:
+            be.forceVariant(None)
+        outs.append(be.ops.read(y).copy())
+        y.destroy()
+    assert np.array_equal(outs[0].view(np.uint32), outs[1].view(np.uint32))
+    wref = orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k)
+    ref = orc.linear_reference(cs["x"], wref, cs["bias"], "silu")
+    assert cases.rel_err(outs[1], ref) <= TOL_F32
+    for t in (x, b, w.scales, w):
+        t.destroy()
+
+
+def test_wide_ring_tiles_grouped_scales_and_batched_launch(backend):
+    be = backend
+    lib, ctx = be._lib, be._ctx
+    m, k, group = 6, 512, 64
+    rng = np.random.default_rng(61)
+    x = rng.standard_normal((m, k)).astype(np.float16)
+    xt = be.ops.tensorFromArray(x, [m, k], "f16")
+    fmt = tb.StorageFormat("f16", tb.QuantPacking("int8-grouped", group, "f16"))
+    ws, outs, refs = [], [], []
+    for n in (200, 72, 33):
+        wf = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+        packed, scales = be.quantizeLinearWeight(wf, group)
+        ws.append(be.createQuantizedWeight(packed, scales, n, k, fmt))
+        outs.append(be.ops.empty([m, n], "f32"))
+        refs.append(orc.matmul_nt(x.astype(np.float32), orc.dequantize_to_f32(packed, scales, k, group)))
+    items = (B.QGemvItem * 3)()
+    for i, (w, o) in enumerate(zip(ws, outs)):
+        items[i] = B.QGemvItem(w.buffer, w.scales.buffer, o.buffer, w.shape[0], 1.0, None)
+    q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, group, B.TL_F16, B.TL_SCALE_SNORM127)
+    be.forceVariant((1, 4, 4, 4, 2, 0))
+    try:
+        B.check(ctx, lib.tl_qgemv_nt_batched(ctx, xt.buffer, B.TL_F16, items, 3, B.TL_F32, m, k, C.byref(q)))
+    finally:
+        be.forceVariant(None)
+    for o, ref in zip(outs, refs):
+        assert cases.rel_err(be.ops.read(o).reshape(ref.shape), ref) <= TOL_F32
+    for t in [xt] + outs + [w.scales for w in ws] + ws:
+        t.destroy()
+    assert be.getGpuUncapturedErrorCount() == 0

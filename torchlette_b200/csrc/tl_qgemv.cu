@@ -863,6 +863,156 @@ __global__ void __launch_bounds__(MAXT, MINB) qgemv_ring_kernel(GemvArgs p, EpiP
   ring_tile<AT, NT, GROUPED, S>(p, epi, blockIdx.x, ring_smem);
 }
 
+// ---------------------------------------------------------------------------
+// Wide ring tile: 32 weight rows per CTA (two MMA row tiles per warp and k block).
+// From m = 8 up the activation fragments weigh as much as the weights (m x 64 x 2 bytes against
+// 16 x 64 per warp and k block) and, re-read by every 16-row tile, they make L2 -> SM traffic
+// and load-store issue the limit instead of HBM: 5.0 TB/s at m = 8 and 4.1 TB/s at m = 16 on a
+// 622 MB matrix against 6.5 TB/s at m = 1.  Here one activation fragment feeds two row tiles:
+// half the activation traffic and twice the independent MMA work per load.  Same fragment
+// mapping, k interleave and summation order as ring_tile, so the outputs have the same bits.
+// ---------------------------------------------------------------------------
+template <typename AT, int NT, bool GROUPED, int S>
+__device__ __forceinline__ void ring_tile2(const GemvArgs& p, const EpiParams& epi, int64_t tile_index, uint8_t* ring_raw) {
+  uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [S][4][blockDim.x]
+  const int nthreads = blockDim.x, tid = threadIdx.x;
+  float* red = reinterpret_cast<float*>(ring_raw + size_t(S) * 4 * nthreads * 16);  // [warps][2][NT][4][32]
+  const int warps = nthreads >> 5, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t tile_row = tile_index * 32;
+  const uint8_t* wbytes = reinterpret_cast<const uint8_t*>(p.packed);
+  int64_t rows[4];
+  const uint8_t* wp[4];  // rows g, g+8 (first row tile), g+16, g+24 (second)
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    rows[r] = min(tile_row + g + 8 * r, int64_t(p.n) - 1);
+    wp[r] = wbytes + rows[r] * p.k + 16 * t + warp * 64;
+  }
+  const int kstride = warps * 64;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const AT* a_col[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) a_col[nt] = a + int64_t(min(g + 8 * nt, p.m - 1)) * p.k + 16 * t + warp * 64;
+  const int kblocks = p.k >> 6;
+  const int nkb = (kblocks - warp + warps - 1) / warps;
+  const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
+  const uint32_t slot_bytes = uint32_t(nthreads) * 16u;
+
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#pragma unroll
+  for (int s = 0; s < S; ++s) {
+    if (s < nkb) {
+#pragma unroll
+      for (int r = 0; r < 4; ++r) cp_async16(ring_base + (4 * s + r) * slot_bytes, wp[r] + int64_t(s) * kstride);
+    }
+    cp_async_commit();
+  }
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+
+  float total[2][NT][4];
+#pragma unroll
+  for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) total[rt][nt][i] = 0.f;
+
+  for (int i0 = 0; i0 < nkb; i0 += S) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int i = i0 + s;
+      if (i < nkb) {
+        uint4 bx[NT][2];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(i) * kstride);
+          bx[nt][0] = __ldg(src);
+          bx[nt][1] = __ldg(src + 1);
+        }
+        cp_async_wait<S - 1>();
+#pragma unroll
+        for (int rt = 0; rt < 2; ++rt) {
+          const uint4 wl = ring[(4 * s + 2 * rt) * nthreads + tid];
+          const uint4 wh = ring[(4 * s + 2 * rt + 1) * nthreads + tid];
+          float c[NT][4];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) c[nt][e] = GROUPED ? 0.f : total[rt][nt][e];
+          const uint32_t wlo[4] = {wl.x, wl.y, wl.z, wl.w};
+          const uint32_t whi[4] = {wh.x, wh.y, wh.z, wh.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint32_t a0, a1, a2, a3;
+            MmaOps<AT>::cvt(wlo[j], a0, a2);
+            MmaOps<AT>::cvt(whi[j], a1, a3);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const uint4 v = bx[nt][j >> 1];
+              const uint32_t b0 = (j & 1) ? v.z : v.x, b1 = (j & 1) ? v.w : v.y;
+              MmaOps<AT>::mma(c[nt], a0, a1, a2, a3, b0, b1);
+            }
+          }
+          if (GROUPED) {
+            const int gi = ((warp + i * warps) * 64) / p.group;
+            const float s_lo = tl_load_scale(p.scales, p.scales_dtype, rows[2 * rt] * p.groups_per_row + gi);
+            const float s_hi = tl_load_scale(p.scales, p.scales_dtype, rows[2 * rt + 1] * p.groups_per_row + gi);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              total[rt][nt][0] = fmaf(s_lo, c[nt][0], total[rt][nt][0]);
+              total[rt][nt][1] = fmaf(s_lo, c[nt][1], total[rt][nt][1]);
+              total[rt][nt][2] = fmaf(s_hi, c[nt][2], total[rt][nt][2]);
+              total[rt][nt][3] = fmaf(s_hi, c[nt][3], total[rt][nt][3]);
+            }
+          } else {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) total[rt][nt][e] = c[nt][e];
+          }
+        }
+        if (i + S < nkb) {
+#pragma unroll
+          for (int r = 0; r < 4; ++r) cp_async16(ring_base + (4 * s + r) * slot_bytes, wp[r] + int64_t(i + S) * kstride);
+        }
+        cp_async_commit();
+      } else {
+        cp_async_commit();
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int rt = 0; rt < 2; ++rt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) red[(((warp * 2 + rt) * NT + nt) * 4 + i) * 32 + lane] = total[rt][nt][i];
+  __syncthreads();
+  for (int o = tid; o < 2 * NT * 128; o += nthreads) {
+    const int rt = o / (NT * 128), o1 = o - rt * (NT * 128);
+    const int nt = o1 >> 7, i = (o1 >> 5) & 3, ln = o1 & 31;
+    float v = 0.f;
+    for (int w = 0; w < warps; ++w) v += red[(((w * 2 + rt) * NT + nt) * 4 + i) * 32 + ln];
+    const int gg = ln >> 2, tt = ln & 3;
+    const int64_t row = tile_row + 16 * rt + gg + ((i & 2) ? 8 : 0);
+    const int col = 8 * nt + 2 * tt + (i & 1);
+    if (row < p.n && col < p.m) {
+      float sc = p.wscale;
+      if (!GROUPED) sc *= tl_load_scale(p.scales, p.scales_dtype, row);
+      const float r = tl_apply_epilogue(epi, v * sc, p.row0 + col, row, p.n);
+      tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
+    }
+  }
+}
+
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring2_kernel(GemvArgs p, EpiParams epi) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  ring_tile2<AT, NT, GROUPED, S>(p, epi, blockIdx.x, ring_smem);
+}
+
 // Row-parallel projection fused with its all-reduce (tensor parallelism, o / down): every CTA
 // computes its 16-row tile of the local partial product, pushes it into all ranks' exchange
 // buffers over NVLink (plain peer stores), signals, waits for the other ranks' versions of the
@@ -889,6 +1039,14 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_batched_kernel(c
   const int blk = int(blockIdx.x);
   const int i = (blk >= b.tile_start[1]) + (blk >= b.tile_start[2]) + (blk >= b.tile_start[3]);
   ring_tile<AT, NT, GROUPED, S>(b.p[i], b.e[i], blk - b.tile_start[i], ring_smem);
+}
+// the same with 32-row tiles (tile_start counts 32-row tiles)
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring2_batched_kernel(const __grid_constant__ RingBatchArgs b) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int blk = int(blockIdx.x);
+  const int i = (blk >= b.tile_start[1]) + (blk >= b.tile_start[2]) + (blk >= b.tile_start[3]);
+  ring_tile2<AT, NT, GROUPED, S>(b.p[i], b.e[i], blk - b.tile_start[i], ring_smem);
 }
 
 // ---------------------------------------------------------------------------
@@ -1403,9 +1561,16 @@ int ring_occupancy(tl_ctx* ctx, bool batched, int a_dtype, bool two, bool groupe
   return occ;
 }
 void ring_pick_shape(tl_ctx* ctx, bool batched, int a_dtype, int m, bool grouped, int64_t tiles, int64_t k, int* warps,
-                     int* depth) {
+                     int* depth, int* wide = nullptr) {
+  if (wide) *wide = 0;
   const bool two = m > 8;
   const int kblocks = int(k >> 6);
+  if (wide && two && tiles <= 2 * int64_t(ctx->sm_count)) {
+    // Two token tiles on a matrix of few tiles (4096 rows): 32-row tiles, where one activation
+    // fragment feeds two row tiles, measured 17.3 against 22.0 us (4096 x 14336, m = 16).
+    *wide = 1; *warps = 16; *depth = 4;
+    return;
+  }
   for (int w : {16, 8, 4}) {
     const int nkb = (kblocks + w - 1) / w;  // k blocks of one warp
     for (int s : {8, 6, 4, 2}) {
@@ -1424,6 +1589,39 @@ void ring_pick_shape(tl_ctx* ctx, bool batched, int a_dtype, int m, bool grouped
   // CTAs, and rings deeper than 4 measured 1.5x slower
   if (two) d = std::min(d, 4);
   *warps = 4; *depth = d;
+  // many waves and two token tiles: 32-row tiles are ~5 % faster (lm_head at m = 16: 134 against 142 us)
+  if (wide && two) *wide = 1;
+}
+
+// wide (32-row) ring tiles: depths 2 and 4
+template <typename K>
+void launch_pdl(K kernel, int grid, int block, size_t smem, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, p, e);
+}
+inline size_t ring2_smem_bytes(int warps, int depth, bool two) {
+  return size_t(depth) * 4 * warps * 32 * 16 + size_t(warps) * 2 * (two ? 2 : 1) * 128 * 4;
+}
+template <typename AT, int NT, bool GROUPED>
+void launch_ring2_s(int depth, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  const size_t smem = ring2_smem_bytes(block / 32, depth >= 4 ? 4 : 2, NT == 2);
+  if (depth >= 4) launch_pdl(qgemv_ring2_kernel<AT, NT, GROUPED, 4>, grid, block, smem, s, p, e);
+  else launch_pdl(qgemv_ring2_kernel<AT, NT, GROUPED, 2>, grid, block, smem, s, p, e);
+}
+template <typename AT>
+void launch_ring2(bool two, bool grouped, int depth, int grid, int block, cudaStream_t s, const GemvArgs& p, const EpiParams& e) {
+  if (two) { if (grouped) launch_ring2_s<AT, 2, true>(depth, grid, block, s, p, e); else launch_ring2_s<AT, 2, false>(depth, grid, block, s, p, e); }
+  else { if (grouped) launch_ring2_s<AT, 1, true>(depth, grid, block, s, p, e); else launch_ring2_s<AT, 1, false>(depth, grid, block, s, p, e); }
 }
 
 template <typename AT, bool M16, bool GROUPED>
@@ -1496,7 +1694,8 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
              (v.p0 == 4 || v.p0 == 5 || v.p0 == 6);
     case kRing:
       return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0 &&
-             (v.p1 == 2 || v.p1 == 4 || v.p1 == 6 || v.p1 == 8);
+             (v.p1 == 2 || v.p1 == 4 || v.p1 == 6 || v.p1 == 8) &&
+             (v.p2 == 0 || v.p2 == 1 || (v.p2 == 2 && v.p1 <= 4));  // p2 = 2: 32-row tiles
     case kSk:
       // a thread's 32 contiguous weight bytes feed all of a unit's MMAs, so one MMA spans the whole
       // 128-wide unit: a scale group must cover it
@@ -1513,9 +1712,9 @@ int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, i
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 64 == 0 && q.group_size % 64 == 0) {
     const int64_t tiles = (n + 15) / 16;
     v.kernel = kRing;
-    int w = 4, d = 2;
-    ring_pick_shape(ctx, false, a_dtype, m, q.group_size != k, tiles, k, &w, &d);
-    v.p0 = w; v.p1 = d;
+    int w = 4, d = 2, wide = 0;
+    ring_pick_shape(ctx, false, a_dtype, m, q.group_size != k, tiles, k, &w, &d, &wide);
+    v.p0 = w; v.p1 = d; v.p2 = wide ? 2 : 0;
   } else if (k % 16 == 0 && q.group_size % 16 == 0) {
     v.kernel = kSimt; v.p0 = 8; v.p1 = 2;
   } else {
@@ -1536,7 +1735,7 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
     v.family = TL_FAMILY_QGEMV; v.kernel = kernel; v.p0 = p0; v.p1 = p1; v.p2 = kernel == kMma ? 1 : 0;
     if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q)) return;
     for (const auto& o : *out)
-      if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1) return;
+      if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1 && o.p2 == v.p2) return;
     out->push_back(v);
   };
   for (int w : {8, 16})
@@ -1544,6 +1743,14 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
   for (int st : {4, 6}) add(kTma, st, 0);
   for (int w : {2, 4, 8, 16})
     for (int u : {2, 4, 6, 8}) add(kRing, w, u);
+  for (int w : {4, 8, 16})
+    for (int u : {2, 4}) {  // 32-row tiles
+      tl_variant v{};
+      v.family = TL_FAMILY_QGEMV; v.kernel = kRing; v.p0 = w; v.p1 = u; v.p2 = 2;
+      bool dup = false;
+      for (const auto& o : *out) dup = dup || (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1 && o.p2 == v.p2);
+      if (!dup && tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q)) out->push_back(v);
+    }
   for (int b : {2, 4, 8})
     for (int u : {2, 4}) add(kSk, b, u);
   for (int w : {4, 8, 16})
@@ -1600,6 +1807,7 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
     grid = (sk.warps_used + 7) / 8;
   } else if (v.kernel == kScalar) grid = int((n + v.p0 - 1) / v.p0);
   else if (v.kernel == kSimt) { grid = int((n + int64_t(v.p0) * v.p1 - 1) / (int64_t(v.p0) * v.p1)); launches = (m + 3) / 4; }
+  else if (v.kernel == kRing && v.p2 == 2) grid = int((n + 31) / 32);
   else grid = int((n + 15) / 16);
   if (receipt) {
     receipt->choice = v;
@@ -1695,6 +1903,9 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
       else if (a_dtype == TL_F16) launch_simt_r<__half>(v.p1, mt, grouped, grid, block, s, ps, epi);
       else launch_simt_r<__nv_bfloat16>(v.p1, mt, grouped, grid, block, s, ps, epi);
     }
+  } else if (v.kernel == kRing && v.p2 == 2) {
+    if (a_dtype == TL_F16) launch_ring2<__half>(m > 8, grouped, v.p1, grid, block, s, p, epi);
+    else launch_ring2<__nv_bfloat16>(m > 8, grouped, v.p1, grid, block, s, p, epi);
   } else if (v.kernel == kRing) {
     if (a_dtype == TL_F16) launch_ring<__half>(m > 8, grouped, v.p1, grid, block, s, p, epi);
     else launch_ring<__nv_bfloat16>(m > 8, grouped, v.p1, grid, block, s, p, epi);
@@ -1862,6 +2073,30 @@ void launch_ring_batched(int grid, int block, cudaStream_t s, const RingBatchArg
   cfg.numAttrs = 1;
   cudaLaunchKernelEx(&cfg, kern, b);
 }
+template <typename AT, int NT, bool GROUPED, int S>
+void launch_ring2_batched(int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
+  const size_t smem = ring2_smem_bytes(block / 32, S, NT == 2);
+  auto kern = qgemv_ring2_batched_kernel<AT, NT, GROUPED, S>;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kern, b);
+}
+template <typename AT>
+void launch_ring2_batched_at(bool two, bool grouped, int depth, int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
+#define TL_R2B(NT_, G_) { if (depth >= 4) launch_ring2_batched<AT, NT_, G_, 4>(grid, block, s, b); else launch_ring2_batched<AT, NT_, G_, 2>(grid, block, s, b); }
+  if (two) { if (grouped) TL_R2B(2, true) else TL_R2B(2, false) }
+  else { if (grouped) TL_R2B(1, true) else TL_R2B(1, false) }
+#undef TL_R2B
+}
 template <typename AT, int NT, bool GROUPED>
 void launch_ring_batched_s(int depth, int grid, int block, cudaStream_t s, const RingBatchArgs& b) {
   if (depth >= 8) launch_ring_batched<AT, NT, GROUPED, 8>(grid, block, s, b);
@@ -1920,9 +2155,6 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
 #ifdef TL_TRACE
     p.trace_id = g_ring_trace_next;
 #endif
-#ifdef TL_TRACE
-  p.trace_id = g_ring_trace_next++;
-#endif
     tiles += (items[i].n + 15) / 16;
   }
   b.tile_start[kMaxBatchItems] = int32_t(tiles);
@@ -1935,19 +2167,31 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
   int64_t n_total = 0;
   for (int i = 0; i < n_items; ++i) n_total += items[i].n;
   DeviceGuard guard(ctx->device);
-  int warps = 4, depth = 2;
-  ring_pick_shape(ctx, true, a_dtype, m, qdesc->group_size != k, tiles, k, &warps, &depth);
+  int warps = 4, depth = 2, wide = 0;
+  ring_pick_shape(ctx, true, a_dtype, m, qdesc->group_size != k, tiles, k, &warps, &depth, &wide);
   tl_variant tv{};
   if (ctx->has_forced && ctx->forced.family == TL_FAMILY_QGEMV && ctx->forced.kernel == kRing) {
-    warps = ctx->forced.p0; depth = ctx->forced.p1;
+    warps = ctx->forced.p0; depth = ctx->forced.p1; wide = ctx->forced.p2 == 2;
   } else if (tl_lookup_tuned(ctx, m, n_total, k, a_dtype, *qdesc, &tv) && tv.family == TL_FAMILY_QGEMV && tv.kernel == kRing) {
-    warps = tv.p0; depth = tv.p1;
+    warps = tv.p0; depth = tv.p1; wide = tv.p2 == 2;
   }
   if (warps != 2 && warps != 4 && warps != 8 && warps != 16)
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_batched: ring variant with %d warps", warps);
+  if (wide) {  // 32-row tiles: the items' tile ranges are counted in those
+    tiles = 0;
+    for (int i = 0; i < kMaxBatchItems; ++i) {
+      b.tile_start[i] = int32_t(tiles);
+      if (i < n_items) tiles += (items[i].n + 31) / 32;
+    }
+    b.tile_start[kMaxBatchItems] = int32_t(tiles);
+    depth = depth >= 4 ? 4 : 2;
+  }
   const int block = warps * 32, grid = int(tiles);
   const bool grouped = qdesc->group_size != k;
-  if (a_dtype == TL_F16) launch_ring_batched_at<__half>(m > 8, grouped, depth, grid, block, ctx->stream, b);
+  if (wide) {
+    if (a_dtype == TL_F16) launch_ring2_batched_at<__half>(m > 8, grouped, depth, grid, block, ctx->stream, b);
+    else launch_ring2_batched_at<__nv_bfloat16>(m > 8, grouped, depth, grid, block, ctx->stream, b);
+  } else if (a_dtype == TL_F16) launch_ring_batched_at<__half>(m > 8, grouped, depth, grid, block, ctx->stream, b);
   else launch_ring_batched_at<__nv_bfloat16>(m > 8, grouped, depth, grid, block, ctx->stream, b);
   TL_CUDA(ctx, cudaGetLastError());
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
