@@ -14,7 +14,11 @@
 //              accumulators; the batch is the MMA n dimension.  f16/bf16
 //              activations, K % 64 == 0, G % 64 == 0.
 //   4 "ring"   kernel 2's tiling with the weight bytes prefetched global -> shared by
-//              per-thread cp.async rings (no registers held in flight).
+//              per-thread cp.async rings (no registers held in flight).  The default.
+//              p0 = warps per tile, p1 = ring depth (2/4/6/8), p2 = 2: 32-row tiles.
+//              Also: a batched launch (several matrices, same activations), a launch fused
+//              with the tensor-parallel all-reduce, and the persistent chain (kernel id 7
+//              only names the chain's CTA shape for tl_force_variant).
 //   6 "bulk"   persistent grid fed by contiguous cp.async.bulk copies of whole 8-row
 //              blocks; batch as the MMA A operand; no cross-CTA partial sums.
 //              p0 = consumer warps, p1 = stage size target in KB.
@@ -25,7 +29,7 @@
 //              shares of 8-row x 128-byte units; partial tiles meet in an f32
 //              scratch.  f16/bf16 activations, K % 128 == 0, G % 128 == 0.
 // Variant parameters: p0 = warps per CTA (sk: CTAs per SM), p1 = rows per warp
-// (simt) / k blocks in flight (mma, sk), p2, p3 = reserved.
+// (simt) / k blocks in flight (mma, sk, ring), p2 = see ring, p3 = reserved.
 #include <algorithm>
 
 #include "tl_common.cuh"
