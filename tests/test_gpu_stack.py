@@ -29,7 +29,9 @@ def _oracle_proj(x, p, out_f16=True):
 
 def test_tiny_stack_matches_the_oracle_end_to_end(backend):
     st = DecodeStack(backend, TINY, seed=3)
-    x = torch.randn(TINY.batch, TINY.hidden, device=st.dev).to(st.tdt)
+    gen = torch.Generator(device=st.dev)
+    gen.manual_seed(11)
+    x = torch.randn(TINY.batch, TINY.hidden, device=st.dev, generator=gen).to(st.tdt)
     st.x.copy_(x)
     torch.cuda.synchronize()
     st.capture()
@@ -52,7 +54,9 @@ def test_full_size_stack_properties(backend):
     cfg8 = StackConfig(**{**QWEN3_8B.__dict__, "batch": 8})
     cfg1 = StackConfig(**{**QWEN3_8B.__dict__, "batch": 1})
     s8 = DecodeStack(backend, cfg8, seed=0)
-    x8 = torch.randn(8, cfg8.hidden, device=s8.dev).to(s8.tdt)
+    gen = torch.Generator(device=s8.dev)
+    gen.manual_seed(12)  # seeded: the inputs, like the weights, are the same in every run
+    x8 = torch.randn(8, cfg8.hidden, device=s8.dev, generator=gen).to(s8.tdt)
     s8.x.copy_(x8)
     torch.cuda.synchronize()
     s8.capture()
@@ -72,7 +76,9 @@ def test_full_size_stack_properties(backend):
     w *= s8.lm_head.s[torch.as_tensor(rows, device=s8.dev)].cpu().numpy().astype(np.float32)[:, None]
     ref = orc.linear_reference(h, w, None, None, alpha=s8.lm_head.alpha)
     got = first[:, torch.as_tensor(rows, device=s8.dev)].cpu().numpy()
-    assert cases.rel_err(got, ref) <= 1e-3
+    err = cases.rel_err(got, ref)
+    print(f"lm_head sampled rows: rel err {err:.3e}")
+    assert err <= 1e-3
     # batch-row independence: the same weights (same seed), batch 1, activation row 5
     s1 = DecodeStack(backend, cfg1, seed=0)
     s1.x.copy_(x8[5:6])
