@@ -121,7 +121,8 @@ class CpuArm:
         from torchlette_b200.decode_stack import QWEN3_8B as cfg
 
         self.orc, self.cfg, self.batch, self.lm_rows = orc, cfg, batch, lm_rows
-        self.threads = threads or orc.max_threads()
+        # explicit: under torch.distributed.run OMP_NUM_THREADS is 1, which is not the box's core count
+        self.threads = threads or len(os.sched_getaffinity(0)) or orc.max_threads()
         rng = np.random.Generator(np.random.PCG64(0))
         self.items = []
         shapes = [(name, k, n) for name, k, n, _ in cfg.projections()] + [("lm_head", cfg.hidden, lm_rows)]
@@ -132,11 +133,12 @@ class CpuArm:
             x = rng.standard_normal((batch, k)).astype(np.float16).astype(np.float32)
             self.items.append((name, w, x))
 
-    def step_seconds(self) -> float:
+    def step_seconds(self, threads: int = 0) -> float:
+        threads = threads or self.threads
         t_layer = t_lm = 0.0
         for name, w, x in self.items:
             t0 = time.perf_counter()
-            y = self.orc.matmul_nt(x, w, self.threads)
+            y = self.orc.matmul_nt(x, w, threads)
             if name == "gate":
                 self.orc.unary("silu", y)
             dt = time.perf_counter() - t0
@@ -155,7 +157,10 @@ class CpuArm:
 def cpu_sample(batch: int):
     arm = CpuArm(batch)
     arm.step_seconds()
-    return arm.describe(batch / arm.step_seconds())
+    d = arm.describe(batch / arm.step_seconds())
+    # the reference's JavaScript CPU backend is single-threaded: the faithful figure beside the all-core one
+    d["value_1_thread"] = batch / arm.step_seconds(threads=1)
+    return d
 
 
 def run_reference(args):
@@ -172,10 +177,11 @@ def run_reference(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f64 accumulate over f32 (CPU)", "data": "synthetic",
-        "config": {"workload": "qwen3-8b-decode-matmul-stack", "batch": args.batch, "layers": 36,
+        "config": {"workload": "qwen3-8b-decode-matmul-stack", "batch": args.batch, "layers": 36, "hidden": 4096,
+                   "intermediate": 12288, "vocab": 151936, "weights": "int8 per-channel, f32 scales, random init",
                    "note": "the reference is TypeScript and no node runtime exists here; this arm is the C port of its "
                            "CPU path (oracle/tl_oracle.c) on all host cores, each step a bounded sample extrapolated"},
-        "cpu_baseline": arm.describe(val),
+        "cpu_baseline": {**arm.describe(val), "value_1_thread": args.batch / arm.step_seconds(threads=1)},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -271,6 +277,67 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
     lib.tl_event_destroy(ctx, ev0)
     lib.tl_event_destroy(ctx, ev1)
     return out
+
+
+def stack_parity(stack, dist):
+    """The stack's last step against the CPU oracle, on its own intermediate values, at any N:
+    (a) 64 lm_head columns spread over all ranks' shards, oracle on the final hidden state
+    (column-parallel path and the logits gather; f32 logits, gate 1e-3);
+    (b) 64 output columns of the LAST layer's down projection, oracle partial products of every rank
+    summed over the ranks (row-parallel path and its all-reduce; f16 hand-over, gate 1e-2);
+    (c) the gathered logits and the reduced hidden state are bit-identical on all ranks."""
+    import numpy as np
+    import torch
+
+    from oracle import oracle as orc
+
+    world, dev = stack.world, stack.dev
+    per = max(8, 64 // world)
+
+    def rel(got, ref):
+        got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
+        return float(np.max(np.abs(got - ref) / np.maximum(1.0, np.abs(ref))))
+
+    def rows_of(n):
+        return torch.as_tensor(np.unique(np.linspace(0, n - 1, per).astype(np.int64)), device=dev)
+
+    # (a) lm_head: this rank's own columns
+    lm = stack.lm_head
+    rows = rows_of(lm.n)
+    w = lm.w[rows].cpu().numpy().astype(np.float32) * lm.s[rows].cpu().numpy().astype(np.float32)[:, None]
+    h = stack.h2.float().cpu().numpy()
+    ref = orc.linear_reference(h, w, None, None, alpha=lm.alpha)
+    err_lm = rel(stack.logits_local[:, rows].float().cpu().numpy(), ref)
+    # (b) last layer's down projection: partial reference per rank, summed over ranks
+    pd = stack.layers[-1][6]
+    rows_d = rows_of(pd.n)
+    wd = pd.w[rows_d].cpu().numpy().astype(np.float32) * pd.s[rows_d].cpu().numpy().astype(np.float32)[:, None]
+    part = orc.linear_reference(stack.g.float().cpu().numpy(), wd, None, None, alpha=pd.alpha).astype(np.float64)
+    if dist is not None:
+        t = torch.as_tensor(part, device=dev)
+        dist.all_reduce(t)
+        part = t.cpu().numpy()
+    err_down = rel(stack.h2[:, rows_d].float().cpu().numpy(), part)
+    identical = True
+    if dist is not None:
+        # (c) every rank holds the same gathered logits and the same reduced hidden state, and the
+        # gathered logits hold this rank's own slice at its column offset
+        nl = stack.logits_local.shape[1]
+        own = torch.equal(stack.logits[:, stack.rank * nl:(stack.rank + 1) * nl], stack.logits_local)
+        sums = torch.stack([stack.logits.double().sum(), stack.logits.double().abs().sum(), stack.h2.double().sum(),
+                            stack.h2.double().abs().sum()])
+        lo, hi = sums.clone(), sums.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        flag = torch.tensor([1.0 if (own and torch.equal(lo, hi)) else 0.0], device=dev, dtype=torch.float64)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        identical = bool(flag.item() == 1.0)
+        e = torch.tensor([err_lm, err_down], device=dev, dtype=torch.float64)
+        dist.all_reduce(e, op=dist.ReduceOp.MAX)
+        err_lm, err_down = float(e[0]), float(e[1])
+    return {"rows": int(per * world), "rel_err": err_lm, "lm_head_rel_err": err_lm, "down_rows": int(len(rows_d)),
+            "down_rel_err": err_down, "ranks_identical": identical,
+            "oracle": "CPU restatement of the reference (oracle/tl_oracle.c) on the stack's own intermediate values"}
 
 
 def run_gpu(args):
@@ -369,22 +436,32 @@ def run_gpu(args):
     B.check(ctx, lib.tl_event_create(ctx, C.byref(ev1)))
 
     # ---- device-timed steps ------------------------------------------------
+    # Blocks of exactly --steps steps, each bracketed by a barrier + synchronize on both sides and
+    # timed with CUDA events on the library's stream; repeated until at least 0.5 s has been timed
+    # (3 blocks at least) and the MEDIAN block (of the max over ranks) is reported.  The clock sampler
+    # starts before the barrier, and one untimed step right behind the barrier aligns the ranks on
+    # the device (it holds all-reduces), so host start-up skew never lands inside a timed block.
     for _ in range(args.warmup):
         stack.step()
-    barrier()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = be.getKernelLaunchCount()
-    B.check(ctx, lib.tl_event_record(ctx, ev0))
-    for _ in range(args.steps):
+    block_ms, timed_s = [], 0.0
+    while len(block_ms) < 3 or (timed_s < 0.5 and len(block_ms) < 200):
+        barrier()
         stack.step()
-    B.check(ctx, lib.tl_event_record(ctx, ev1))
-    barrier()
-    ms = C.c_float()
-    B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-    launches = be.getKernelLaunchCount() - launches0
-    dev_ms = max_over_ranks(ms.value)
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        for _ in range(args.steps):
+            stack.step()
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        barrier()
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        block_ms.append(max_over_ranks(ms.value))
+        timed_s += block_ms[-1] * 1e-3
+    launches = (be.getKernelLaunchCount() - launches0) * args.steps // ((args.steps + 1) * len(block_ms))
+    dev_ms = statistics.median(block_ms)
     ms_per_step = dev_ms / args.steps
     value = cfg.batch * args.steps / (dev_ms * 1e-3)
 
@@ -410,6 +487,8 @@ def run_gpu(args):
     clocks = sampler.stop() if rank == 0 else None
     e2e_value = cfg.batch * args.steps / e2e_s
     finite = bool(torch.isfinite(hlogits).all().item()) and float(hlogits.abs().max()) > 0
+
+    parity = stack_parity(stack, dist if world > 1 else None)
 
     hbm_peak, tf_peak, which = measured_peaks()
     # Per rank: the algorithmic bytes of its own shard, summed over the 253 launches of a step.
@@ -466,7 +545,8 @@ def run_gpu(args):
                        "autotune": bool(args.autotune)},
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_s / args.steps * 1e3, "logits_finite": finite},
-            "gpu_launches": int(launches), "clocks": clocks, "roofline": roofline,
+            "gpu_launches": int(launches), "timed_blocks": len(block_ms), "clocks": clocks, "roofline": roofline,
+            "parity": parity,
             "weight_GB_per_step": cfg.weight_bytes_per_step() / 1e9,
         }
         if cpu is not None:
@@ -475,10 +555,13 @@ def run_gpu(args):
             line["kernels"] = extras
         print(json.dumps(line))
     stack.destroy()
+    parity_ok = parity["lm_head_rel_err"] <= 1e-3 and parity["down_rel_err"] <= 1e-2 and parity["ranks_identical"]
     if world > 1:
         lib.tl_comm_destroy(ctx)
         dist.barrier()
         dist.destroy_process_group()
+    if not parity_ok:
+        raise SystemExit(f"bench.py: parity check failed: {parity}")
 
 
 def main():

@@ -115,6 +115,12 @@ TL_API const char* tl_last_error(tl_ctx* ctx);
  * can order its own work or record its own events on it. */
 TL_API int32_t tl_ctx_stream(tl_ctx* ctx, void** out_stream);
 TL_API int32_t tl_device_sm_count(tl_ctx* ctx, int32_t* out_sms);
+/* Per-context settings by name, the analogue of the reference's single ENV accessor
+ * (src/core/env.ts:14-26).  Unknown names return TL_ERR_INVALID_ARG.
+ *   "wait_limit_polls"       upper bound of the polls of one bounded device-side wait of the
+ *                            peer collectives (default 2^26). */
+TL_API int32_t tl_set_option(tl_ctx* ctx, const char* name, int64_t value);
+TL_API int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value);
 
 /* ---- memory: tensorFromArray / read / destroy (src/backend/types.ts:341-345,
  * :666) ---------------------------------------------------------------------- */

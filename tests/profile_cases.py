@@ -1,8 +1,8 @@
 """Single-kernel driver for profiling: runs one kernel family on one shape a few
 times so that a profiler can capture it on a small, bounded case.
 
-    python -m torchlette_b200.profile_cases gemv --m 1 --n 14336 --k 4096 --variant 1,4,4,4,0,0 --copies 3
-    python -m torchlette_b200.profile_cases gemm --m 2048 --n 14336 --k 4096 --variant 2,0,128,128,4,8 --epilogue gelu
+    python tests/profile_cases.py gemv --m 1 --n 14336 --k 4096 --variant 1,4,4,4,0,0 --copies 3
+    python tests/profile_cases.py gemm --m 2048 --n 14336 --k 4096 --variant 2,0,128,128,4,8 --epilogue gelu
 
 Each launch uses its own weight copy (copies x N x K bytes; keep it to a few hundred
 MB) so that every launch streams from HBM rather than L2.  Prints "ok" and exits 0.
@@ -14,8 +14,12 @@ import ctypes as C
 
 import torch
 
-from . import backend as tb
-from . import binding as B
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from torchlette_b200 import backend as tb  # noqa: E402
+from torchlette_b200 import binding as B  # noqa: E402
 
 
 def main():

@@ -26,7 +26,8 @@ GEMV_VARIANTS_HALF = GEMV_VARIANTS_F32 + [(1, 2, 8, 4, 1, 0), (1, 2, 4, 2, 1, 0)
                                           (1, 3, 4, 4, 0, 0), (1, 3, 2, 2, 0, 0), (1, 3, 8, 4, 0, 0),
                                           (1, 4, 4, 4, 0, 0), (1, 4, 2, 8, 0, 0), (1, 4, 16, 2, 0, 0),
                                           (1, 5, 6, 0, 0, 0), (1, 5, 4, 0, 0, 0),
-                                          (1, 6, 16, 32, 0, 0), (1, 6, 8, 64, 0, 0)]
+                                          (1, 6, 16, 32, 0, 0), (1, 6, 8, 64, 0, 0),
+                                          (1, 8, 8, 3, 2, 16), (1, 8, 8, 5, 2, 16), (1, 8, 8, 2, 1, 16), (1, 8, 8, 3, 2, 32)]
 
 
 def _out_to_f32(arr, dtype):

@@ -503,6 +503,16 @@ class CudaBackend:
             v = B.Variant(*choice)
             B.check(self._ctx, self._lib.tl_force_variant(self._ctx, C.byref(v)))
 
+    def setOption(self, name: str, value: int):
+        """Per-context setting by name (tl_set_option); the counterpart of the
+        reference's ENV accessor (src/core/env.ts:14-26)."""
+        B.check(self._ctx, self._lib.tl_set_option(self._ctx, name.encode(), int(value)))
+
+    def getOption(self, name: str) -> int:
+        v = C.c_int64()
+        B.check(self._ctx, self._lib.tl_get_option(self._ctx, name.encode(), C.byref(v)))
+        return int(v.value)
+
     def getQuantGemvDispatchCount(self) -> int:
         return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_QGEMV))
 

@@ -84,6 +84,8 @@ SIGNATURES = {
     "tl_last_error": (C.c_char_p, [_P]),
     "tl_ctx_stream": (_I32, [_P, C.POINTER(_P)]),
     "tl_device_sm_count": (_I32, [_P, C.POINTER(_I32)]),
+    "tl_set_option": (_I32, [_P, C.c_char_p, _I64]),
+    "tl_get_option": (_I32, [_P, C.c_char_p, C.POINTER(_I64)]),
     "tl_alloc": (_I32, [_P, _SZ, C.POINTER(_P)]),
     "tl_free": (_I32, [_P, _P]),
     "tl_upload": (_I32, [_P, _P, _P, _SZ]),

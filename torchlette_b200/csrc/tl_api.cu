@@ -1,5 +1,6 @@
 // Context, memory, counters, replay graphs, events, argument validation and the
 // quantized-matmul seam of libtlcuda.
+#include <cstdlib>
 #include <cstring>
 
 #include "tl_common.cuh"
@@ -101,12 +102,17 @@ int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx) {
     delete ctx;
     return tl_set_error(nullptr, TL_ERR_CUDA, "tl_ctx_create: stream: %s", cudaGetErrorString(e));
   }
-  if (cudaMalloc(&ctx->dev_status, sizeof(int)) != cudaSuccess || cudaMemset(ctx->dev_status, 0, sizeof(int)) != cudaSuccess) {
+  // one small block: the status word, then (from byte 64) the eight flag words of the timed
+  // weight prefetch, which start out raised ("no launch is streaming")
+  const uint32_t ones[8] = {1, 1, 1, 1, 1, 1, 1, 1};
+  if (cudaMalloc(&ctx->dev_status, 128) != cudaSuccess || cudaMemset(ctx->dev_status, 0, 128) != cudaSuccess ||
+      cudaMemcpy(reinterpret_cast<uint8_t*>(ctx->dev_status) + 64, ones, sizeof(ones), cudaMemcpyHostToDevice) != cudaSuccess) {
     cudaGetLastError();
     cudaStreamDestroy(ctx->stream);
     delete ctx;
     return tl_set_error(nullptr, TL_ERR_OOM, "tl_ctx_create: cannot allocate the device status word");
   }
+  ctx->pf_flags = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctx->dev_status) + 64);
   *out_ctx = ctx;
   return TL_OK;
 }
@@ -119,6 +125,7 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->zscratch) cudaFree(ctx->zscratch);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
+  if (ctx->stream_scratch) cudaFree(ctx->stream_scratch);
   for (int r = 0; r < tl_ctx::kMaxPeers; ++r)
     if (ctx->p2p_peer[r] && ctx->p2p_peer[r] != ctx->p2p_local) cudaIpcCloseMemHandle(ctx->p2p_peer[r]);
   if (ctx->p2p_local) cudaFree(ctx->p2p_local);
@@ -158,6 +165,27 @@ int32_t tl_device_sm_count(tl_ctx* ctx, int32_t* out_sms) {
   TL_CHECK_CTX(ctx);
   if (!out_sms) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_device_sm_count: null out pointer");
   *out_sms = ctx->sm_count;
+  return TL_OK;
+}
+
+int32_t tl_set_option(tl_ctx* ctx, const char* name, int64_t value) {
+  TL_CHECK_CTX(ctx);
+  if (!name) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: null name");
+  if (!strcmp(name, "wait_limit_polls")) {
+    if (value < 1 || value > (int64_t(1) << 30))
+      return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: wait_limit_polls outside [1, 2^30]");
+    ctx->wait_limit_polls = int(value);
+  } else {
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: unknown option '%s'", name);
+  }
+  return TL_OK;
+}
+
+int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value) {
+  TL_CHECK_CTX(ctx);
+  if (!name || !out_value) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: null argument");
+  if (!strcmp(name, "wait_limit_polls")) *out_value = ctx->wait_limit_polls;
+  else return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: unknown option '%s'", name);
   return TL_OK;
 }
 

@@ -50,6 +50,14 @@ struct tl_ctx {
   void* zscratch = nullptr;
   size_t zscratch_bytes = 0;
   int* dev_status = nullptr;  // written by kernels whose bounded waits ran out; read back by tl_sync
+  // drain-timed ring fill of the streaming GEMV (tl_qgemv_stream.cu): flag words on the device
+  // and the slot the next launch takes; stream_scratch holds the partial sums and arrival
+  // counters of row tiles that two CTAs share (fixed size, allocated once)
+  uint32_t* pf_flags = nullptr;
+  int pf_next = 0;
+  int pf_last_grid = 0;
+  void* stream_scratch = nullptr;
+  int wait_limit_polls = 1 << 26;  // bound of one device-side wait of the peer collectives
   // selection
   bool has_forced = false;
   tl_variant forced{};
@@ -167,6 +175,13 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
                         const void* packed, const void* scales, void* out, int32_t out_dtype,
                         int64_t m, int64_t n, int64_t k, const tl_quant_desc& q,
                         const EpiParams& epi, tl_plan_receipt* receipt_only);
+bool tl_qgemv_stream_applicable(const tl_variant& v, int64_t m, int64_t k, int32_t a_dtype, const tl_quant_desc& q);
+void tl_qgemv_stream_geometry(tl_ctx* ctx, const tl_variant& v, int32_t m, int64_t tiles, int64_t k, int* grid, int* block,
+                              size_t* smem);
+int32_t tl_launch_qgemv_stream(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t a_dtype, int32_t n_items,
+                               const void* const* packed, const void* const* scales, void* const* out, const int64_t* n,
+                               const struct EpiParams* epi, int32_t out_dtype, int32_t m, int64_t k,
+                               const tl_quant_desc& q, tl_plan_receipt* receipt_only);
 int32_t tl_qgemv_default_variant(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q, tl_variant* out);
 int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_t a_dtype,

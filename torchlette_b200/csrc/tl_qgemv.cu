@@ -28,16 +28,21 @@
 //   3 "sk"     persistent grid, the weight dealt out to warps in equal contiguous
 //              shares of 8-row x 128-byte units; partial tiles meet in an f32
 //              scratch.  f16/bf16 activations, K % 128 == 0, G % 128 == 0.
+//   8 "stream" persistent warp-specialised kernel (tl_qgemv_stream.cu): bulk-copy producers, MMA
+//              consumers, an epilogue warp; two launches resident per SM with a drain-timed
+//              ring fill.  p0 = consumer warps (8), p1 = ring stages, p2 = producer warps,
+//              p3 = k blocks per stage (16 or 32).
 // Variant parameters: p0 = warps per CTA (sk: CTAs per SM), p1 = rows per warp
 // (simt) / k blocks in flight (mma, sk, ring), p2 = see ring, p3 = reserved.
 #include <algorithm>
 
 #include "tl_common.cuh"
+#include "tl_mma_frag.cuh"
 #include "tl_tma.cuh"
 
 namespace {
 
-constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4, kTma = 5, kBulk = 6, kChain = 7;
+constexpr int kScalar = 0, kSimt = 1, kMma = 2, kSk = 3, kRing = 4, kTma = 5, kBulk = 6, kChain = 7, kStream = 8;
 
 // geometry of the "bulk" kernel for a given k: tiles per stage, stage bytes, stages, warps per tile
 struct BulkGeom { int rt, nstages, p; uint32_t stage_bytes; size_t smem; bool ok; };
@@ -276,45 +281,6 @@ __global__ void __launch_bounds__(256) qgemv_simt_kernel(GemvArgs p, EpiParams e
 // B for MMA j: halves [4j, 4j+4) of the thread's 16 contiguous activations of
 // batch row g (columns of the MMA n dimension = batch rows).
 // ---------------------------------------------------------------------------
-template <typename AT> struct MmaOps;
-template <> struct MmaOps<__half> {
-  // bytes (b0,b1) / (b2,b3) of x = word ^ 0x80808080 -> f16 pairs holding q exactly:
-  // 0x6400 | u is 1024 + u; subtracting 1152 (0x6480) leaves u - 128 = q.
-  __device__ static void cvt(uint32_t word, uint32_t& lo, uint32_t& hi) {
-    const uint32_t x = word ^ 0x80808080u;
-    uint32_t l = __byte_perm(x, 0x64646464u, 0x4140);
-    uint32_t h = __byte_perm(x, 0x64646464u, 0x4342);
-    const uint32_t magic = 0x64806480u;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(lo) : "r"(l), "r"(magic));
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(hi) : "r"(h), "r"(magic));
-  }
-  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                             uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-};
-template <> struct MmaOps<__nv_bfloat16> {
-  // bf16 keeps 8 significant bits, so the byte cannot be stuffed whole.  With s the
-  // sign bit and l the low 7 bits of the raw byte, q = l - 128*s:
-  // (0x4300 | l) is 128 + l and (0x4300 | s<<7) is 128 or 256; their difference is q.
-  __device__ static void cvt(uint32_t word, uint32_t& lo, uint32_t& hi) {
-    const uint32_t l = __byte_perm(word, 0u, 0x4140);  // [b0,0,b1,0]
-    const uint32_t h = __byte_perm(word, 0u, 0x4342);
-    const uint32_t lm = (l & 0x007f007fu) | 0x43004300u, lc = (l & 0x00800080u) | 0x43004300u;
-    const uint32_t hm = (h & 0x007f007fu) | 0x43004300u, hc = (h & 0x00800080u) | 0x43004300u;
-    asm("sub.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(lm), "r"(lc));
-    asm("sub.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(hm), "r"(hc));
-  }
-  __device__ static void mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
-                             uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-  }
-};
-
 constexpr int kMmaMaxWarps = 16;
 
 // NT = number of 8-wide batch tiles (1: m <= 8, 2: m <= 16); UNROLL k blocks in flight per warp.
@@ -1685,6 +1651,7 @@ bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
   if (v.family != TL_FAMILY_QGEMV || m < 1 || m > 16) return false;
   if (v.p0 < 1 || v.p0 > kMmaMaxWarps) return false;
   switch (v.kernel) {
+    case kStream: return tl_qgemv_stream_applicable(v, m, k, a_dtype, q);
     case kScalar: return v.p0 <= 8;
     case kSimt: return v.p0 <= 8 && k % 16 == 0 && q.group_size % 16 == 0 && (v.p1 == 1 || v.p1 == 2 || v.p1 == 4);
     case kMma:
@@ -1742,6 +1709,12 @@ int32_t tl_qgemv_candidates(tl_ctx* ctx, int32_t m, int64_t n, int64_t k, int32_
       if (o.kernel == v.kernel && o.p0 == v.p0 && o.p1 == v.p1 && o.p2 == v.p2) return;
     out->push_back(v);
   };
+  for (int st : {3, 5}) {
+    tl_variant v{};
+    v.family = TL_FAMILY_QGEMV; v.kernel = kStream; v.p0 = 8; v.p1 = st; v.p2 = 2; v.p3 = st == 3 ? 32 : 16;
+    if (m > 8 && st == 3) continue;  // two token tiles double the fragment buffers: 16-block stages only
+    if (tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q)) out->push_back(v);
+  }
   for (int w : {8, 16})
     for (int kb : {32, 64}) add(kBulk, w, kb);
   for (int st : {4, 6}) add(kTma, st, 0);
@@ -1771,6 +1744,13 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q))
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "qgemv: variant %s cannot run m=%d n=%lld k=%lld G=%d %s",
                         tl_variant_name(&v), m, (long long)n, (long long)k, q.group_size, tl_dtype_name(a_dtype));
+  if (v.kernel == kStream) {
+    const void* pk[1] = {packed};
+    const void* sc[1] = {scales};
+    void* ot[1] = {out};
+    const int64_t nn[1] = {n};
+    return tl_launch_qgemv_stream(ctx, v, a, a_dtype, 1, pk, sc, ot, nn, &epi, out_dtype, m, k, q, receipt);
+  }
   GemvArgs p{};
   p.a = a; p.packed = reinterpret_cast<const uint32_t*>(packed); p.scales = scales; p.out = out;
   p.m = m; p.n = int32_t(n); p.k = int32_t(k);

@@ -123,10 +123,15 @@ class DecodeStack:
         sh = plan_shard(mode, n, k, k, self.rank, self.world)
         p = _Proj()
         p.name, p.k, p.n, p.mode = name, sh.k, sh.n, mode
-        # every rank draws its own shard; the full matrix is never materialised
-        gen.manual_seed(seed * 64 + self.rank)
-        p.w = torch.randint(-127, 128, (sh.n, sh.k), dtype=torch.int8, device=self.dev, generator=gen)
-        p.s = torch.empty(sh.n, dtype=torch.float32, device=self.dev).uniform_(0.001, 0.01, generator=gen)
+        # Every rank draws the FULL [N, K] matrix and its scales from the projection's seed (the
+        # device generator gives the same stream on every GPU) and keeps its own slice, so a stack
+        # sharded over g ranks is the same model as the single-GPU stack with that seed.
+        gen.manual_seed(seed)
+        full = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=self.dev, generator=gen)
+        scales = torch.empty(n, dtype=torch.float32, device=self.dev).uniform_(0.001, 0.01, generator=gen)
+        p.w = full[sh.n_offset:sh.n_offset + sh.n, sh.k_offset:sh.k_offset + sh.k].contiguous()
+        p.s = scales[sh.n_offset:sh.n_offset + sh.n].contiguous()
+        del full, scales
         # silu(gate) roughly halves the rms at unit amplitude but is linear at large amplitude, and the
         # stack has no normalisation between layers: 1.6 keeps the hidden state inside the f16 range
         # over 36 layers (1.8 let it grow to ~3e4, half of the f16 maximum)
@@ -243,27 +248,35 @@ class DecodeStack:
             B.check(self.ctx, self.lib.tl_qgemv_chain_launch(self.ctx, self._chain))
             return
         x = self.x
-        gather = self.tp_mode == "gather" and self.world > 1
         for projs in self.layers:
-            pq, pk, pv, po, pg, pu, pd = projs
-            self._run_batched((pq, pk, pv), x, (self.q, self.kk, self.v))
-            o_in = self.q
-            if gather:
-                self._allgather(self.q, self.q_full, self.adt)
-                self._slice_cols(self.q_full, self.q_slice)
-                o_in = self.q_slice
-            self._run_row_parallel(po, o_in, self.h1)
-            self._run_batched((pg, pu), self.h1, (self.g, self.u))
-            d_in = self.g
-            if gather:
-                self._allgather(self.g, self.g_full, self.adt)
-                self._slice_cols(self.g_full, self.g_slice)
-                d_in = self.g_slice
-            self._run_row_parallel(pd, d_in, self.h2)
-            x = self.h2
+            x = self._enqueue_layer(projs, x)
         self._run(self.lm_head, x, self.logits_local)
         if self.world > 1:
             self._allgather(self.logits_local, self.logits, B.TL_F32)
+
+    def _enqueue_layer(self, projs, x: torch.Tensor) -> torch.Tensor:
+        gather = self.tp_mode == "gather" and self.world > 1
+        pq, pk, pv, po, pg, pu, pd = projs
+        self._run_batched((pq, pk, pv), x, (self.q, self.kk, self.v))
+        o_in = self.q
+        if gather:
+            self._allgather(self.q, self.q_full, self.adt)
+            self._slice_cols(self.q_full, self.q_slice)
+            o_in = self.q_slice
+        self._run_row_parallel(po, o_in, self.h1)
+        self._run_batched((pg, pu), self.h1, (self.g, self.u))
+        d_in = self.g
+        if gather:
+            self._allgather(self.g, self.g_full, self.adt)
+            self._slice_cols(self.g_full, self.g_slice)
+            d_in = self.g_slice
+        self._run_row_parallel(pd, d_in, self.h2)
+        return self.h2
+
+    def run_layer(self, li: int):
+        """Enqueue layer ``li`` alone (input self.x for layer 0, else the current self.h2): the buffers
+        q/kk/v/h1/g/u/h2 then hold that layer's results, which a test checks projection by projection."""
+        self._enqueue_layer(self.layers[li], self.x if li == 0 else self.h2)
 
     def capture(self):
         """Run once eagerly (sizes scratch, warms caches), then capture the step
