@@ -407,6 +407,7 @@ def run_gpu(args):
     chained = stack.uses_chain()
     if args.autotune:
         shapes = sorted({(cfg.batch, p.n, p.k) for p in stack.layers[0]} | {(cfg.batch, stack.lm_head.n, stack.lm_head.k)})
+        be.setAutotuneEnabled(True)
         for (m, n, k) in shapes:
             be.pretuneMatmulShapes([(m, n, k)], cfg.act_dtype, cfg.act_dtype, tb.QuantPacking("int8-grouped", k, "f32", "direct"))
     if chained and args.chain_shape:

@@ -118,7 +118,8 @@ TL_API int32_t tl_device_sm_count(tl_ctx* ctx, int32_t* out_sms);
 /* Per-context settings by name, the analogue of the reference's single ENV accessor
  * (src/core/env.ts:14-26).  Unknown names return TL_ERR_INVALID_ARG.
  *   "wait_limit_polls"       upper bound of the polls of one bounded device-side wait of the
- *                            peer collectives (default 2^26). */
+ *                            peer collectives (default 2^26; the fused GEMV + all-reduce caps it
+ *                            at 2^22). */
 TL_API int32_t tl_set_option(tl_ctx* ctx, const char* name, int64_t value);
 TL_API int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value);
 
@@ -206,15 +207,15 @@ TL_API int32_t tl_qgemv_chain_launch(tl_ctx* ctx, tl_chain* chain);
 TL_API int32_t tl_qgemv_chain_destroy(tl_ctx* ctx, tl_chain* chain);
 
 /* No counterpart in the reference.  Same operation and arguments as tl_qgemv_nt for
- * hosts that must not allocate device memory at call time (a stream capture is open,
- * all memory belongs to the host's own pool, or cudaMalloc's device-wide
- * synchronisation cannot be tolerated): the kernel's partial-sum scratch is a fixed
+ * hosts that must not allocate device memory at call time (all device memory belongs
+ * to the host's own pool, so a library's cudaMalloc can only fail; or cudaMalloc's
+ * device-wide synchronisation cannot be tolerated): the kernel's partial-sum scratch is a fixed
  * 4 MiB array inside the library image instead of a buffer grown with cudaMalloc, so
  * the call makes no allocation.  Limits: f16/bf16 activations, K % 128 == 0,
  * group_size % 64 == 0, and m*n*4 + ceil(n/256)*64 <= 4 MiB (else TL_ERR_UNSUPPORTED).
  * All calls on a device share the array: calls ordered on one stream are safe, calls
- * that overlap on the GPU race.  The first call on a device looks up the array's
- * address; make it before any stream capture starts. */
+ * that overlap on the GPU race.  The first call on a device also looks up the array's
+ * address (a one-time set-up step); make that call before any stream capture starts. */
 TL_API int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
                                           const void* scales, void* out, int32_t out_dtype, int32_t m,
                                           int64_t n, int64_t k, const tl_quant_desc* qdesc, float alpha,
@@ -308,6 +309,10 @@ TL_API int32_t tl_tune_import_json(tl_ctx* ctx, const char* json);
 
 /* ---- replay: the analogue of the reference's CompiledPlan replay
  * (src/executor/executor.ts:1249) is a captured CUDA graph of enqueued calls. */
+/* A captured graph keeps the addresses of the library's scratch buffers of its capture time.  A
+ * later call that needs more scratch allocates a new buffer; the old one stays allocated for as
+ * long as any graph of the context is alive, so earlier graphs remain valid to replay.  Growing
+ * the scratch DURING a capture is refused (run the call once before capturing). */
 typedef struct tl_graph tl_graph;
 TL_API int32_t tl_graph_begin(tl_ctx* ctx);
 TL_API int32_t tl_graph_end(tl_ctx* ctx, tl_graph** out_graph);
@@ -352,6 +357,19 @@ TL_API int32_t tl_allreduce_sum(tl_ctx* ctx, void* buf, int64_t count, int32_t d
 TL_API int32_t tl_p2p_create(tl_ctx* ctx, size_t max_bytes, void* out_handle64);
 TL_API int32_t tl_p2p_attach(tl_ctx* ctx, const void* handles_world_x64);
 TL_API int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype);
+/* After a wait of a peer collective ran out (tl_sync returned TL_ERR_TIMEOUT) the ranks disagree
+ * on call counts and the exchange is unusable: every rank must call tl_p2p_reset (it waits for the
+ * context's stream, then clears flags, call counters and the status word of ITS buffer), and the
+ * host must put a barrier between the resets and the next peer collective.  No counterpart in the
+ * reference. */
+TL_API int32_t tl_p2p_reset(tl_ctx* ctx);
+/* Diagnostic hook: maps this rank's OWN exchange buffer in place of every peer of a `world`-rank
+ * group (rank 0), so that a single process can run the peer kernels on local memory only.  The
+ * other ranks' flags are then never raised: a peer collective waits until the context's
+ * "wait_limit_polls" is used up and gives up, which is how the time-out path is tested without
+ * a second GPU and without a rank that has to be killed.  Needs tl_p2p_create; not for contexts that
+ * called tl_comm_init. */
+TL_API int32_t tl_p2p_attach_loopback(tl_ctx* ctx, int32_t world);
 
 /* Row-parallel projection fused with its all-reduce (tensor parallelism; no counterpart in
  * the reference): out[m, n] = sum over ranks of alpha * a_r[m, k_r] . W_r[n, k_r]^T in ONE

@@ -116,7 +116,9 @@ ORC_API int orc_quantize_linear_weight(const float* weight, int64_t n, int64_t k
       double inv = scale > 0 ? 127.0 / scale : 0.0;
       for (int64_t j = 0; j < group; j++) {
         double r = js_math_round((double)weight[g_base + j] * inv);
-        double q = fmax(-127.0, fmin(127.0, r));
+        /* Math.min / Math.max propagate NaN (C's fmin / fmax would drop it), and `NaN & 0xff`
+         * is 0 (:121-126): a NaN weight, or Inf * 0 under an infinite group scale, packs 0. */
+        double q = isnan(r) ? 0.0 : fmax(-127.0, fmin(127.0, r));
         int32_t qi = (int32_t)q;
         int64_t k_idx = g * group + j;
         int64_t word = row * words_per_row + (k_idx >> 2);

@@ -184,3 +184,112 @@ def test_p2p_allreduce_and_nccl_wrappers_two_gpus():
     assert same is True, "ranks disagree bit-wise on an all-reduce result"
     assert errs == 0
     assert all(p.exitcode == 0 for p in procs)
+
+
+# ---------------------------------------------------------------------------
+# The tensor-parallel decode stack against the oracle and against the single-GPU stack
+# ---------------------------------------------------------------------------
+
+def _stack_rank_main(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from oracle import oracle as orc
+    from torchlette_b200 import backend as tb
+    from torchlette_b200 import binding as B
+    from torchlette_b200.decode_stack import TINY, DecodeStack
+
+    def f16(x):
+        return np.asarray(x, dtype=np.float32).astype(np.float16).astype(np.float32)
+
+    try:
+        torch.cuda.set_device(rank)
+        B.preload_nccl()
+        be = tb.CudaBackend(rank)
+        lib, ctx = be._lib, be._ctx
+        ident = [None]
+        if rank == 0:
+            buf = (C.c_char * B.TL_COMM_ID_BYTES)()
+            B.check(None, lib.tl_comm_unique_id(buf))
+            ident[0] = bytes(buf)
+        dist.broadcast_object_list(ident, src=0)
+        B.check(ctx, lib.tl_comm_init(ctx, rank, world, (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])))
+        hbuf = (C.c_char * 64)()
+        B.check(ctx, lib.tl_p2p_create(ctx, TINY.batch * TINY.hidden * 4, hbuf))
+        handles = [None] * world
+        dist.all_gather_object(handles, bytes(hbuf))
+        B.check(ctx, lib.tl_p2p_attach(ctx, (C.c_char * (64 * world)).from_buffer_copy(b"".join(handles))))
+        dist.barrier()
+        dev = torch.device("cuda", rank)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(11)
+        x = torch.randn(TINY.batch, TINY.hidden, device=dev, generator=gen).to(torch.float16)
+        # the oracle and the single-GPU stack: the SAME model (same seed), whole on this GPU
+        single = DecodeStack(be, TINY, 0, 1, seed=3)
+        single.x.copy_(x)
+        torch.cuda.synchronize(dev)
+        single.enqueue_step()
+        be.sync()
+        h = x.float().cpu().numpy()
+        for pq, pk, pv, po, pg, pu, pd in single.layers:
+            def proj(a, p):
+                w = p.w.cpu().numpy().astype(np.float32) * p.s.cpu().numpy().astype(np.float32)[:, None]
+                return orc.linear_reference(a, w, None, p.act, alpha=p.alpha)
+            h = f16(proj(f16(proj(f16(proj(f16(proj(h, pq)), po)), pg)), pd))
+        w = single.lm_head.w.cpu().numpy().astype(np.float32) * single.lm_head.s.cpu().numpy().astype(np.float32)[:, None]
+        ref = orc.linear_reference(h, w, None, None, alpha=single.lm_head.alpha)
+        one_gpu = single.logits.float().cpu().numpy()
+        rel = lambda a, b: float(np.max(np.abs(a - b) / np.maximum(1.0, np.abs(b))))  # noqa: E731
+        assert rel(one_gpu, ref) <= 2e-2
+        report = {}
+        for tp_mode in ("chained", "gather"):
+            for allreduce in ("p2p", "fused", "nccl"):
+                st = DecodeStack(be, TINY, rank, world, tp_mode, seed=3, allreduce=allreduce)
+                st.x.copy_(x)
+                torch.cuda.synchronize(dev)
+                dist.barrier()
+                st.capture()          # an eager step, then the captured one
+                for _ in range(2):    # replays
+                    st.step()
+                be.sync()
+                got = st.logits.float().cpu().numpy()
+                assert got.shape == ref.shape
+                assert rel(got, ref) <= 2e-2, (tp_mode, allreduce, rel(got, ref))
+                assert rel(got, one_gpu) <= 2e-2, (tp_mode, allreduce)
+                report[(tp_mode, allreduce)] = (st.logits.cpu().numpy().tobytes(), st.h2.cpu().numpy().tobytes())
+                dist.barrier()
+                st.destroy()
+        single.destroy()
+        allrep = [None] * world
+        dist.all_gather_object(allrep, report)
+        if rank == 0:
+            same = all(allrep[0][k] == allrep[r][k] for r in range(world) for k in allrep[0])
+            q.put(("ok", same, be.getGpuUncapturedErrorCount()))
+        dist.barrier()
+        lib.tl_comm_destroy(ctx)
+        be.destroy()
+    except Exception as e:
+        if rank == 0:
+            q.put(("error", repr(e), -1))
+        raise
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_stack_matches_oracle_and_single_gpu():
+    """The tiny stack sharded over two GPUs, both hand-over modes and all three row-parallel sums:
+    logits against the CPU oracle and against the unsharded stack with the same seed (<= 2e-2, the
+    single-GPU tiny-stack gate), logits and final hidden state bit-identical on both ranks."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_stack_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    status, same, errs = q.get(timeout=600)
+    for p in procs:
+        p.join(timeout=120)
+    assert status == "ok", same
+    assert same is True, "ranks disagree bit-wise on the sharded stack's outputs"
+    assert errs == 0
+    assert all(p.exitcode == 0 for p in procs)

@@ -472,6 +472,50 @@ def test_forced_variant_must_be_applicable(backend):
 # replay (captured graph) and counters
 # ---------------------------------------------------------------------------
 
+def test_captured_graph_survives_scratch_growth():
+    """A graph captured on a kernel that uses library scratch (the TMA-fed GEMV's partial-sum
+    meeting point) must stay valid when a later, larger call makes the scratch grow: the old buffer
+    is retired, not freed, while the graph lives."""
+    be = tb.CudaBackend(0)  # its own context: the scratch starts at its minimum size
+    try:
+        tma = (1, 5, 6, 0, 0, 0)
+        pc = lambda kk: tb.QuantPacking("int8-grouped", kk, "f32", "direct")  # noqa: E731
+        n, k, m = 512, 1024, 4
+        cs = cases.per_channel_case(n, k, m, seed=21, act_dtype="f16")
+        w = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, tb.perChannelFormat(k))
+        x = be.ops.tensorFromArray(cs["x_bits"], [m, k], "f16")
+        out = be.ops.empty([m, n], "f32")
+        be.forceVariant(tma)
+        be.dispatchQuantizedGemvNT(x, w, w.scales, out, n, k, k, m=m, packing=pc(k))  # eager: sizes the scratch (1 MiB minimum)
+        first = np.array(be.ops.read(out), dtype=np.float32)
+        ref = orc.linear_reference(cs["x"], orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k), None, None)
+        assert cases.rel_err(first, ref) <= TOL_F32
+        be.beginCapture()
+        be.dispatchQuantizedGemvNT(x, w, w.scales, out, n, k, k, m=m, packing=pc(k))
+        graph = be.endCapture()
+        # a larger problem on the same variant: m*n*4 bytes of partial sums exceed 1 MiB -> the scratch grows
+        n_big, kb = 80_000, 128
+        cb = cases.per_channel_case(n_big, kb, 4, seed=22, act_dtype="f16")
+        wb = be.createQuantizedWeight(cb["packed"], cb["scales"], n_big, kb, tb.perChannelFormat(kb))
+        xb = be.ops.tensorFromArray(cb["x_bits"], [4, kb], "f16")
+        outb = be.ops.empty([4, n_big], "f32")
+        be.dispatchQuantizedGemvNT(xb, wb, wb.scales, outb, n_big, kb, kb, m=4, packing=pc(kb))
+        refb = orc.linear_reference(cb["x"], orc.dequantize_direct_f32(cb["packed"], cb["scales"], kb, kb), None, None)
+        assert cases.rel_err(be.ops.read(outb), refb) <= TOL_F32
+        # the earlier graph still runs on its own (retired) scratch and gives the same bits
+        for _ in range(2):
+            be._upload(out.buffer, np.zeros((m, n), dtype=np.float32))
+            be.replay(graph)
+            assert np.array_equal(np.array(be.ops.read(out), dtype=np.float32), first)
+        be.forceVariant(None)
+        be.destroyGraph(graph)
+        for t in (outb, xb, wb.scales, wb, out, x, w.scales, w):
+            t.destroy()
+        assert be.getGpuUncapturedErrorCount() == 0
+    finally:
+        be.destroy()
+
+
 def test_graph_replay_matches_eager_and_counts(backend):
     """The reference's compiled plans engage on the 2nd+ run (probe-quant-compiled.ts
     loops 12 iterations at N=2048, K=2304, G=64, seed 0x93, w = rng()*0.05, drift <= 5e-3)."""
@@ -516,6 +560,11 @@ def test_autotune_cache_semantics(backend):
     default = be.planQuantizedMatmul(1, 2048, 1024, "f16", "f32", pk)
     assert default["family"] == "gemv" and not default["fromTuningCache"]
     runs = be.getAutotuneRunCount()
+    # pretune is a no-op until autotuning is switched on (dispatch.ts:557-562)
+    assert not be.isAutotuneEnabled()
+    be.pretuneMatmulShapes([(1, 2048, 1024)], "f16", "f32", pk)
+    assert be.getAutotuneRunCount() == runs and be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) is None
+    be.setAutotuneEnabled(True)
     be.pretuneMatmulShapes([(1, 2048, 1024)], "f16", "f32", pk)
     assert be.getAutotuneRunCount() == runs + 1
     won = be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk)
@@ -542,7 +591,6 @@ def test_autotune_cache_semantics(backend):
     be.importTuningCache(text)
     assert be.getPerShapeMatmulChoice(1, 2048, 1024, "f16", pk) == (1, 1, 4, 2, 1, 0)
     be.clearPerShapeMatmulChoices()
-    be.setAutotuneEnabled(True)
     assert be.isAutotuneEnabled()
     be.setAutotuneEnabled(False)
     assert not be.isAutotuneEnabled()
@@ -552,7 +600,10 @@ def test_tuned_winner_still_matches_oracle(backend):
     be = backend
     n, k = 3072, 1024
     pk = tb.perChannelFormat(k).packing
+    be.setAutotuneEnabled(True)
     be.pretuneMatmulShapes([(1, n, k), (8, n, k)], "f16", "f32", pk)
+    be.setAutotuneEnabled(False)
+    assert be.getPerShapeMatmulChoice(1, n, k, "f16", pk) is not None
     for m in (1, 8):
         cs = cases.per_channel_case(n, k, m, seed=31 + m, act_dtype="f16")
         got, ref = _run_direct(be, cs, m, n, k, "f16", "f32")

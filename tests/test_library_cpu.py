@@ -47,6 +47,9 @@ def test_host_quantizer_bit_exact_vs_oracle(group):
     w[5, :group] = 0
     w[7, 3] = 1e-6  # tiny group values exercise the f16 subnormal branch
     w[7, :group] *= 1e-6
+    w[9, 2] = np.nan      # Math.min/Math.max propagate NaN and `NaN & 0xff` is 0: the byte is 0
+    w[11, 1] = np.inf     # infinite group scale: inv = 0, Inf * 0 = NaN -> 0, everything else 0 as well
+    w[13, 0] = -np.inf
     packed = np.zeros((96, 96), dtype=np.uint32)
     scales = np.zeros((96, 384 // group), dtype=np.uint16)
     rc = lib.tl_quantize_linear_weight(w.ctypes.data_as(C.c_void_p), 96, 384, group,
@@ -54,6 +57,11 @@ def test_host_quantizer_bit_exact_vs_oracle(group):
     assert rc == 0
     op, os_ = orc.quantize_linear_weight(w, group)
     assert np.array_equal(packed, op) and np.array_equal(scales, os_)
+    # known answers read off quantize.ts:100-126 for the non-finite rows
+    q = orc.unpack_int8(op, 384)
+    assert q[9, 2] == 0 and np.count_nonzero(q[9, :group]) > 0  # NaN is skipped by `a > absMax`, the rest quantizes
+    assert os_[11, 0] == 0x7C00 and not q[11, :group].any()
+    assert os_[13, 0] == 0x7C00 and not q[13, :group].any()
 
 
 def test_host_quantizer_large_threaded_matches_oracle():

@@ -139,6 +139,8 @@ SIGNATURES = {
     "tl_p2p_create": (_I32, [_P, _SZ, _P]),
     "tl_p2p_attach": (_I32, [_P, _P]),
     "tl_allreduce_sum_p2p": (_I32, [_P, _P, _P, _I64, _I32]),
+    "tl_p2p_reset": (_I32, [_P]),
+    "tl_p2p_attach_loopback": (_I32, [_P, _I32]),
 }
 
 

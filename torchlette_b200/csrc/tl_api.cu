@@ -26,7 +26,8 @@ int32_t tl_ensure_scratch(tl_ctx* ctx, size_t bytes, void** out) {
                           "call once before capturing", ctx->scratch_bytes, bytes);
     if (ctx->scratch) {
       TL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-      TL_CUDA(ctx, cudaFree(ctx->scratch));
+      if (ctx->live_graphs > 0) ctx->retired_scratch.push_back({ctx->scratch, ctx->scratch_bytes});  // a captured graph may still use it
+      else TL_CUDA(ctx, cudaFree(ctx->scratch));
       ctx->scratch = nullptr;
       ctx->scratch_bytes = 0;
     }
@@ -51,7 +52,8 @@ int32_t tl_ensure_zeroed_scratch(tl_ctx* ctx, size_t bytes, void** out) {
                           "call once before capturing", ctx->zscratch_bytes, bytes);
     if (ctx->zscratch) {
       TL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-      TL_CUDA(ctx, cudaFree(ctx->zscratch));
+      if (ctx->live_graphs > 0) ctx->retired_scratch.push_back({ctx->zscratch, ctx->zscratch_bytes});  // a captured graph may still use it
+      else TL_CUDA(ctx, cudaFree(ctx->zscratch));
       ctx->zscratch = nullptr;
       ctx->zscratch_bytes = 0;
     }
@@ -124,6 +126,7 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   cudaStreamSynchronize(ctx->stream);
   if (ctx->scratch) cudaFree(ctx->scratch);
   if (ctx->zscratch) cudaFree(ctx->zscratch);
+  for (auto& p : ctx->retired_scratch) cudaFree(p.first);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->stream_scratch) cudaFree(ctx->stream_scratch);
   for (int r = 0; r < tl_ctx::kMaxPeers; ++r)
@@ -144,6 +147,8 @@ int32_t tl_sync(tl_ctx* ctx) {
     // a bounded device-side wait ran out: the scratch may hold partial sums, so clear it
     cudaMemset(ctx->dev_status, 0, sizeof(int));
     if (ctx->zscratch) cudaMemset(ctx->zscratch, 0, ctx->zscratch_bytes);
+    for (auto& p : ctx->retired_scratch) cudaMemset(p.first, 0, p.second);  // older graphs' meeting points too
+    if (ctx->stream_scratch) cudaMemset(ctx->stream_scratch, 0, size_t(ctx->sm_count) * (2 * 2 * 128 * sizeof(float) + sizeof(unsigned)));
     ctx->async_errors++;
     return tl_set_error(ctx, TL_ERR_TIMEOUT, "tl_sync: a kernel gave up a bounded wait (device code %d)", status);
   }
@@ -331,6 +336,7 @@ int32_t tl_graph_end(tl_ctx* ctx, tl_graph** out_graph) {
     ctx->counters[i] = g_capture_base[i];
   }
   *out_graph = g;
+  ctx->live_graphs++;
   return TL_OK;
 }
 
@@ -351,6 +357,10 @@ int32_t tl_graph_destroy(tl_ctx* ctx, tl_graph* graph) {
   if (graph->exec) cudaGraphExecDestroy(graph->exec);
   if (graph->graph) cudaGraphDestroy(graph->graph);
   delete graph;
+  if (ctx->live_graphs > 0 && --ctx->live_graphs == 0) {
+    for (auto& p : ctx->retired_scratch) cudaFree(p.first);  // no graph can reference them any more
+    ctx->retired_scratch.clear();
+  }
   return TL_OK;
 }
 

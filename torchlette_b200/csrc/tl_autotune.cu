@@ -82,6 +82,10 @@ int32_t tl_pretune(tl_ctx* ctx, const tl_shape* shapes, int32_t n_shapes, int32_
   if (n_shapes < 0 || (n_shapes > 0 && !shapes) || !q)
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_pretune: null argument");
   if (ctx->capturing) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_pretune: not allowed during graph capture");
+  // pretuneMatmulShapes returns at once unless autotuning was switched on, by setAutotuneEnabled(true)
+  // or by TORCHLETTE_AUTOTUNE=1 (src/backend/webgpu/matmul/dispatch.ts:557-562)
+  const char* env = std::getenv("TORCHLETTE_AUTOTUNE");
+  if (!ctx->autotune_enabled && !(env && env[0] == '1')) return TL_OK;
   DeviceGuard guard(ctx->device);
   const bool debug = std::getenv("TORCHLETTE_DEBUG_AUTOTUNE") != nullptr;
   for (int32_t si = 0; si < n_shapes; ++si) {

@@ -176,7 +176,6 @@ int32_t tl_allreduce_sum(tl_ctx* ctx, void* buf, int64_t count, int32_t dtype) {
 namespace {
 constexpr int kP2PCtas = 8;
 constexpr int kP2PThreads = 512;
-constexpr int kP2PSpinLimit = 1 << 26;  // polls; seconds, not forever
 
 struct P2PArgs {
   void* base[tl_ctx::kMaxPeers];  // every rank's exchange buffer as mapped HERE (own = local)
@@ -186,6 +185,7 @@ struct P2PArgs {
   const void* src;
   void* dst;
   int* status;
+  int spin_limit;  // polls of one wait before it gives up (the context's wait_limit_polls)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(P2PArgs a) {
     const uint32_t* f = my_flags + (half * tl_ctx::kMaxPeers + tid) * kP2PCtas + cta;
     int spins = 0;
     while (int32_t(ld_acquire_sys(f) - epoch) < 0) {
-      if (++spins > kP2PSpinLimit) { ok_flag = 0; atomicExch(a.status, TL_ERR_TIMEOUT); break; }
+      if (++spins > a.spin_limit) { ok_flag = 0; atomicExch(a.status, TL_ERR_TIMEOUT); break; }
     }
   }
   __syncthreads();
@@ -359,6 +359,34 @@ int32_t tl_p2p_attach(tl_ctx* ctx, const void* handles) {
   return TL_OK;
 }
 
+int32_t tl_p2p_attach_loopback(tl_ctx* ctx, int32_t world) {
+  TL_CHECK_CTX(ctx);
+  if (!ctx->p2p_local) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: call tl_p2p_create first");
+  if (ctx->nccl_comm || ctx->p2p_attached)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: the context already has peers");
+  if (world < 2 || world > tl_ctx::kMaxPeers)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: world %d outside [2,%d]", world, tl_ctx::kMaxPeers);
+  for (int r = 0; r < world; ++r) ctx->p2p_peer[r] = ctx->p2p_local;  // every "peer" is this rank's own buffer
+  ctx->rank = 0;
+  ctx->world = world;
+  ctx->p2p_attached = true;
+  return TL_OK;
+}
+
+int32_t tl_p2p_reset(tl_ctx* ctx) {
+  TL_CHECK_CTX(ctx);
+  if (!ctx->p2p_local) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_reset: no exchange buffer");
+  DeviceGuard guard(ctx->device);
+  TL_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+  // flags, per-CTA epochs, and the fused kernel's tile epochs and arrival counters: everything but the slots
+  const size_t flags_off = 2 * size_t(tl_ctx::kMaxPeers) * ctx->p2p_max_bytes;
+  TL_CUDA(ctx, cudaMemset(reinterpret_cast<uint8_t*>(ctx->p2p_local) + flags_off, 0,
+                          tl_p2p_fused_slots_offset(ctx->p2p_max_bytes) - flags_off));
+  TL_CUDA(ctx, cudaMemset(ctx->dev_status, 0, sizeof(int)));
+  ctx->fused_tiles = 0;
+  return TL_OK;
+}
+
 int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype) {
   TL_CHECK_CTX(ctx);
   if (!src || !dst) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: null pointer");
@@ -379,7 +407,7 @@ int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t co
   P2PArgs a{};
   for (int r = 0; r < ctx->world; ++r) a.base[r] = ctx->p2p_peer[r];
   a.rank = ctx->rank; a.world = ctx->world; a.max_bytes = ctx->p2p_max_bytes; a.count = count;
-  a.src = src; a.dst = dst; a.status = ctx->dev_status;
+  a.src = src; a.dst = dst; a.status = ctx->dev_status; a.spin_limit = ctx->wait_limit_polls;
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(kP2PCtas);
   cfg.blockDim = dim3(kP2PThreads);

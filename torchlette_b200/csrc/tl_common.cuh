@@ -11,6 +11,7 @@
 #include <cstdio>
 #include <map>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/tlcuda.h"
@@ -49,6 +50,12 @@ struct tl_ctx {
   // the zeros themselves (partial-sum meeting point of the balanced GEMV)
   void* zscratch = nullptr;
   size_t zscratch_bytes = 0;
+  // Captured graphs have the scratch pointers of their capture time baked in.  While any tl_graph
+  // of this context is alive, a scratch buffer that has to grow is not freed but retired: it stays
+  // allocated (the old graphs keep replaying on it) until the last graph is destroyed or the
+  // context goes away.
+  int live_graphs = 0;
+  std::vector<std::pair<void*, size_t>> retired_scratch;
   int* dev_status = nullptr;  // written by kernels whose bounded waits ran out; read back by tl_sync
   // drain-timed ring fill of the streaming GEMV (tl_qgemv_stream.cu): flag words on the device
   // and the slot the next launch takes; stream_scratch holds the partial sums and arrival

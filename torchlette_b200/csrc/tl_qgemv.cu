@@ -606,8 +606,8 @@ struct PushArgs {
   uint64_t max_bytes;                // size of one slot
   void* dst;                         // [m, n] sum over ranks, in the output type
   int* status;
+  int spin_limit;                    // polls of one wait before it gives up (the context's wait_limit_polls)
 };
-constexpr int kPushSpinLimit = 1 << 22;  // polls of one thread; seconds, not forever
 __device__ __forceinline__ uint32_t push_ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -802,7 +802,7 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       const uint32_t want = uint32_t(q->world) * (push_epoch / 2 + 1);  // every use of (half, tile) adds `world` arrivals
       int spins = 0;
       while (int32_t(push_ld_acquire_sys(arrive_local) - want) < 0) {
-        if (++spins > kPushSpinLimit) { push_ok = 0; atomicExch(q->status, TL_ERR_TIMEOUT); break; }
+        if (++spins > q->spin_limit) { push_ok = 0; atomicExch(q->status, TL_ERR_TIMEOUT); break; }
       }
     }
     __syncthreads();
@@ -1913,11 +1913,10 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
 // must not allocate.
 //
 // tl_qgemv_nt may grow the context's partial-sum scratch with cudaMalloc the first
-// time a shape needs it.  That is unacceptable for a host that calls from inside a
-// region where device allocation is off limits: while a stream capture is open on
-// the device (cudaMalloc is not capturable and, in global capture mode, is an
-// error), inside a serving loop that has handed all device memory to its own pool,
-// or in a real-time path where the implicit device-wide synchronisation of
+// time a shape needs it.  That is unacceptable for a host that calls from a place
+// where device allocation is off limits: a serving process that has handed all
+// device memory to its own pool (a cudaMalloc from a library can only fail there),
+// or a latency-critical loop where the device-wide synchronisation hidden in
 // cudaMalloc/cudaFree would stall every other stream.  This entry point runs the
 // TMA-fed persistent kernel (variant "tma") with its partial-sum meeting point in a
 // fixed array that is part of the loaded module, so the call itself performs no
@@ -1934,8 +1933,8 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
 //     the same device) race on it and must be serialised by the caller.
 // The array's device address is looked up with cudaGetSymbolAddress the first time
 // the entry point is called on a device (the name of a __device__ array is only a
-// host-side handle, never a pointer a kernel may be given).  That first call should
-// therefore be made before any stream capture begins.
+// host-side handle, never a pointer a kernel may be given).  That first call on a
+// device therefore does a little set-up work and should come before any stream capture.
 // ---------------------------------------------------------------------------
 #define TL_STATIC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) unsigned char tl_static_scratch[TL_STATIC_SCRATCH_BYTES];
@@ -2851,6 +2850,7 @@ extern "C" int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_d
   PushArgs q{};
   for (int r = 0; r < ctx->world; ++r) q.base[r] = static_cast<uint8_t*>(ctx->p2p_peer[r]);
   q.rank = ctx->rank; q.world = ctx->world; q.max_bytes = ctx->p2p_max_bytes; q.dst = out; q.status = ctx->dev_status;
+  q.spin_limit = ctx->wait_limit_polls < (1 << 22) ? ctx->wait_limit_polls : (1 << 22);
   // widest CTA that keeps the launch in one wave at two resident CTAs per SM
   int warps = 4;
   for (int w : {16, 8})

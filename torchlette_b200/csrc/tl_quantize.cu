@@ -63,7 +63,8 @@ static void quantize_rows(const float* weight, int64_t row0, int64_t row1, int64
       const double inv = s > 0 ? 127.0 / s : 0.0;
       for (int32_t j = 0; j < group; ++j) {
         double q = round_half_up(double(wg[j]) * inv);
-        q = std::max(-127.0, std::min(127.0, q));
+        // JS Math.min/Math.max propagate NaN and `NaN & 0xff` is 0 (quantize.ts:115-126)
+        q = std::isnan(q) ? 0.0 : std::max(-127.0, std::min(127.0, q));
         bytes[g * group + j] = uint8_t(int8_t(int32_t(q)));
       }
     }
