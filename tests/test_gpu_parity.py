@@ -502,11 +502,13 @@ def test_captured_graph_survives_scratch_growth():
         be.dispatchQuantizedGemvNT(xb, wb, wb.scales, outb, n_big, kb, kb, m=4, packing=pc(kb))
         refb = orc.linear_reference(cb["x"], orc.dequantize_direct_f32(cb["packed"], cb["scales"], kb, kb), None, None)
         assert cases.rel_err(be.ops.read(outb), refb) <= TOL_F32
-        # the earlier graph still runs on its own (retired) scratch and gives the same bits
+        # the earlier graph still runs on its own (retired) scratch (this variant sums partial tiles
+        # with atomics, so replays agree to rounding, not bit for bit)
         for _ in range(2):
             be._upload(out.buffer, np.zeros((m, n), dtype=np.float32))
             be.replay(graph)
-            assert np.array_equal(np.array(be.ops.read(out), dtype=np.float32), first)
+            again = np.array(be.ops.read(out), dtype=np.float32)
+            assert cases.rel_err(again, ref) <= TOL_F32 and cases.rel_err(again, first) <= 1e-5
         be.forceVariant(None)
         be.destroyGraph(graph)
         for t in (outb, xb, wb.scales, wb, out, x, w.scales, w):
