@@ -372,7 +372,7 @@ def run_gpu(args):
         dist.broadcast_object_list(ident, src=0)
         idbuf = (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])
         B.check(ctx, lib.tl_comm_init(ctx, rank, world, idbuf))
-        if args.allreduce in ("p2p", "fused"):
+        if args.allreduce in ("p2p", "fused", "push"):
             # exchange buffers for the one-shot peer all-reduce: [batch, hidden] partial sums.
             # If any rank cannot map its peers (no peer access between some pair of GPUs), every
             # rank switches to the NCCL all-reduce and the JSON line says so.
@@ -402,7 +402,7 @@ def run_gpu(args):
             dist.barrier()
 
     cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
-    stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if (world > 1 and args.allreduce in ("p2p", "fused")) else "nccl",
+    stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if (world > 1 and args.allreduce in ("p2p", "fused", "push")) else "nccl",
                         fuse=not args.no_fuse, chain=args.step_launch == "chain")
     chained = stack.uses_chain()
     if args.autotune:
@@ -574,7 +574,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tp-mode", default="chained", choices=["chained", "gather"])
     ap.add_argument("--autotune", action="store_true")
-    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "fused", "nccl"],
+    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "fused", "push", "nccl"],
                     help="row-parallel sums: the library's one-shot peer-memory kernel (default, fastest measured), "
                          "the GEMV fused with its all-reduce (tl_qgemv_nt_allreduce), or NCCL")
     ap.add_argument("--step-launch", default="graph", choices=["chain", "graph"],

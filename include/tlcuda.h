@@ -367,8 +367,9 @@ TL_API int32_t tl_p2p_reset(tl_ctx* ctx);
  * group (rank 0), so that a single process can run the peer kernels on local memory only.  The
  * other ranks' flags are then never raised: a peer collective waits until the context's
  * "wait_limit_polls" is used up and gives up, which is how the time-out path is tested without
- * a second GPU and without a rank that has to be killed.  Needs tl_p2p_create; not for contexts that
- * called tl_comm_init. */
+ * a second GPU and without a rank that has to be killed.  With world = 1 the group is complete, and
+ * tl_qgemv_nt_push followed by its consumer runs the whole push / reduce-on-read path on one GPU
+ * (the sum has a single term).  Needs tl_p2p_create; not for contexts that called tl_comm_init. */
 TL_API int32_t tl_p2p_attach_loopback(tl_ctx* ctx, int32_t world);
 
 /* Row-parallel projection fused with its all-reduce (tensor parallelism; no counterpart in
@@ -385,6 +386,24 @@ TL_API int32_t tl_p2p_attach_loopback(tl_ctx* ctx, int32_t world);
 TL_API int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
                                      const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n,
                                      int64_t k, const tl_quant_desc* qdesc, float alpha);
+
+/* Row-parallel sum WITHOUT a collective launch (tensor parallelism; no counterpart in the
+ * reference).  tl_qgemv_nt_push computes this rank's partial product alpha * a_r . W_r^T exactly as
+ * tl_qgemv_nt would and, instead of storing it, pushes it -- rounded to out_dtype -- into every
+ * rank's exchange buffer over NVLink; it waits for nobody.  `out` names the local [m, n] buffer
+ * that is to hold the sum over ranks.  The NEXT small-batch launch on the context (tl_qgemv_nt,
+ * tl_qgemv_nt_batched or tl_qmatmul_nt with m <= 16) must be the one that reads `out` as its
+ * activations: after its weight prefetch it waits (bounded, TL_ERR_TIMEOUT at tl_sync) for all
+ * ranks' partials, sums them in rank order into `out` (identical bits on every rank) and then runs
+ * its own product.  Any other consumer calls tl_reduce_pending first, which does the same sum in a
+ * small launch of its own.  Needs tl_p2p_create / tl_p2p_attach with max_bytes >= m*n*4; m in
+ * [1,16]; f16/bf16 activations and outputs; K % 64 == 0; N % 16 == 0; no epilogue ops (alpha only:
+ * anything non-linear would have to follow the sum).  Collective: every rank makes the same calls
+ * in the same order.  With one rank (and no loopback exchange attached) it is tl_qgemv_nt. */
+TL_API int32_t tl_qgemv_nt_push(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed,
+                                const void* scales, void* out, int32_t out_dtype, int32_t m, int64_t n,
+                                int64_t k, const tl_quant_desc* qdesc, float alpha);
+TL_API int32_t tl_reduce_pending(tl_ctx* ctx);
 
 #ifdef __cplusplus
 }

@@ -242,7 +242,7 @@ def _stack_rank_main(rank, world, port, q):
         assert rel(one_gpu, ref) <= 2e-2
         report = {}
         for tp_mode in ("chained", "gather"):
-            for allreduce in ("p2p", "fused", "nccl"):
+            for allreduce in ("p2p", "fused", "push", "nccl"):
                 st = DecodeStack(be, TINY, rank, world, tp_mode, seed=3, allreduce=allreduce)
                 st.x.copy_(x)
                 torch.cuda.synchronize(dev)

@@ -140,6 +140,8 @@ SIGNATURES = {
     "tl_p2p_attach": (_I32, [_P, _P]),
     "tl_allreduce_sum_p2p": (_I32, [_P, _P, _P, _I64, _I32]),
     "tl_p2p_reset": (_I32, [_P]),
+    "tl_qgemv_nt_push": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F]),
+    "tl_reduce_pending": (_I32, [_P]),
     "tl_p2p_attach_loopback": (_I32, [_P, _I32]),
 }
 

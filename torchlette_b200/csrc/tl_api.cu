@@ -190,6 +190,8 @@ int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value) {
   TL_CHECK_CTX(ctx);
   if (!name || !out_value) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: null argument");
   if (!strcmp(name, "wait_limit_polls")) *out_value = ctx->wait_limit_polls;
+  else if (!strcmp(name, "p2p_buffer_address")) *out_value = int64_t(reinterpret_cast<uintptr_t>(ctx->p2p_local));
+  else if (!strcmp(name, "p2p_slot_bytes")) *out_value = int64_t(ctx->p2p_max_bytes);
   else return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: unknown option '%s'", name);
   return TL_OK;
 }

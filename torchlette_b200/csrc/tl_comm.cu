@@ -364,8 +364,8 @@ int32_t tl_p2p_attach_loopback(tl_ctx* ctx, int32_t world) {
   if (!ctx->p2p_local) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: call tl_p2p_create first");
   if (ctx->nccl_comm || ctx->p2p_attached)
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: the context already has peers");
-  if (world < 2 || world > tl_ctx::kMaxPeers)
-    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: world %d outside [2,%d]", world, tl_ctx::kMaxPeers);
+  if (world < 1 || world > tl_ctx::kMaxPeers)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_p2p_attach_loopback: world %d outside [1,%d]", world, tl_ctx::kMaxPeers);
   for (int r = 0; r < world; ++r) ctx->p2p_peer[r] = ctx->p2p_local;  // every "peer" is this rank's own buffer
   ctx->rank = 0;
   ctx->world = world;
@@ -382,8 +382,12 @@ int32_t tl_p2p_reset(tl_ctx* ctx) {
   const size_t flags_off = 2 * size_t(tl_ctx::kMaxPeers) * ctx->p2p_max_bytes;
   TL_CUDA(ctx, cudaMemset(reinterpret_cast<uint8_t*>(ctx->p2p_local) + flags_off, 0,
                           tl_p2p_fused_slots_offset(ctx->p2p_max_bytes) - flags_off));
+  // the push words AND its slots: their data carries epochs, which restart from zero
+  TL_CUDA(ctx, cudaMemset(reinterpret_cast<uint8_t*>(ctx->p2p_local) + tl_p2p_push_words_offset(ctx->p2p_max_bytes), 0,
+                          tl_p2p_total_bytes(ctx->p2p_max_bytes) - tl_p2p_push_words_offset(ctx->p2p_max_bytes)));
   TL_CUDA(ctx, cudaMemset(ctx->dev_status, 0, sizeof(int)));
   ctx->fused_tiles = 0;
+  ctx->push_pending = false;
   return TL_OK;
 }
 

@@ -83,6 +83,11 @@ struct tl_ctx {
   size_t p2p_max_bytes = 0;
   bool p2p_attached = false;
   int64_t fused_tiles = 0;  // tiles of the fused GEMV + all-reduce calls made on this context (0: none yet)
+  // a tl_qgemv_nt_push whose partial sums wait to be reduced by the next small-batch launch
+  bool push_pending = false;
+  void* push_dst = nullptr;
+  int32_t push_m = 0, push_dtype = 0;
+  int64_t push_n = 0, push_tiles = 0;
 };
 
 int32_t tl_set_error(tl_ctx* ctx, int32_t code, const char* fmt, ...);
@@ -162,8 +167,21 @@ __host__ __device__
 inline size_t tl_p2p_fused_slots_offset(size_t max_bytes) {
   return tl_p2p_fused_offset(max_bytes) + ((sizeof(uint32_t) * 3 * kP2PFusedMaxTiles + 255) & ~size_t(255));
 }
-inline size_t tl_p2p_total_bytes(size_t max_bytes) {
+// After the fused kernel's slots: the words of the push / reduce-on-read pair (tl_qgemv_nt_push and
+// the consuming launch): u32 arrive[2], done[2], epoch_p, epoch_c (256 bytes reserved), and ITS slots
+// [2 halves][kMaxPeers][max_bytes].
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline size_t tl_p2p_push_words_offset(size_t max_bytes) {
   return tl_p2p_fused_slots_offset(max_bytes) + 2 * size_t(tl_ctx::kMaxPeers) * max_bytes;
+}
+#ifdef __CUDACC__
+__host__ __device__
+#endif
+inline size_t tl_p2p_push_slots_offset(size_t max_bytes) { return tl_p2p_push_words_offset(max_bytes) + 256; }
+inline size_t tl_p2p_total_bytes(size_t max_bytes) {
+  return tl_p2p_push_slots_offset(max_bytes) + 2 * size_t(tl_ctx::kMaxPeers) * max_bytes;
 }
 
 bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, tl_variant* v);

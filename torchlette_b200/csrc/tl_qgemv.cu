@@ -624,12 +624,124 @@ __device__ __forceinline__ float push_load(const void* base, int dtype, int64_t 
   return __uint_as_float(uint32_t(bits) << 16);
 }
 
+// ---------------------------------------------------------------------------
+// Push / reduce-on-read: the row-parallel sum of tensor parallelism without a collective launch.
+//
+// tl_qgemv_nt_push (ring tile, PUSH == 2): every CTA rounds its 16-row tile of the LOCAL partial
+// product to the output type, stages it in shared memory and stores it into slot (half, rank) of
+// EVERY rank's exchange buffer as 8-byte words {two output values, epoch}.  An 8-byte store arrives
+// whole, so the epoch that travels with the data is the arrival signal: the producer needs no fence,
+// no atomic and no flag (a system-scope release per CTA, 256 per launch, cost 8 us; fences from
+// every thread 12 us), and it waits for nobody.
+//
+// The NEXT small-batch launch of every rank (the column-parallel q+k+v / gate+up / lm_head product,
+// which reads the summed vector as its activations) does the sum in its prologue, after
+// griddepcontrol.wait and with its weight prefetch already in flight: its first `nsum` CTAs each
+// take a slice of the vector, poll (bounded) the words of all ranks until they carry this push's
+// epoch, add them in rank order (every rank computes the same bits) into the activation buffer and
+// arrive on done[half]; all CTAs wait for `nsum` arrivals there (a grid-wide gate that can not
+// deadlock: the summing CTAs are the first of the grid) and then read the activations.  No
+// all-reduce kernel, no NCCL, and the NVLink trip runs under the consumer's weight prefetch.
+//
+// Words of a rank's exchange buffer (tl_p2p_push_words_offset): done[2] at words 2-3, epoch_p (4),
+// epoch_c (5).  Halves alternate per push (epoch_p & 1) so that a rank that is ahead overwrites the
+// half its peers no longer read.  The epochs live on the device (a replayed graph keeps counting):
+// the producer reads epoch_p and publishes epoch_c = epoch_p + 1, the consumer reads epoch_c and
+// publishes epoch_p = epoch_c.  A producer clears done[] of the OTHER half when it starts (its own
+// previous consumer has finished with it).  Slots are [2 halves][kMaxPeers][max_bytes] with
+// max_bytes >= m * n * 4 (every pair of 2-byte values carries a 4-byte epoch).
+// ---------------------------------------------------------------------------
+struct ReduceIn {
+  uint8_t* base;        // this rank's exchange buffer
+  uint64_t max_bytes;
+  void* dst;            // [m, n] summed vector = the consumer's activations
+  int32_t world, expected, nsum, count_vec;  // arrivals to wait for; summing CTAs; 16-byte vectors in m*n
+  int32_t dtype;        // TL_F16 or TL_BF16
+  int* status;
+  int32_t spin_limit;
+};
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void reduce_in_prologue(const ReduceIn& r) {
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  uint32_t* words = reinterpret_cast<uint32_t*>(r.base + tl_p2p_push_words_offset(r.max_bytes));
+  // published by the producer kernel, which has completed.  Read through L2: under programmatic
+  // dependent launch this CTA's SM may still hold the line from an overlapping earlier kernel.
+  const uint32_t epoch = __ldcv(words + 5);
+  const int half = int((epoch - 1u) & 1u);
+  if (int(blockIdx.x) < r.nsum) {
+    {
+      const uint8_t* slots = r.base + tl_p2p_push_slots_offset(r.max_bytes) + size_t(half) * tl_ctx::kMaxPeers * r.max_bytes;
+      const int per = (r.count_vec + r.nsum - 1) / r.nsum;
+      const int v0 = int(blockIdx.x) * per, v1 = min(v0 + per, r.count_vec);
+      for (int i = v0 + tid; i < v1; i += nthreads) {
+        // output vector i = 8 values = four {pair, epoch} words (32 bytes) of every rank's slot
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int rr = 0; rr < r.world; ++rr) {
+          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 2 * i;
+          uint4 u0, u1;
+          int spins = 0;
+          for (;;) {
+            u0 = __ldcv(src);
+            u1 = __ldcv(src + 1);
+            if (u0.y == epoch && u0.w == epoch && u1.y == epoch && u1.w == epoch) break;
+            if (++spins > r.spin_limit) { atomicExch(r.status, TL_ERR_TIMEOUT); break; }
+            __nanosleep(200);  // thousands of threads poll lines that a peer is writing: leave the L2 slice room
+          }
+          const uint32_t w[4] = {u0.x, u0.z, u1.x, u1.z};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (r.dtype == TL_F16) {
+              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+              acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
+            } else {
+              acc[2 * j] += __uint_as_float(w[j] << 16); acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
+            }
+          }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (r.dtype == TL_F16) {
+            const __half2 h = __floats2half2_rn(acc[2 * j], acc[2 * j + 1]);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+          } else {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+            o[j] = *reinterpret_cast<const uint32_t*>(&h);
+          }
+        }
+        __stcg(reinterpret_cast<uint4*>(r.dst) + i, make_uint4(o[0], o[1], o[2], o[3]));
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      atomicAdd(words + 2 + half, 1u);  // also after a time-out: nobody must wait for this CTA
+    }
+  }
+  if (tid == 0) {
+    int spins = 0;
+    while (int32_t(ld_acquire_gpu_u32(words + 2 + half) - uint32_t(r.nsum)) < 0) {
+      if (++spins > r.spin_limit) { atomicExch(r.status, TL_ERR_TIMEOUT); break; }
+      __nanosleep(64);  // hundreds of CTAs watch this word; the summing CTAs' arrivals must get through
+    }
+    if (blockIdx.x == 0) words[4] = epoch;  // the next push takes the other half
+  }
+  __syncthreads();
+}
+
 // MAXT / MINB: launch bounds.  The 4-warp configuration asks for 12 resident CTAs per SM
 // (<= 42 registers) so that, under programmatic dependent launch, the CTAs of the NEXT kernel
 // fit beside the 6-7 CTAs per SM of the running one and prefetch their weights early.
-template <typename AT, int NT, bool GROUPED, int S, bool PUSH = false>
+// PUSH: 0 plain store, 1 fused all-reduce (push, wait, sum), 2 push only (see above).  rin: the
+// launch first reduces a pending push into its activation buffer (null for every other launch;
+// the wrappers pass a literal, so the branch folds away).
+template <typename AT, int NT, bool GROUPED, int S, int PUSH = 0>
 __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& epi, int64_t tile_index, uint8_t* ring_raw,
-                                          const PushArgs* q = nullptr) {
+                                          const PushArgs* q = nullptr, const ReduceIn* rin = nullptr) {
   uint4* ring = reinterpret_cast<uint4*>(ring_raw);  // [S][2][blockDim.x]
   const int nthreads = blockDim.x, tid = threadIdx.x;
   float* red = reinterpret_cast<float*>(ring_raw + size_t(S) * 2 * nthreads * 16);  // [warps][NT][4][32]
@@ -673,6 +785,18 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   asm volatile("griddepcontrol.wait;" ::: "memory");
   TL_RT_MIN(trace_id, 2);
   TL_RT_MAX(trace_id, 3);
+  if (rin) reduce_in_prologue(*rin);  // the activations are written by CTAs of THIS grid: read them through L2
+  uint32_t push2_half = 0, push2_epoch = 0;
+  if (PUSH == 2) {
+    uint32_t* words = reinterpret_cast<uint32_t*>(q->base[q->rank] + tl_p2p_push_words_offset(q->max_bytes));
+    const uint32_t ep = __ldcv(words + 4);  // epoch_p: stable while this kernel runs (its consumer bumps it); read through L2
+    push2_half = ep & 1u;
+    if (blockIdx.x == 0 && tid == 0) {
+      words[2 + (push2_half ^ 1u)] = 0u;   // done[other half]
+      words[5] = ep + 1u;                  // epoch_c, read by the consumer after this kernel has completed
+    }
+    push2_epoch = ep + 1u;
+  }
 
   float total[NT][4];
 #pragma unroll
@@ -689,8 +813,10 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
           const uint4* src = reinterpret_cast<const uint4*>(a_col[nt] + int64_t(i) * kstride);
-          bx[nt][0] = __ldg(src);
-          bx[nt][1] = __ldg(src + 1);
+          // (written by CTAs of THIS grid before the gate: ordinary loads, never the non-coherent path;
+          // no line of the buffer can be in this SM's L1 yet, the gate comes before the first read)
+          bx[nt][0] = rin ? *src : __ldg(src);
+          bx[nt][1] = rin ? *(src + 1) : __ldg(src + 1);
         }
         cp_async_wait<S - 1>();
         const uint4 wl = ring[(2 * s) * nthreads + tid];
@@ -754,7 +880,8 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   // into slot (half, rank) of EVERY rank's exchange buffer instead of into p.out.
   uint32_t push_epoch = 0;
   uint32_t* push_words = nullptr;
-  if (PUSH) {
+  __shared__ __align__(16) uint16_t push_stage[16][16];  // PUSH == 2: [batch column][row of the tile], output type bits
+  if (PUSH == 1) {
     push_words = reinterpret_cast<uint32_t*>(q->base[q->rank] + tl_p2p_fused_offset(q->max_bytes));
     push_epoch = push_words[tile_index];  // owner-only counter; every thread reads it before thread 0 bumps it
   }
@@ -770,16 +897,33 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       float s = p.wscale;
       if (!GROUPED) s *= tl_load_scale(p.scales, p.scales_dtype, row);
       const float r = tl_apply_epilogue(epi, v * s, p.row0 + col, row, p.n);
-      if (PUSH) {
+      if (PUSH == 1) {
         for (int rr = 0; rr < q->world; ++rr)
           tl_store_out(q->base[rr] + tl_p2p_fused_slots_offset(q->max_bytes) + (size_t(push_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes, p.out_dtype,
                        int64_t(col) * p.n + row, r);
+      } else if (PUSH == 2) {
+        push_stage[col][row - tile_row] = p.out_dtype == TL_F16 ? __half_as_ushort(__float2half_rn(r))
+                                                                : __bfloat16_as_ushort(__float2bfloat16_rn(r));
       } else {
         tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
       }
     }
   }
-  if (PUSH) {
+  if (PUSH == 2) {
+    // the tile [m columns][16 rows] leaves as 8-byte words {two values, epoch}, one copy per peer
+    __syncthreads();
+    const int per_peer = p.m * 8;
+    for (int idx = tid; idx < per_peer * q->world; idx += nthreads) {
+      const int peer = idx / per_peer, v = idx - peer * per_peer, col = v >> 3, rp = v & 7;
+      const uint32_t pair = *reinterpret_cast<const uint32_t*>(&push_stage[col][2 * rp]);
+      uint8_t* slot = q->base[peer] + tl_p2p_push_slots_offset(q->max_bytes) +
+                      (size_t(push2_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes;
+      uint2* dst = reinterpret_cast<uint2*>(slot) + ((int64_t(col) * p.n + tile_row) >> 1) + rp;
+      // volatile (relaxed at system scope): a weak store to peer memory may be held back indefinitely
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pair), "r"(push2_epoch) : "memory");
+    }
+  }
+  if (PUSH == 1) {
     // One arrival per rank on the tile's counter (release at system scope, cumulative over the
     // barrier, so the pushes above are visible first); then wait -- bounded -- until all ranks'
     // versions of THIS tile have arrived here, and sum them in rank order: every rank computes
@@ -991,7 +1135,20 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring2_kernel(GemvArgs
 template <typename AT, int NT, bool GROUPED, int S>
 __global__ void __launch_bounds__(kMmaMaxWarps * 32, 2) qgemv_ring_allreduce_kernel(GemvArgs p, EpiParams epi, PushArgs q) {
   extern __shared__ __align__(16) uint8_t ring_smem[];
-  ring_tile<AT, NT, GROUPED, S, true>(p, epi, blockIdx.x, ring_smem, &q);
+  ring_tile<AT, NT, GROUPED, S, 1>(p, epi, blockIdx.x, ring_smem, &q);
+}
+
+// Row-parallel projection that only pushes its partial tiles to every rank (PUSH == 2).
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32, 2) qgemv_ring_push_kernel(GemvArgs p, EpiParams epi, PushArgs q) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  ring_tile<AT, NT, GROUPED, S, 2>(p, epi, blockIdx.x, ring_smem, &q);
+}
+// A launch that first reduces a pending push into its activations (reduce-on-read), one matrix.
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_rin_kernel(GemvArgs p, EpiParams epi, const __grid_constant__ ReduceIn rin) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  ring_tile<AT, NT, GROUPED, S, 0>(p, epi, blockIdx.x, ring_smem, nullptr, &rin);
 }
 
 // Horizontal fusion: up to four projections that read the SAME activations (q/k/v, gate/up) in
@@ -1009,6 +1166,15 @@ __global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_batched_kernel(c
   const int blk = int(blockIdx.x);
   const int i = (blk >= b.tile_start[1]) + (blk >= b.tile_start[2]) + (blk >= b.tile_start[3]);
   ring_tile<AT, NT, GROUPED, S>(b.p[i], b.e[i], blk - b.tile_start[i], ring_smem);
+}
+// the batched launch with the reduce-on-read prologue
+template <typename AT, int NT, bool GROUPED, int S>
+__global__ void __launch_bounds__(kMmaMaxWarps * 32) qgemv_ring_rin_batched_kernel(const __grid_constant__ RingBatchArgs b,
+                                                                                   const __grid_constant__ ReduceIn rin) {
+  extern __shared__ __align__(16) uint8_t ring_smem[];
+  const int blk = int(blockIdx.x);
+  const int i = (blk >= b.tile_start[1]) + (blk >= b.tile_start[2]) + (blk >= b.tile_start[3]);
+  ring_tile<AT, NT, GROUPED, S, 0>(b.p[i], b.e[i], blk - b.tile_start[i], ring_smem, nullptr, &rin);
 }
 // the same with 32-row tiles (tile_start counts 32-row tiles)
 template <typename AT, int NT, bool GROUPED, int S>
@@ -1645,6 +1811,10 @@ void launch_mma(bool grouped, int unroll, int grid, int block, cudaStream_t s, c
 
 }  // namespace
 
+bool tl_push_matches(tl_ctx* ctx, const void* a, int32_t a_dtype, int32_t m, int64_t k);
+int32_t tl_launch_qgemv_rin(tl_ctx* ctx, const void* a, int32_t a_dtype, const GemvArgs* items, const EpiParams* epis, int n_items,
+                            int32_t m, int64_t k, bool grouped);
+
 bool tl_qgemv_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q) {
   (void)n;
@@ -1744,6 +1914,22 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   if (!tl_qgemv_variant_applicable(v, m, n, k, a_dtype, q))
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "qgemv: variant %s cannot run m=%d n=%lld k=%lld G=%d %s",
                         tl_variant_name(&v), m, (long long)n, (long long)k, q.group_size, tl_dtype_name(a_dtype));
+  if (!receipt && ctx->push_pending) {
+    // a tl_qgemv_nt_push is waiting for its sum: this launch must be the one that reads it
+    if (!tl_push_matches(ctx, a, a_dtype, m, k) || k % 64 != 0 || q.group_size % 64 != 0 ||
+        (reinterpret_cast<uintptr_t>(packed) & 15))
+      return tl_set_error(ctx, TL_ERR_INVALID_ARG,
+                          "qgemv: a pushed partial sum is pending; the next small-batch launch must read it as its activations "
+                          "([m, k] = [%d, %lld]), or call tl_reduce_pending first", ctx->push_m, (long long)ctx->push_n);
+    GemvArgs pr{};
+    pr.a = a; pr.packed = reinterpret_cast<const uint32_t*>(packed); pr.scales = scales; pr.out = out;
+    pr.m = m; pr.n = int32_t(n); pr.k = int32_t(k);
+    pr.group = q.group_size; pr.groups_per_row = int32_t(k / q.group_size);
+    pr.scales_dtype = q.scales_dtype; pr.out_dtype = out_dtype;
+    pr.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+    pr.row0 = 0; pr.m_total = m;
+    return tl_launch_qgemv_rin(ctx, a, a_dtype, &pr, &epi, 1, m, k, q.group_size != k);
+  }
   if (v.kernel == kStream) {
     const void* pk[1] = {packed};
     const void* sc[1] = {scales};
@@ -2144,6 +2330,18 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
 #ifdef TL_TRACE
   g_ring_trace_next++;
 #endif
+  if (ctx->push_pending) {
+    if (!tl_push_matches(ctx, a, a_dtype, m, k))
+      return tl_set_error(ctx, TL_ERR_INVALID_ARG,
+                          "tl_qgemv_nt_batched: a pushed partial sum is pending; this launch must read it as its activations "
+                          "([m, k] = [%d, %lld]), or call tl_reduce_pending first", ctx->push_m, (long long)ctx->push_n);
+    DeviceGuard guard(ctx->device);
+    int32_t rc = tl_launch_qgemv_rin(ctx, a, a_dtype, b.p, b.e, n_items, m, k, qdesc->group_size != k);
+    if (rc != TL_OK) return rc;
+    ctx->counters[TL_COUNTER_QGEMV] += n_items;
+    ctx->counters[TL_COUNTER_QGEMV_EPILOGUE] += n_epi;
+    return TL_OK;
+  }
   for (int i = n_items; i < kMaxBatchItems; ++i) b.tile_start[i] = int32_t(tiles);  // unused items are empty ranges
   // the single-matrix shape rule (one wave if possible); a forced or tuned ring variant (keyed on
   // the summed N) overrides it
@@ -2866,5 +3064,206 @@ extern "C" int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_d
   ctx->fused_tiles = tiles;
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   ctx->counters[TL_COUNTER_QGEMV]++;
+  return TL_OK;
+}
+
+
+// ---------------------------------------------------------------------------
+// Push / reduce-on-read (host side)
+// ---------------------------------------------------------------------------
+namespace {
+template <typename K, typename... Args>
+cudaError_t launch_pdl_args(K kern, int grid, int block, size_t smem, cudaStream_t s, Args... args) {
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+constexpr int kTpStages = 4;  // ring depth of the tensor-parallel launches (their k loops are short)
+inline size_t tp_smem(int block, int nt) { return size_t(kTpStages) * 2 * block * 16 + size_t(block / 32) * nt * 128 * 4; }
+
+#define TL_TP_GO(KERN_, NT_, ...)                                                                  \
+  do {                                                                                            \
+    auto kern = KERN_;                                                                            \
+    const int block = tp_warps_for(ctx, kern, NT_, grid) * 32;                                    \
+    return launch_pdl_args(kern, grid, block, tp_smem(block, NT_), ctx->stream, __VA_ARGS__);     \
+  } while (0)
+template <typename AT>
+cudaError_t launch_push(tl_ctx* ctx, bool two, bool grouped, int grid, const GemvArgs& p, const EpiParams& e, const PushArgs& q) {
+  if (two) {
+    if (grouped) TL_TP_GO((qgemv_ring_push_kernel<AT, 2, true, kTpStages>), 2, p, e, q);
+    TL_TP_GO((qgemv_ring_push_kernel<AT, 2, false, kTpStages>), 2, p, e, q);
+  }
+  if (grouped) TL_TP_GO((qgemv_ring_push_kernel<AT, 1, true, kTpStages>), 1, p, e, q);
+  TL_TP_GO((qgemv_ring_push_kernel<AT, 1, false, kTpStages>), 1, p, e, q);
+}
+template <typename AT>
+cudaError_t launch_rin(tl_ctx* ctx, bool two, bool grouped, int grid, const GemvArgs& p, const EpiParams& e, ReduceIn r) {
+  r.nsum = std::min(grid, 16);
+  if (two) {
+    if (grouped) TL_TP_GO((qgemv_ring_rin_kernel<AT, 2, true, kTpStages>), 2, p, e, r);
+    TL_TP_GO((qgemv_ring_rin_kernel<AT, 2, false, kTpStages>), 2, p, e, r);
+  }
+  if (grouped) TL_TP_GO((qgemv_ring_rin_kernel<AT, 1, true, kTpStages>), 1, p, e, r);
+  TL_TP_GO((qgemv_ring_rin_kernel<AT, 1, false, kTpStages>), 1, p, e, r);
+}
+template <typename AT>
+cudaError_t launch_rin_batched(tl_ctx* ctx, bool two, bool grouped, int grid, const RingBatchArgs& b, ReduceIn r) {
+  r.nsum = std::min(grid, 16);
+  if (two) {
+    if (grouped) TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 2, true, kTpStages>), 2, b, r);
+    TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 2, false, kTpStages>), 2, b, r);
+  }
+  if (grouped) TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 1, true, kTpStages>), 1, b, r);
+  TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 1, false, kTpStages>), 1, b, r);
+}
+#undef TL_TP_GO
+
+// stand-alone form of the consumer's prologue (tl_reduce_pending)
+__global__ void __launch_bounds__(256) reduce_pending_kernel(const __grid_constant__ ReduceIn rin) {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  reduce_in_prologue(rin);
+}
+
+// CTA width of a tensor-parallel launch: the widest CTA whose whole launch is resident at once (one
+// wave), asked of the occupancy calculator for the kernel that will actually run.
+template <typename K>
+int tp_warps_for(tl_ctx* ctx, K kern, int nt, int64_t tiles) {
+  for (int w : {16, 8, 4}) {
+    const size_t smem = tp_smem(w * 32, nt);
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    int occ = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, w * 32, smem) != cudaSuccess) { cudaGetLastError(); occ = 0; }
+    if (int64_t(occ) * ctx->sm_count >= tiles) return w;
+  }
+  return 4;
+}
+
+ReduceIn make_reduce_in(tl_ctx* ctx, void* dst, int grid) {
+  ReduceIn r{};
+  r.base = static_cast<uint8_t*>(ctx->p2p_local);
+  r.max_bytes = ctx->p2p_max_bytes;
+  r.dst = dst;
+  r.world = ctx->world;
+  r.expected = 0;
+  r.nsum = std::min(grid, 16);
+  r.count_vec = int32_t(int64_t(ctx->push_m) * ctx->push_n * 2 / 16);
+  r.dtype = ctx->push_dtype;
+  r.status = ctx->dev_status;
+  r.spin_limit = ctx->wait_limit_polls;
+  return r;
+}
+}  // namespace
+
+// Can the pending push be reduced by a launch that reads `a` as [m, k] activations of a_dtype?
+bool tl_push_matches(tl_ctx* ctx, const void* a, int32_t a_dtype, int32_t m, int64_t k) {
+  return ctx->push_pending && a == ctx->push_dst && a_dtype == ctx->push_dtype && m == ctx->push_m && k == ctx->push_n;
+}
+
+extern "C" int32_t tl_qgemv_nt_push(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed, const void* scales,
+                                    void* out, int32_t out_dtype, int32_t m, int64_t n, int64_t k, const tl_quant_desc* qdesc,
+                                    float alpha) {
+  TL_CHECK_CTX(ctx);
+  if (ctx->world <= 1 && !ctx->p2p_attached)  // nothing to sum: the plain product, straight into out
+    return tl_qgemv_nt(ctx, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc, alpha, nullptr);
+  int32_t rc = tl_check_qargs(ctx, "tl_qgemv_nt_push", a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc);
+  if (rc != TL_OK) return rc;
+  if (m < 1 || m > 16) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_push: m=%d outside the GEMV range [1,16]", m);
+  if (!ctx->p2p_attached) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_push: peers not attached (tl_p2p_create / tl_p2p_attach)");
+  if (ctx->push_pending)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_qgemv_nt_push: the previous push has not been reduced yet (run the launch that reads it, or tl_reduce_pending)");
+  if (!(a_dtype == TL_F16 || a_dtype == TL_BF16) || !(out_dtype == TL_F16 || out_dtype == TL_BF16) || k % 64 != 0 ||
+      qdesc->group_size % 64 != 0 || n % 16 != 0 || n < 16 || (reinterpret_cast<uintptr_t>(a) & 15) ||
+      (reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
+                        "tl_qgemv_nt_push: needs f16/bf16 activations and outputs, K %% 64 == 0, group %% 64 == 0, N %% 16 == 0, 16-byte aligned operands");
+  if (size_t(m) * size_t(n) * 4 > ctx->p2p_max_bytes)  // every 2-byte pair travels with a 4-byte epoch
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_push: %zu bytes exceed the exchange buffer (%zu)", size_t(m) * size_t(n) * 4,
+                        ctx->p2p_max_bytes);
+  EpiParams epi;
+  bool has_ops = false;
+  rc = tl_make_epi(ctx, nullptr, alpha, &epi, &has_ops);
+  if (rc != TL_OK) return rc;
+  DeviceGuard guard(ctx->device);
+  GemvArgs p{};
+  p.a = a; p.packed = reinterpret_cast<const uint32_t*>(packed); p.scales = scales; p.out = out;
+  p.m = m; p.n = int32_t(n); p.k = int32_t(k);
+  p.group = qdesc->group_size; p.groups_per_row = int32_t(k / qdesc->group_size);
+  p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
+  p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+  p.row0 = 0; p.m_total = m;
+  PushArgs q{};
+  for (int r = 0; r < ctx->world; ++r) q.base[r] = static_cast<uint8_t*>(ctx->p2p_peer[r]);
+  q.rank = ctx->rank; q.world = ctx->world; q.max_bytes = ctx->p2p_max_bytes; q.dst = out; q.status = ctx->dev_status;
+  q.spin_limit = ctx->wait_limit_polls;
+  const int64_t tiles = n / 16;
+  const int grid = int(tiles);
+  const bool grouped = qdesc->group_size != k;
+  cudaError_t e = a_dtype == TL_F16 ? launch_push<__half>(ctx, m > 8, grouped, grid, p, epi, q)
+                                    : launch_push<__nv_bfloat16>(ctx, m > 8, grouped, grid, p, epi, q);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_qgemv_nt_push: launch failed: %s", cudaGetErrorString(e));
+  }
+  ctx->push_pending = true;
+  ctx->push_dst = out; ctx->push_m = m; ctx->push_n = n; ctx->push_tiles = tiles; ctx->push_dtype = out_dtype;
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  ctx->counters[TL_COUNTER_QGEMV]++;
+  return TL_OK;
+}
+
+extern "C" int32_t tl_reduce_pending(tl_ctx* ctx) {
+  TL_CHECK_CTX(ctx);
+  if (!ctx->push_pending) return TL_OK;
+  DeviceGuard guard(ctx->device);
+  const int grid = 16;
+  const ReduceIn r = make_reduce_in(ctx, ctx->push_dst, grid);
+  cudaError_t e = launch_pdl_args(reduce_pending_kernel, grid, 256, 0, ctx->stream, r);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "tl_reduce_pending: launch failed: %s", cudaGetErrorString(e));
+  }
+  ctx->push_pending = false;
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  return TL_OK;
+}
+
+// One launch that reduces the pending push into `a` and then runs up to four products over it.
+int32_t tl_launch_qgemv_rin(tl_ctx* ctx, const void* a, int32_t a_dtype, const GemvArgs* items, const EpiParams* epis, int n_items,
+                            int32_t m, int64_t k, bool grouped) {
+  int64_t tiles = 0;
+  RingBatchArgs b{};
+  for (int i = 0; i < kMaxBatchItems; ++i) {
+    b.tile_start[i] = int32_t(tiles);
+    if (i >= n_items) continue;
+    b.p[i] = items[i];
+    b.e[i] = epis[i];
+    tiles += (items[i].n + 15) / 16;
+  }
+  b.tile_start[kMaxBatchItems] = int32_t(tiles);
+  const int grid = int(tiles);
+  const ReduceIn r = make_reduce_in(ctx, const_cast<void*>(a), grid);
+  cudaError_t e;
+  if (n_items == 1)
+    e = a_dtype == TL_F16 ? launch_rin<__half>(ctx, m > 8, grouped, grid, items[0], epis[0], r)
+                          : launch_rin<__nv_bfloat16>(ctx, m > 8, grouped, grid, items[0], epis[0], r);
+  else
+    e = a_dtype == TL_F16 ? launch_rin_batched<__half>(ctx, m > 8, grouped, grid, b, r)
+                          : launch_rin_batched<__nv_bfloat16>(ctx, m > 8, grouped, grid, b, r);
+  if (e != cudaSuccess) {
+    ctx->async_errors++;
+    return tl_set_error(ctx, TL_ERR_CUDA, "qgemv: reduce-on-read launch failed: %s", cudaGetErrorString(e));
+  }
+  ctx->push_pending = false;
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   return TL_OK;
 }

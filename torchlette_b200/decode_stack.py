@@ -77,17 +77,22 @@ class _Proj:
 
 class DecodeStack:
     def __init__(self, be: CudaBackend, cfg: StackConfig, rank: int = 0, world: int = 1, tp_mode: str = "chained",
-                 seed: int = 0, allreduce: str = "nccl", fuse: bool = True, chain: bool = False):
-        assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p", "fused")
+                 seed: int = 0, allreduce: str = "nccl", fuse: bool = True, chain: bool = False,
+                 loopback_push: bool = False):
+        assert tp_mode in ("chained", "gather") and allreduce in ("nccl", "p2p", "fused", "push")
         # chain: the whole step as ONE persistent cooperative launch (tl_qgemv_chain_*); single rank,
         # batch <= 16 only -- elsewhere the step stays a graph of per-projection launches
         self.chain_requested = chain
+        # one rank with a loopback exchange attached (tl_p2p_attach_loopback(ctx, 1)): the row-parallel
+        # projections still go through tl_qgemv_nt_push and its reduce-on-read consumer
+        self.loopback_push = loopback_push
         self._chain = None
         self._chain_keep = []
         self.be, self.cfg, self.rank, self.world, self.tp_mode = be, cfg, rank, world, tp_mode
         self.fuse = fuse  # q/k/v and gate/up as one launch each
         # "p2p": the library's one-shot peer-memory all-reduce (peers must be attached);
-        # "fused": the row-parallel projections do their own all-reduce (tl_qgemv_nt_allreduce)
+        # "fused": the row-parallel projections do their own all-reduce (tl_qgemv_nt_allreduce);
+        # "push": they push their partials and the next launch sums them (tl_qgemv_nt_push)
         self.allreduce = allreduce
         self.dev = torch.device("cuda", be.device)
         self.lib, self.ctx = be._lib, be._ctx
@@ -183,12 +188,21 @@ class DecodeStack:
                 self.ctx, x.data_ptr(), self.adt, p.w.data_ptr(), p.s.data_ptr(), out.data_ptr(),
                 B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha))
             return
+        if (self.world > 1 or self.loopback_push) and self.allreduce == "push" and self.cfg.batch <= 16 and not p.act \
+                and self.tp_mode == "chained":
+            # the partial goes to every rank's exchange buffer; the NEXT launch (q+k+v, gate+up or lm_head,
+            # which reads `out`) sums the ranks' partials in its prologue: no collective launch at all
+            q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, p.k, B.TL_F32, B.TL_SCALE_DIRECT)
+            B.check(self.ctx, self.lib.tl_qgemv_nt_push(
+                self.ctx, x.data_ptr(), self.adt, p.w.data_ptr(), p.s.data_ptr(), out.data_ptr(),
+                B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha))
+            return
         self._run(p, x, out)
         self._allreduce(out)
 
     def _allreduce(self, t: torch.Tensor):
         if self.world > 1:
-            if self.allreduce in ("p2p", "fused"):
+            if self.allreduce in ("p2p", "fused", "push"):
                 B.check(self.ctx, self.lib.tl_allreduce_sum_p2p(self.ctx, t.data_ptr(), t.data_ptr(), t.numel(), self.adt))
             else:
                 B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, t.data_ptr(), t.numel(), self.adt))
