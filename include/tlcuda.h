@@ -137,6 +137,14 @@ TL_API int32_t tl_memset(tl_ctx* ctx, void* dptr, int32_t byte_value, size_t byt
 TL_API int32_t tl_copy2d(tl_ctx* ctx, void* dst, size_t dst_pitch, const void* src, size_t src_pitch,
                          size_t width_bytes, size_t height);
 
+/* ---- device quantizer: the same function with the weight already on the GPU ----
+ * (src/backend/quantize.ts:77-131; the loader quantizes at load time,
+ * examples/qwen3/loader.ts:228-253).  weight f32 [n,k], packed u32 [n,k/4] and scales
+ * u16 [n,k/group] are DEVICE buffers; enqueued on the context's stream.  Bit-identical to
+ * tl_quantize_linear_weight.  group_size must be a multiple of 4. */
+TL_API int32_t tl_quantize_linear_weight_device(tl_ctx* ctx, const float* weight, int64_t n, int64_t k,
+                                                int32_t group_size, uint32_t* packed, uint16_t* scales);
+
 /* ---- host quantizer: quantizeLinearWeight (src/backend/quantize.ts:77-131) --
  * weight f32 [n,k] (host) -> packed u32 [n,k/4] + scales u16 [n,k/group] (f16
  * bits of the group abs-max), both host buffers.  Multi-threaded over rows. */

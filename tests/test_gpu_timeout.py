@@ -76,8 +76,60 @@ def test_loopback_needs_an_exchange_buffer_and_a_sane_world():
         assert lib.tl_p2p_reset(ctx) == B.TL_ERR_INVALID_ARG
         handle = (C.c_char * 64)()
         B.check(ctx, lib.tl_p2p_create(ctx, 4096, handle))
-        assert lib.tl_p2p_attach_loopback(ctx, 1) == B.TL_ERR_INVALID_ARG
+        assert lib.tl_p2p_attach_loopback(ctx, 0) == B.TL_ERR_INVALID_ARG
         assert lib.tl_p2p_attach_loopback(ctx, 9) == B.TL_ERR_INVALID_ARG
         assert lib.tl_sync(ctx) == B.TL_OK
+    finally:
+        be.destroy()
+
+
+def test_push_and_reduce_on_read_on_one_gpu():
+    """tl_qgemv_nt_push followed by its consumer on a loopback group of one rank: the whole push /
+    reduce-on-read path (epoch-tagged words, the summing CTAs, the grid-wide gate) on local memory.
+    The sum has one term, so the consumer must see exactly the f16-rounded product, and a consumer
+    that does not read the pushed buffer is refused."""
+    import numpy as np
+
+    be = tb.CudaBackend(0)
+    lib, ctx = be._lib, be._ctx
+    try:
+        m, n1, k1, n2 = 8, 512, 256, 320
+        handle = (C.c_char * 64)()
+        B.check(ctx, lib.tl_p2p_create(ctx, m * n1 * 4, handle))
+        B.check(ctx, lib.tl_p2p_attach_loopback(ctx, 1))
+        c1 = cases.per_channel_case(n1, k1, m, seed=41, act_dtype="f16")
+        c2 = cases.per_channel_case(n2, n1, m, seed=42, act_dtype="f16")
+        w1 = be.createQuantizedWeight(c1["packed"], c1["scales"], n1, k1, tb.perChannelFormat(k1))
+        w2 = be.createQuantizedWeight(c2["packed"], c2["scales"], n2, n1, tb.perChannelFormat(n1))
+        x = be.ops.tensorFromArray(c1["x_bits"], [m, k1], "f16")
+        h = be.ops.empty([m, n1], "f16")
+        y = be.ops.empty([m, n2], "f32")
+        other = be.ops.empty([m, n1], "f16")
+        q1, q2 = be._qdesc(w1.format.packing), be._qdesc(w2.format.packing)
+        alpha = 0.01
+        for rep in range(3):  # successive pushes alternate the halves of the exchange buffer
+            B.check(ctx, lib.tl_qgemv_nt_push(ctx, x.buffer, B.TL_F16, w1.buffer, w1.scales.buffer, h.buffer, B.TL_F16,
+                                              m, n1, k1, C.byref(q1), alpha))
+            # a launch that does not read `h` must be refused while the push is pending, and launch nothing
+            rc = lib.tl_qgemv_nt(ctx, other.buffer, B.TL_F16, w2.buffer, w2.scales.buffer, y.buffer, B.TL_F32, m, n2, n1,
+                                 C.byref(q2), 1.0, None)
+            assert rc == B.TL_ERR_INVALID_ARG and b"pending" in lib.tl_last_error(ctx)
+            B.check(ctx, lib.tl_qgemv_nt(ctx, h.buffer, B.TL_F16, w2.buffer, w2.scales.buffer, y.buffer, B.TL_F32, m, n2, n1,
+                                         C.byref(q2), 1.0, None))
+            be.sync()
+            ref_h = orc.linear_reference(c1["x"], orc.dequantize_direct_f32(c1["packed"], c1["scales"], k1, k1), None, None, alpha=alpha)
+            got_h = np.asarray(be.ops.read(h), dtype=np.float32)
+            assert cases.rel_err(got_h, ref_h) <= 1e-2
+            ref_y = orc.linear_reference(got_h, orc.dequantize_direct_f32(c2["packed"], c2["scales"], n1, n1), None, None)
+            assert cases.rel_err(be.ops.read(y), ref_y) <= 1e-3
+        # the stand-alone reduction
+        B.check(ctx, lib.tl_qgemv_nt_push(ctx, x.buffer, B.TL_F16, w1.buffer, w1.scales.buffer, h.buffer, B.TL_F16,
+                                          m, n1, k1, C.byref(q1), alpha))
+        B.check(ctx, lib.tl_reduce_pending(ctx))
+        be.sync()
+        assert cases.rel_err(np.asarray(be.ops.read(h), dtype=np.float32), ref_h) <= 1e-2
+        assert be.getGpuUncapturedErrorCount() == 0
+        for t in (other, y, h, x, w2.scales, w2, w1.scales, w1):
+            t.destroy()
     finally:
         be.destroy()

@@ -288,6 +288,30 @@ class CudaBackend:
                                                           scales.ctypes.data_as(C.c_void_p)))
         return packed, scales
 
+    def quantizeLinearWeightOnDevice(self, weight: CudaTensor, format: StorageFormat) -> CudaTensor:
+        """quantizeLinearWeight (quantize.ts:77-131) + createQuantizedWeight (engine.ts:2041-2149) with
+        the f32 [N, K] weight already on the GPU: one kernel writes the packed words and the f16 scale
+        bits, bit-identical to the host quantizer; nothing travels back to the host."""
+        packing = format.packing
+        if packing is None or packing.scheme != "int8-grouped" or packing.scalesDtype != "f16":
+            raise TlError(B.TL_ERR_UNSUPPORTED, "quantizeLinearWeightOnDevice: the reference quantizer emits int8-grouped with f16 scales")
+        if weight.dtype != "f32" or len(weight.shape) != 2:
+            raise TlError(B.TL_ERR_INVALID_ARG, "quantize: weight must be f32 [N, K]")
+        n, k = weight.shape
+        if k % 4 != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by 4")
+        g = packing.groupSize
+        if g <= 0 or k % g != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by groupSize={g}")
+        wt = self.ops.empty([n, k // 4], "u32")
+        st = self.ops.empty([n, k // g], "u16")
+        B.check(self._ctx, self._lib.tl_quantize_linear_weight_device(self._ctx, weight.buffer, n, k, g, wt.buffer, st.buffer))
+        wt.shape = [n, k]
+        wt.dtype = format.elementType
+        wt.format = format
+        wt.scales = st
+        return wt
+
     def createQuantizedWeight(self, packed, scales, n: int, k: int, format: StorageFormat) -> CudaTensor:
         """engine.ts:2041-2149: validate lengths, upload the packed words and the
         scales, return the logical [N,K] tensor carrying format + scales."""

@@ -95,6 +95,7 @@ SIGNATURES = {
     "tl_memset": (_I32, [_P, _P, _I32, _SZ]),
     "tl_copy2d": (_I32, [_P, _P, _SZ, _P, _SZ, _SZ, _SZ]),
     "tl_quantize_linear_weight": (_I32, [_P, _I64, _I64, _I32, _P, _P]),
+    "tl_quantize_linear_weight_device": (_I32, [_P, _P, _I64, _I64, _I32, _P, _P]),
     "tl_f32_to_f16_bits": (C.c_uint32, [_F]),
     "tl_f16_bits_to_f32": (_F, [C.c_uint32]),
     "tl_qgemv_nt": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),

@@ -200,3 +200,107 @@ int32_t tl_unpack_int8(tl_ctx* ctx, const void* packed, void* out_i8, int64_t n,
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Device-side quantizeLinearWeight (src/backend/quantize.ts:77-131): the weight
+// stays on the GPU, one warp per (row, group).  Same arithmetic as the host
+// quantizer, step by step: group abs-max in f32 with NaN skipped (`a > absMax`),
+// the f16 scale bits through the reference's converter (half-up subnormal
+// branch included), 127 / scale and weight * inv in f64, Math.round as
+// floor-and-compare, clamp with NaN -> 0, two's-complement byte lanes.  The
+// packed words and scale bits are bit-identical to the host's.
+// ---------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ uint32_t dev_f32_to_f16_bits(float value) {
+  const uint32_t x = __float_as_uint(value);
+  const uint32_t sign = (x >> 16) & 0x8000u;
+  const int32_t e = int32_t((x >> 23) & 0xffu) - 112;
+  const uint32_t mant = x & 0x7fffffu;
+  if (e <= 0) {
+    if (e < -10) return sign;
+    const uint32_t shifted = (mant | 0x800000u) >> (1 - e);
+    return (sign | ((shifted >> 13) + ((shifted >> 12) & 1u))) & 0xffffu;
+  }
+  if (e >= 31) return sign | 0x7c00u;
+  uint32_t h = sign | (uint32_t(e) << 10) | (mant >> 13);
+  const uint32_t rest = mant & 0x1fffu;
+  if (rest > 0x1000u || (rest == 0x1000u && (h & 1u))) ++h;
+  return h & 0xffffu;
+}
+__device__ __forceinline__ double dev_f16_bits_to_f64(uint32_t bits) {
+  const uint32_t e = (bits >> 10) & 0x1fu, frac = bits & 0x3ffu;
+  double mag;
+  if (e == 0) mag = ldexp(double(frac), -24);
+  else if (e == 31) mag = frac == 0 ? double(INFINITY) : double(NAN);
+  else mag = ldexp(double(frac | 0x400u), int(e) - 25);
+  return (bits & 0x8000u) ? -mag : mag;
+}
+
+__global__ void __launch_bounds__(256) quantize_kernel(const float* __restrict__ weight, int64_t n_groups, int32_t group,
+                                                       uint32_t* __restrict__ packed, uint16_t* __restrict__ scales) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = (int64_t(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int64_t nwarps = (int64_t(gridDim.x) * blockDim.x) >> 5;
+  const int words = group >> 2;  // group % 4 == 0: a packed word never straddles two groups
+  for (int64_t g = warp0; g < n_groups; g += nwarps) {
+    const float4* src = reinterpret_cast<const float4*>(weight + g * group);  // rows are k floats, groups contiguous in k
+    float amax = 0.f;
+    for (int w = lane; w < words; w += 32) {
+      const float4 v = __ldg(src + w);
+      const float a0 = fabsf(v.x), a1 = fabsf(v.y), a2 = fabsf(v.z), a3 = fabsf(v.w);
+      if (a0 > amax) amax = a0;  // a NaN never compares greater: skipped, as in the reference
+      if (a1 > amax) amax = a1;
+      if (a2 > amax) amax = a2;
+      if (a3 > amax) amax = a3;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, amax, o);
+      if (other > amax) amax = other;
+    }
+    const uint32_t sbits = dev_f32_to_f16_bits(amax);
+    if (lane == 0) scales[g] = uint16_t(sbits);
+    const double sc = dev_f16_bits_to_f64(sbits);
+    const double inv = sc > 0 ? 127.0 / sc : 0.0;
+    uint32_t* dst = packed + g * words;
+    for (int w = lane; w < words; w += 32) {
+      const float4 v = __ldg(src + w);
+      const float f[4] = {v.x, v.y, v.z, v.w};
+      uint32_t word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        const double x = double(f[b]) * inv;
+        const double fl = floor(x);
+        double q = (x - fl >= 0.5) ? fl + 1.0 : fl;  // Math.round: ties toward +infinity
+        q = (q != q) ? 0.0 : fmax(-127.0, fmin(127.0, q));  // NaN packs 0 (`NaN & 0xff`)
+        word |= (uint32_t(int32_t(q)) & 0xffu) << (8 * b);
+      }
+      dst[w] = word;
+    }
+  }
+}
+}  // namespace
+
+extern "C" int32_t tl_quantize_linear_weight_device(tl_ctx* ctx, const float* weight, int64_t n, int64_t k, int32_t group_size,
+                                                    uint32_t* packed, uint16_t* scales) {
+  TL_CHECK_CTX(ctx);
+  if (!weight || !packed || !scales) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "quantize (device): null pointer");
+  if (n < 0 || k < 0) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "quantize (device): negative shape");
+  if (k % 4 != 0) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "quantize: K=%lld must be divisible by 4", (long long)k);
+  if (group_size <= 0 || k % group_size != 0)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "quantize: K=%lld must be divisible by groupSize=%d", (long long)k, group_size);
+  if (group_size % 4 != 0)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "quantize (device): groupSize=%d must be a multiple of 4 (use the host quantizer)", group_size);
+  if ((reinterpret_cast<uintptr_t>(weight) & 15) || (reinterpret_cast<uintptr_t>(packed) & 3) || (reinterpret_cast<uintptr_t>(scales) & 1))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "quantize (device): weight must be 16-byte aligned, packed 4, scales 2");
+  if (n == 0 || k == 0) return TL_OK;
+  DeviceGuard guard(ctx->device);
+  const int64_t n_groups = n * (k / group_size);
+  const int block = 256;
+  const int64_t want = (n_groups + 7) / 8;  // 8 warps per CTA, one group per warp and pass
+  const int grid = int(std::min<int64_t>(want, int64_t(ctx->sm_count) * 32));
+  quantize_kernel<<<grid, block, 0, ctx->stream>>>(weight, n_groups, group_size, packed, scales);
+  TL_CUDA(ctx, cudaGetLastError());
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+  return TL_OK;
+}
