@@ -257,10 +257,25 @@ TL_API int32_t tl_dequant_int8(tl_ctx* ctx, const void* packed, const void* scal
 /* Debug op: the signed byte lanes as int8 [n,k] (integer half of the dequant). */
 TL_API int32_t tl_unpack_int8(tl_ctx* ctx, const void* packed, void* out_i8, int64_t n, int64_t k);
 
+/* ---- companion ops: the unfused forms of what the epilogue fuses, and the materialization of
+ * a transposed view (BackendOps add / sub / mul / relu / silu / gelu / cast / contiguous,
+ * src/backend/types.ts:340-680; composed by matmulQuantizedB's explicit-dequant path,
+ * src/backend/webgpu/ops/matmul-ops.ts:163-181).  One HBM pass each.
+ * tl_unary_op: out[i] = op(in[i]); op is TL_UNARY_* or 0 for a plain cast / copy; dtypes independent.
+ * tl_binary_op: out[r,c] = a[r,c] (op) b[r,c], or b[c] when b_is_row (a bias row); op is TL_BINARY_*.
+ * tl_transpose2d: out[b,c,r] = in[b,r,c] for elements of 1, 2 or 4 bytes (in != out). */
+TL_API int32_t tl_unary_op(tl_ctx* ctx, int32_t op, const void* in, int32_t in_dtype, void* out,
+                           int32_t out_dtype, int64_t count);
+TL_API int32_t tl_binary_op(tl_ctx* ctx, int32_t op, const void* a, int32_t a_dtype, const void* b,
+                            int32_t b_dtype, void* out, int32_t out_dtype, int64_t rows, int64_t cols,
+                            int32_t b_is_row);
+TL_API int32_t tl_transpose2d(tl_ctx* ctx, const void* in, void* out, int64_t batch, int64_t rows,
+                              int64_t cols, int32_t elem_bytes);
+
 /* ---- selection: planTiledMatmul / selectMatmulChoice / SelectionReceipt
  * (src/backend/webgpu/matmul/dispatch.ts:171-192, 1130-1329;
  *  src/backend/webgpu/matmul/variants.ts:54-260) ------------------------------ */
-enum { TL_FAMILY_QGEMV = 1, TL_FAMILY_QGEMM = 2 };
+enum { TL_FAMILY_QGEMV = 1, TL_FAMILY_QGEMM = 2, TL_FAMILY_MATMUL = 3 /* dense: 0 tiled, 1 gemv */ };
 typedef struct tl_variant {
   int32_t family;   /* TL_FAMILY_* */
   int32_t kernel;   /* family-specific kernel id (see tl_variant_name) */
@@ -278,6 +293,28 @@ typedef struct tl_plan_receipt {
 TL_API int32_t tl_plan_qmatmul(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
                                int32_t out_dtype, const tl_quant_desc* qdesc,
                                const tl_epilogue* epilogue, tl_plan_receipt* out_receipt);
+/* ---- dense matmul: dispatchTiledMatmul / dispatchMatmul for an unquantized B
+ * (src/backend/webgpu/matmul/dispatch.ts:1331-1700; dense GEMV builders
+ *  src/backend/webgpu/matmul/gemv.ts:430-532; tiled body
+ *  src/schedule/matmul-skeleton.ts:738-908).
+ * out[b] = epilogue(alpha * op(A[b]) . op(B[b])), f32 accumulation.
+ *   A is [m,k] row-major, or [k,m] when trans_a; B is [k,n], or [n,k] when trans_b; out [m,n].
+ *   stride_a / stride_b / stride_c: elements between consecutive batches; 0 broadcasts an
+ *   operand over the batch (dispatch.ts:1411-1510); stride_c >= m*n when batch > 1.
+ *   dtype_a, dtype_b, out_dtype: any of TL_F32 / TL_F16 / TL_BF16, independently.
+ *   cast_a, cast_b: -1, or TL_F16 / TL_BF16 to round the operand through that type as it is
+ *   loaded (the read-wider-cast-on-load prologue, variants.ts:170-175).
+ *   A binary epilogue input is [m,n] and needs batch == 1.
+ * Selection: m <= 16, batch 1, trans_b, no trans_a, both operands the same 2-byte type, k % 32 == 0
+ * and 16-byte aligned pointers run the tensor-core GEMV (counter TL_COUNTER_GEMV) unless the
+ * environment has TORCHLETTE_GEMV=0 or tl_force_variant names {TL_FAMILY_MATMUL, 0}; all else
+ * runs the tiled kernel (TL_COUNTER_MATMUL).  With receipt_only non-NULL nothing is launched
+ * and the operand pointers may be NULL: the choice is written there (planTiledMatmul). */
+TL_API int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n,
+                         int64_t k, int64_t batch, int64_t stride_a, int64_t stride_b,
+                         int64_t stride_c, int32_t trans_a, int32_t trans_b, float alpha,
+                         int32_t dtype_a, int32_t dtype_b, int32_t out_dtype, int32_t cast_a,
+                         int32_t cast_b, const tl_epilogue* epilogue, tl_plan_receipt* receipt_only);
 TL_API const char* tl_variant_name(const tl_variant* v);
 /* Force one variant for every following call (NULL clears).  A/B testing hook,
  * the analogue of an explicit MatmulKernelConfig (variants.ts:214-236). */
@@ -290,7 +327,9 @@ enum {
   TL_COUNTER_QGEMV_EPILOGUE = 2,/* getGemvEpilogueDispatchCount */
   TL_COUNTER_QGEMM = 3,
   TL_COUNTER_KERNEL_LAUNCHES = 4, /* every kernel this library launched */
-  TL_COUNTER_COUNT = 5
+  TL_COUNTER_GEMV = 5,          /* getGemvDispatchCount: dense small-batch GEMV */
+  TL_COUNTER_MATMUL = 6,        /* dense tiled matmul */
+  TL_COUNTER_COUNT = 7
 };
 TL_API int64_t tl_counter_get(tl_ctx* ctx, int32_t which);
 TL_API int32_t tl_counters_reset(tl_ctx* ctx);
@@ -332,6 +371,11 @@ typedef struct tl_event tl_event;
 TL_API int32_t tl_event_create(tl_ctx* ctx, tl_event** out_event);
 TL_API int32_t tl_event_record(tl_ctx* ctx, tl_event* ev);
 TL_API int32_t tl_event_elapsed_ms(tl_ctx* ctx, tl_event* start, tl_event* stop, float* out_ms);
+/* Blocks the calling host thread until the event has happened.  The one call that another host
+ * thread may make while the context's own thread keeps enqueueing: it neither reads nor writes
+ * the context's error state (so it returns a bare status, no tl_last_error text).  The N-API
+ * shim's Promise-returning download waits with it on a worker thread. */
+TL_API int32_t tl_event_synchronize(tl_ctx* ctx, tl_event* ev);
 TL_API int32_t tl_event_destroy(tl_ctx* ctx, tl_event* ev);
 
 /* ---- multi-GPU (no counterpart in the reference, whose only parallelism is

@@ -1,0 +1,267 @@
+"""GPU parity of the dense matmul / GEMV + epilogue (tl_matmul through the backend's
+dispatchMatmul) against the CPU oracle.
+
+Inputs and tolerances follow the reference's own tests of this op:
+test/webgpu/matmul-epilogue.spec.ts:21-27 (values ((i + off) % 7) - 3, rtol = atol = 1e-3,
+1e-2 with gelu, including the non-tile-aligned 50 x 70 x 60 product) and
+examples/qwen3/probe-gemv.ts:38-39 (GEMV vs f64 over K, N in {33, 128, 1024, 2048}, NN and NT,
+f32 x f32 and f32 x f16, relative error <= 5e-4; epilogue battery <= 1e-4 relative).
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as orc
+from torchlette_b200 import backend as tb
+
+pytestmark = pytest.mark.gpu
+
+
+def _pattern(count, off):
+    return (((np.arange(count) + off) % 7) - 3).astype(np.float32)
+
+
+def _to_dev(be, arr_f32, shape, dtype):
+    if dtype == "f32":
+        return be.ops.tensorFromArray(arr_f32, shape, "f32"), arr_f32.reshape(shape)
+    if dtype == "f16":
+        h = arr_f32.astype(np.float16)
+        return be.ops.tensorFromArray(h, shape, "f16"), h.astype(np.float32).reshape(shape)
+    bits = orc.bf16_bits_rne(arr_f32)
+    return be.ops.tensorFromArray(bits, shape, "bf16"), orc.bf16_bits_to_f32(bits).reshape(shape)
+
+
+def _read_f32(be, t):
+    r = be.ops.read(t)
+    return orc.bf16_bits_to_f32(r) if t.dtype == "bf16" else np.asarray(r, dtype=np.float32)
+
+
+def _ref(a, b, bias=None, act=None, alpha=1.0):
+    """a [M,K], b [K,N] as f32 values: f64 sequential-k accumulate (the oracle's matmul)."""
+    return orc.linear_reference(np.ascontiguousarray(a), np.ascontiguousarray(b.T), bias, act, alpha)
+
+
+EPILOGUES = [None, ("bias", None), (None, "relu"), (None, "gelu"), (None, "silu"), ("bias", "relu"), ("bias", "gelu")]
+
+
+@pytest.mark.parametrize("m,k,n", [(64, 64, 64), (50, 70, 60), (1, 128, 96), (130, 33, 257)])
+@pytest.mark.parametrize("epi", EPILOGUES)
+def test_dense_matmul_epilogue_battery(backend, m, k, n, epi):
+    be = backend
+    a, a_v = _to_dev(be, _pattern(m * k, 0), [m, k], "f32")
+    b, b_v = _to_dev(be, _pattern(k * n, 3), [k, n], "f32")
+    bias_v = _pattern(n, 5) * 0.5
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    chain, act = [], None
+    if epi is not None:
+        if epi[0]:
+            chain.append(("add", bias_t))
+        if epi[1]:
+            chain.append((epi[1], None))
+            act = epi[1]
+    opts = {}
+    if chain:
+        plan = tb.detectMatmulEpilogue(chain)
+        opts["epilogue"], opts["epilogueInputs"], _ = plan
+    y = be.ops.matmul(a, b, opts)
+    got = _read_f32(be, y)
+    ref = _ref(a_v, b_v, bias_v if (epi and epi[0]) else None, act)
+    tol = 1e-2 if act == "gelu" else 1e-3
+    np.testing.assert_allclose(got, ref.reshape(got.shape), rtol=tol, atol=tol)
+    for t in (a, b, bias_t, y):
+        t.destroy()
+
+
+@pytest.mark.parametrize("trans_a", [False, True])
+@pytest.mark.parametrize("trans_b", [False, True])
+@pytest.mark.parametrize("dtypes", [("f32", "f32", "f32"), ("f16", "f16", "f32"), ("f32", "f16", "f32"),
+                                    ("bf16", "bf16", "bf16"), ("f16", "f16", "f16")])
+def test_dense_matmul_layouts_and_dtypes(backend, trans_a, trans_b, dtypes):
+    be = backend
+    m, k, n = 37, 100, 45
+    rng = np.random.default_rng(1234)
+    av = rng.uniform(-1, 1, m * k).astype(np.float32)
+    bv = rng.uniform(-1, 1, k * n).astype(np.float32)
+    # the stored buffers: [K,M] when A is a transposed view, [N,K] when B is
+    a_t, a_stored = _to_dev(be, av, [k, m] if trans_a else [m, k], dtypes[0])
+    b_t, b_stored = _to_dev(be, bv, [n, k] if trans_b else [k, n], dtypes[1])
+    a_view = be.ops.transpose(a_t) if trans_a else a_t
+    b_view = be.ops.transpose(b_t) if trans_b else b_t
+    a_log = a_stored.T if trans_a else a_stored
+    b_log = b_stored.T if trans_b else b_stored
+    assert be.planMatmul(m, n, k, dtypes[0], dtypes[1], transA=trans_a, transB=trans_b)["variant"].endswith("tiled")
+    y = be.ops.matmul(a_view, b_view, {"outputDtype": dtypes[2]})
+    got = _read_f32(be, y)
+    ref = _ref(a_log, b_log)
+    tol = 1e-4 if dtypes[2] == "f32" else 2e-2
+    np.testing.assert_allclose(got, ref, rtol=tol, atol=tol * (1 if dtypes[2] == "f32" else 4))
+    for t in (a_t, b_t, y):
+        t.destroy()
+
+
+def test_dense_matmul_cast_on_load_matches_rounded_operands(backend):
+    be = backend
+    m, k, n = 20, 96, 24
+    rng = np.random.default_rng(7)
+    av = rng.uniform(-2, 2, m * k).astype(np.float32)
+    bv = rng.uniform(-2, 2, k * n).astype(np.float32)
+    a, a_v = _to_dev(be, av, [m, k], "f32")
+    b, b_v = _to_dev(be, bv, [k, n], "f32")
+    y = be.ops.matmul(a, b, {"inputCastA": "f16", "inputCastB": "bf16"})
+    a_r = a_v.astype(np.float16).astype(np.float32)
+    b_r = orc.bf16_bits_to_f32(orc.bf16_bits_rne(b_v.reshape(-1))).reshape(k, n)
+    np.testing.assert_allclose(_read_f32(be, y), _ref(a_r, b_r), rtol=1e-5, atol=1e-5)
+    # and differs from the unrounded product: the prologue really ran
+    assert np.abs(_read_f32(be, y) - _ref(a_v, b_v)).max() > 1e-4
+    for t in (a, b, y):
+        t.destroy()
+
+
+def test_dense_matmul_batched_with_broadcast(backend):
+    be = backend
+    bs, m, k, n = 3, 18, 40, 22
+    rng = np.random.default_rng(99)
+    av = rng.uniform(-1, 1, bs * m * k).astype(np.float32)
+    bv = rng.uniform(-1, 1, bs * k * n).astype(np.float32)
+    a, a_v = _to_dev(be, av, [bs, m, k], "f32")
+    b, b_v = _to_dev(be, bv, [bs, k, n], "f32")
+    b1, b1_v = _to_dev(be, bv[: k * n], [k, n], "f32")
+    a1, a1_v = _to_dev(be, av[: m * k], [m, k], "f32")
+    y = be.ops.matmul(a, b)          # both batched
+    yb = be.ops.matmul(a, b1)        # B broadcast (flattened to one [bs*m, k] product)
+    ya = be.ops.matmul(a1, b)        # A broadcast (stride 0)
+    g, gb, ga = _read_f32(be, y), _read_f32(be, yb), _read_f32(be, ya)
+    assert g.shape == (bs, m, n) and gb.shape == (bs, m, n) and ga.shape == (bs, m, n)
+    for i in range(bs):
+        np.testing.assert_allclose(g[i], _ref(a_v[i], b_v[i]), rtol=1e-4, atol=1e-4)
+        np.testing.assert_allclose(gb[i], _ref(a_v[i], b1_v), rtol=1e-4, atol=1e-4)
+        np.testing.assert_allclose(ga[i], _ref(a1_v, b_v[i]), rtol=1e-4, atol=1e-4)
+    for t in (a, b, b1, a1, y, yb, ya):
+        t.destroy()
+
+
+def _rel(x, ref):
+    return float(np.max(np.abs(x - ref) / np.maximum(1.0, np.abs(ref))))
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m", [1, 4, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(33, 128), (128, 1024), (1024, 2048), (2048, 6144), (4096, 32)])
+def test_dense_gemv_nt_routes_to_tensor_core_gemv(backend, dtype, m, n, k):
+    be = backend
+    rng = np.random.default_rng(n * 31 + k + m)
+    xv = rng.uniform(-1, 1, m * k).astype(np.float32)
+    wv = rng.uniform(-1, 1, n * k).astype(np.float32)
+    x, x_v = _to_dev(be, xv, [m, k], dtype)
+    w, w_v = _to_dev(be, wv, [n, k], dtype)
+    assert be.planMatmul(m, n, k, dtype, dtype, transB=True)["variant"].endswith("gemv")
+    be.resetCounters()
+    y = be.ops.matmul(x, be.ops.transpose(w))
+    assert be.getGemvDispatchCount() == 1 and be.getTiledMatmulDispatchCount() == 0
+    got = _read_f32(be, y)
+    ref = _ref(x_v, w_v.T)
+    assert _rel(got, ref) <= 5e-4
+    # forcing the tiled kernel gives the same answer through the other route
+    be.forceVariant((3, 0, 0, 0, 0, 0))
+    try:
+        be.resetCounters()
+        y2 = be.ops.matmul(x, be.ops.transpose(w))
+        assert be.getGemvDispatchCount() == 0 and be.getTiledMatmulDispatchCount() == 1
+    finally:
+        be.forceVariant(None)
+    assert _rel(_read_f32(be, y2), ref) <= 5e-4
+    for t in (x, w, y, y2):
+        t.destroy()
+
+
+@pytest.mark.parametrize("epi", [("bias", None), ("bias", "gelu"), ("bias", "silu"), (None, "silu")])
+def test_dense_gemv_epilogue_battery(backend, epi):
+    be = backend
+    m, n, k = 1, 1024, 2048
+    rng = np.random.default_rng(5)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "f16")
+    w, w_v = _to_dev(be, (rng.uniform(-1, 1, n * k) * 0.1).astype(np.float32), [n, k], "f16")
+    bias_v = rng.uniform(-1, 1, n).astype(np.float32)
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    be.resetCounters()
+    y = be.linear(x, w, bias_t if epi[0] else None, epi[1], "f32")
+    assert be.getGemvDispatchCount() == 1 and be.getGemvEpilogueDispatchCount() == 1
+    ref = _ref(x_v, w_v.T, bias_v if epi[0] else None, epi[1])
+    assert _rel(_read_f32(be, y), ref) <= 1e-4
+    for t in (x, w, bias_t, y):
+        t.destroy()
+
+
+def test_dense_matmul_argument_errors(backend):
+    be = backend
+    a = be.ops.tensorFromArray(np.zeros(12, np.float32), [3, 4], "f32")
+    b = be.ops.tensorFromArray(np.zeros(15, np.float32), [5, 3], "f32")
+    with pytest.raises(tb.TlError):
+        be.ops.matmul(a, b)  # inner dims differ
+    for t in (a, b):
+        t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# companion ops: the unfused sequence the reference's tests use as the control
+# (test/webgpu/matmul-epilogue.spec.ts:77-100): matmul -> add bias -> activation -> cast
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("act", ["relu", "silu", "gelu", "sigmoid", "tanh"])
+def test_unfused_sequence_matches_fused_epilogue_and_oracle(backend, act):
+    be = backend
+    m, k, n = 50, 70, 60
+    a, a_v = _to_dev(be, _pattern(m * k, 0) * 0.25, [m, k], "f32")
+    b, b_v = _to_dev(be, _pattern(k * n, 3) * 0.25, [k, n], "f32")
+    bias_v = _pattern(n, 5) * 0.5
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    y0 = be.ops.matmul(a, b)
+    y1 = be.ops.add(y0, bias_t)
+    y2 = getattr(be.ops, act)(y1)
+    y3 = be.ops.cast(y2, "f16")
+    plan = tb.detectMatmulEpilogue([("add", bias_t), (act, None), ("cast", "f16")])
+    fused = be.ops.matmul(a, b, {"epilogue": plan[0], "epilogueInputs": plan[1]})
+    assert fused.dtype == "f16"
+    ref = _ref(a_v, b_v, bias_v, act)
+    np.testing.assert_allclose(_read_f32(be, y2), ref, rtol=1e-5, atol=1e-5)
+    # fused and unfused round the same f32 value to f16 once: identical bits
+    np.testing.assert_array_equal(be.ops.read(y3).view(np.uint16), be.ops.read(fused).view(np.uint16))
+    for t in (a, b, bias_t, y0, y1, y2, y3, fused):
+        t.destroy()
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_contiguous_of_a_transposed_view(backend, dtype):
+    be = backend
+    rows, cols = 45, 70
+    t, t_v = _to_dev(be, np.arange(rows * cols, dtype=np.float32) % 251, [rows, cols], dtype)
+    c = be.ops.contiguous(be.ops.transpose(t))
+    assert c.shape == [cols, rows] and not c.transposed
+    np.testing.assert_array_equal(_read_f32(be, c), t_v.T)
+    c2 = be.ops.contiguous(t)
+    np.testing.assert_array_equal(_read_f32(be, c2), t_v)
+    # the materialized transposition feeds a plain NN product
+    x, x_v = _to_dev(be, _pattern(8 * rows, 1), [8, rows], dtype)
+    y = be.ops.matmul(x, t)
+    np.testing.assert_allclose(_read_f32(be, y), _ref(x_v, t_v), rtol=2e-2, atol=2e-2)
+    for u in (t, c, c2, x, y):
+        u.destroy()
+
+
+def test_binary_ops_and_cast_round_trip(backend):
+    be = backend
+    rng = np.random.default_rng(3)
+    av = rng.uniform(-4, 4, 33 * 65).astype(np.float32)
+    bv = rng.uniform(-4, 4, 33 * 65).astype(np.float32)
+    a, a_v = _to_dev(be, av, [33, 65], "f32")
+    b, b_v = _to_dev(be, bv, [33, 65], "f32")
+    for name, fn in (("add", np.add), ("sub", np.subtract), ("mul", np.multiply)):
+        r = getattr(be.ops, name)(a, b)
+        np.testing.assert_array_equal(_read_f32(be, r), fn(a_v, b_v))
+        r.destroy()
+    h = be.ops.cast(a, "f16")
+    np.testing.assert_array_equal(be.ops.read(h), a_v.astype(np.float16))
+    bf = be.ops.cast(a, "bf16")
+    np.testing.assert_array_equal(be.ops.read(bf).reshape(-1), orc.bf16_bits_rne(a_v.reshape(-1)))
+    back = be.ops.cast(h, "f32")
+    np.testing.assert_array_equal(_read_f32(be, back), a_v.astype(np.float16).astype(np.float32))
+    for t in (a, b, h, bf, back):
+        t.destroy()

@@ -207,12 +207,62 @@ class CudaOps:
         return CudaTensor(self._b, shape, t.dtype, t.buffer, t.nbytes, ownsBuffer=False, format=t.format,
                           scales=t.scales, transposed=not t.transposed)
 
+    # -- companion ops: the unfused forms of the epilogue (types.ts:340-680) ----------
+    def _unary(self, op: int, t: CudaTensor, out_dtype: Optional[str] = None) -> CudaTensor:
+        src = self.contiguous(t) if t.transposed else t
+        out = self.empty(src.shape, out_dtype or src.dtype)
+        n = int(np.prod(src.shape)) if src.shape else 1
+        B.check(self._b._ctx, self._b._lib.tl_unary_op(self._b._ctx, op, src.buffer, B.DTYPE_ID[src.dtype], out.buffer,
+                                                       B.DTYPE_ID[out.dtype], n))
+        if src is not t:
+            src.destroy()
+        return out
+
+    def relu(self, t): return self._unary(B.TL_UNARY["relu"], t)
+    def silu(self, t): return self._unary(B.TL_UNARY["silu"], t)
+    def sigmoid(self, t): return self._unary(B.TL_UNARY["sigmoid"], t)
+    def tanh(self, t): return self._unary(B.TL_UNARY["tanh"], t)
+    def gelu(self, t, approximate: str = "tanh"): return self._unary(B.TL_UNARY["gelu_tanh" if approximate == "tanh" else "gelu_erf"], t)
+
+    def cast(self, t: CudaTensor, dtype: str) -> CudaTensor:
+        return self._unary(0, t, dtype)
+
+    def _binary(self, name: str, a: CudaTensor, b: CudaTensor) -> CudaTensor:
+        """a [..., N] (op) b of the same shape, or b [N] broadcast over the rows (a bias)."""
+        if a.transposed or b.transposed:
+            raise TlError(B.TL_ERR_UNSUPPORTED, f"{name}: materialize transposed views first (contiguous)")
+        cols = a.shape[-1]
+        rows = int(np.prod(a.shape[:-1])) if len(a.shape) > 1 else 1
+        is_row = list(b.shape) == [cols] and len(a.shape) > 1
+        if not is_row and list(b.shape) != list(a.shape):
+            raise TlError(B.TL_ERR_UNSUPPORTED, f"{name}: b must match a or be its last dim")
+        out = self.empty(a.shape, a.dtype)
+        B.check(self._b._ctx, self._b._lib.tl_binary_op(self._b._ctx, B.TL_BINARY[name], a.buffer, B.DTYPE_ID[a.dtype], b.buffer,
+                                                        B.DTYPE_ID[b.dtype], out.buffer, B.DTYPE_ID[out.dtype], rows, cols,
+                                                        1 if is_row else 0))
+        return out
+
+    def add(self, a, b): return self._binary("add", a, b)
+    def sub(self, a, b): return self._binary("sub", a, b)
+    def mul(self, a, b): return self._binary("mul", a, b)
+
+    def contiguous(self, t: CudaTensor) -> CudaTensor:
+        """Materializes a transposed view (a packed weight cannot be: its bytes are not elements)."""
+        if t.format is not None and t.format.packing is not None:
+            raise TlError(B.TL_ERR_UNSUPPORTED, "contiguous: a packed weight has no element-wise transposition")
+        itemsize = np.dtype(_NP_OF[t.dtype]).itemsize
+        if not t.transposed:
+            return self._unary(0, t)  # a plain copy
+        out = self.empty(t.shape, t.dtype)
+        rows, cols = t.shape[-1], t.shape[-2]  # of the stored buffer
+        B.check(self._b._ctx, self._b._lib.tl_transpose2d(self._b._ctx, t.buffer, out.buffer, 1, rows, cols, itemsize))
+        return out
+
     def matmul(self, a: CudaTensor, b: CudaTensor, options: Optional[dict] = None) -> CudaTensor:
         """Backend matmul; the storage-format seam (matmul-ops.ts:42-59)."""
         if b.format is not None and b.format.packing is not None:
             return self._b._matmulQuantizedB(a, b, options or {})
-        raise TlError(B.TL_ERR_UNIMPLEMENTED,
-                      "matmul: only a packed (quantized) B operand is served by the cuda backend")
+        return self._b.dispatchMatmul(a, b, options or {})
 
 
 class CudaBackend:
@@ -484,6 +534,67 @@ class CudaBackend:
             self._ctx, a.buffer, B.DTYPE_ID[a.dtype], b.buffer, scales.buffer, out.buffer, B.DTYPE_ID[out_dtype],
             m, n, k, C.byref(q), float(options.get("alpha", 1.0)), C.byref(e) if e is not None else None))
         return out
+
+    def dispatchMatmul(self, a: CudaTensor, b: CudaTensor, options: dict) -> CudaTensor:
+        """dispatchMatmul for dense operands (src/backend/webgpu/matmul/dispatch.ts:1331-1700).
+        ``a`` is [..., M, K] and ``b`` [..., K, N] (either may be the transposed view of a
+        contiguous buffer); leading dims are the batch, and an operand without them is
+        broadcast over the batch (dispatch.ts:1411-1510).  Options: ``epilogue`` /
+        ``epilogueInputs`` / ``outputDtype`` / ``alpha`` / ``outBuffer`` as for the quantized
+        product, ``inputCastA`` / ``inputCastB`` ("f16" | "bf16") for the cast-on-load
+        prologue (variants.ts:170-175)."""
+        for t in (a, b):
+            if t.dtype not in ("f32", "f16", "bf16"):
+                raise TlError(B.TL_ERR_UNSUPPORTED, f"matmul: unsupported operand dtype {t.dtype}")
+        a_shape = list(a.shape) if len(a.shape) > 1 else [1] + list(a.shape)
+        b_shape = list(b.shape)
+        if len(b_shape) < 2:
+            raise TlError(B.TL_ERR_INVALID_ARG, "matmul: B needs at least two dims")
+        m, k = a_shape[-2], a_shape[-1]
+        n = b_shape[-1]
+        if b_shape[-2] != k:
+            raise TlError(B.TL_ERR_INVALID_ARG, "matmul dimension mismatch")
+        batch_a, batch_b = a_shape[:-2], b_shape[:-2]
+        if batch_a and batch_b and batch_a != batch_b:
+            raise TlError(B.TL_ERR_UNSUPPORTED, "matmul: batch dims must match or be absent on one operand")
+        batch_dims = batch_a or batch_b
+        batch = int(np.prod(batch_dims)) if batch_dims else 1
+        if (a.transposed and batch_a) or (b.transposed and batch_b):
+            raise TlError(B.TL_ERR_UNSUPPORTED, "matmul: a transposed view must be a single matrix")
+        epilogue: Optional[EpilogueConfig] = options.get("epilogue")
+        epilogueInputs = options.get("epilogueInputs", ())
+        out_dtype = epilogue.outputDtype if epilogue is not None else options.get("outputDtype", "f32")
+        # a flattened [rows, K] x [K, N] product (no batch on B) runs as ONE matrix of batch*M rows
+        if batch > 1 and not batch_b and not a.transposed:
+            m, batch = m * batch, 1
+        out = options.get("outBuffer") or self.ops.empty(list(batch_dims) + [a_shape[-2], n], out_dtype)
+        e = self._epilogue(epilogue, epilogueInputs)
+        cast = {None: -1, "f16": B.TL_F16, "bf16": B.TL_BF16}
+        B.check(self._ctx, self._lib.tl_matmul(
+            self._ctx, a.buffer, b.buffer, out.buffer, m, n, k, batch,
+            m * k if (batch_a and batch > 1) else 0, k * n if (batch_b and batch > 1) else 0, m * n,
+            1 if a.transposed else 0, 1 if b.transposed else 0, float(options.get("alpha", 1.0)),
+            B.DTYPE_ID[a.dtype], B.DTYPE_ID[b.dtype], B.DTYPE_ID[out_dtype],
+            cast[options.get("inputCastA")], cast[options.get("inputCastB")],
+            C.byref(e) if e is not None else None, None))
+        return out
+
+    def planMatmul(self, m, n, k, aDtype, bDtype, *, batch=1, transA=False, transB=False,
+                   inputCastA=None, inputCastB=None):
+        """planTiledMatmul for dense operands: which kernel a call of this geometry runs."""
+        cast = {None: -1, "f16": B.TL_F16, "bf16": B.TL_BF16}
+        r = B.PlanReceipt()
+        B.check(self._ctx, self._lib.tl_matmul(
+            self._ctx, None, None, None, m, n, k, batch, 0, 0, m * n, 1 if transA else 0, 1 if transB else 0, 1.0,
+            B.DTYPE_ID[aDtype], B.DTYPE_ID[bDtype], B.TL_F32, cast[inputCastA], cast[inputCastB], None, C.byref(r)))
+        return {"variant": self._lib.tl_variant_name(C.byref(r.choice)).decode(), "choice": r.choice.as_tuple(),
+                "grid": list(r.grid), "block": r.block}
+
+    def getGemvDispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_GEMV))
+
+    def getTiledMatmulDispatchCount(self) -> int:
+        return int(self._lib.tl_counter_get(self._ctx, B.TL_COUNTER_MATMUL))
 
     def linear(self, x: CudaTensor, weight: CudaTensor, bias: Optional[CudaTensor] = None,
                activation: Optional[str] = None, outputDtype: str = "f32") -> CudaTensor:

@@ -21,9 +21,9 @@ TL_SCALE_SNORM127, TL_SCALE_DIRECT = 0, 1
 TL_EPI_NONE, TL_EPI_BIAS, TL_EPI_UNARY, TL_EPI_BINARY, TL_EPI_CAST = 0, 1, 2, 3, 4
 TL_UNARY = {"relu": 1, "silu": 2, "sigmoid": 3, "tanh": 4, "gelu": 5, "gelu_tanh": 5, "gelu_erf": 6}
 TL_BINARY = {"add": 1, "sub": 2, "mul": 3}
-TL_FAMILY_QGEMV, TL_FAMILY_QGEMM = 1, 2
+TL_FAMILY_QGEMV, TL_FAMILY_QGEMM, TL_FAMILY_MATMUL = 1, 2, 3
 TL_COUNTER_QGEMV, TL_COUNTER_DEQUANT, TL_COUNTER_QGEMV_EPILOGUE = 0, 1, 2
-TL_COUNTER_QGEMM, TL_COUNTER_KERNEL_LAUNCHES = 3, 4
+TL_COUNTER_QGEMM, TL_COUNTER_KERNEL_LAUNCHES, TL_COUNTER_GEMV, TL_COUNTER_MATMUL = 3, 4, 5, 6
 TL_EPI_MAX_OPS, TL_EPI_MAX_INPUTS = 8, 4
 TL_COMM_ID_BYTES = 128
 
@@ -107,6 +107,11 @@ SIGNATURES = {
     "tl_qgemv_chain_destroy": (_I32, [_P, _P]),
     "tl_qgemm_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_qmatmul_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
+    "tl_matmul": (_I32, [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I32, _I32, _F, _I32, _I32, _I32,
+                         _I32, _I32, C.POINTER(Epilogue), C.POINTER(PlanReceipt)]),
+    "tl_unary_op": (_I32, [_P, _I32, _P, _I32, _P, _I32, _I64]),
+    "tl_binary_op": (_I32, [_P, _I32, _P, _I32, _P, _I32, _P, _I32, _I64, _I64, _I32]),
+    "tl_transpose2d": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32]),
     "tl_dequant_int8": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),
     "tl_unpack_int8": (_I32, [_P, _P, _P, _I64, _I64]),
     "tl_plan_qmatmul": (_I32, [_P, _I64, _I64, _I64, _I32, _I32, C.POINTER(QuantDesc), C.POINTER(Epilogue),
@@ -131,6 +136,7 @@ SIGNATURES = {
     "tl_event_create": (_I32, [_P, C.POINTER(_P)]),
     "tl_event_record": (_I32, [_P, _P]),
     "tl_event_elapsed_ms": (_I32, [_P, _P, _P, C.POINTER(_F)]),
+    "tl_event_synchronize": (_I32, [_P, _P]),
     "tl_event_destroy": (_I32, [_P, _P]),
     "tl_comm_unique_id": (_I32, [_P]),
     "tl_comm_init": (_I32, [_P, _I32, _I32, _P]),

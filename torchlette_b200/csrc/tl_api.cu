@@ -402,6 +402,15 @@ int32_t tl_event_elapsed_ms(tl_ctx* ctx, tl_event* start, tl_event* stop, float*
   return TL_OK;
 }
 
+// Host-side wait for one recorded event.  Reads nothing of the context but its device ordinal
+// and writes nothing to it (no error text), so a worker thread may call it while the thread
+// that owns the context keeps enqueueing work.
+int32_t tl_event_synchronize(tl_ctx* ctx, tl_event* ev) {
+  if (!ctx || !ev) return TL_ERR_INVALID_ARG;
+  DeviceGuard guard(ctx->device);
+  return cudaEventSynchronize(ev->ev) == cudaSuccess ? TL_OK : TL_ERR_CUDA;
+}
+
 int32_t tl_event_destroy(tl_ctx* ctx, tl_event* ev) {
   TL_CHECK_CTX(ctx);
   if (!ev) return TL_OK;
@@ -636,7 +645,7 @@ int32_t tl_force_variant(tl_ctx* ctx, const tl_variant* v) {
     ctx->has_forced = false;
     return TL_OK;
   }
-  if (v->family != TL_FAMILY_QGEMV && v->family != TL_FAMILY_QGEMM)
+  if (v->family != TL_FAMILY_QGEMV && v->family != TL_FAMILY_QGEMM && v->family != TL_FAMILY_MATMUL)
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_force_variant: unknown family %d", v->family);
   ctx->forced = *v;
   ctx->has_forced = true;

@@ -38,7 +38,7 @@ struct tl_ctx {
   cudaStream_t stream = nullptr;
   int sm_count = 0;
   int l2_bytes = 0;
-  int64_t counters[TL_COUNTER_COUNT] = {0, 0, 0, 0, 0};
+  int64_t counters[TL_COUNTER_COUNT] = {};
   int64_t async_errors = 0;
   std::string last_error;
   // library-owned scratch (split-K partials, GEMM staging), grown on demand and

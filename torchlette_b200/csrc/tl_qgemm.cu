@@ -31,12 +31,7 @@
 #include "tl_common.cuh"
 #include "tl_tma.cuh"
 
-#ifdef TL_TRACE
-__device__ long long g_tl_trace[4][64][6];
-#define TL_TR(role, it, ev) do { if (blockIdx.x == 0 && (it) < 64) g_tl_trace[role][it][ev] = clock64(); } while (0)
-#else
 #define TL_TR(role, it, ev) do {} while (0)
-#endif
 
 namespace {
 
@@ -772,8 +767,3 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   return TL_OK;
 }
 
-#ifdef TL_TRACE
-extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_trace(void* dst, size_t bytes) {
-  return cudaMemcpyFromSymbol(dst, g_tl_trace, bytes) == cudaSuccess ? 0 : -1;
-}
-#endif

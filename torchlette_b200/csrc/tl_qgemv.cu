@@ -88,27 +88,8 @@ struct GemvArgs {
   float wscale;    // 1/127 for the snorm convention, 1 for direct
   int32_t row0;    // first batch row of this launch (epilogue binary inputs index absolute rows)
   int32_t m_total;
-#ifdef TL_TRACE
-  int32_t trace_id;  // launch number, for the device-side timeline of traced builds
-#endif
 };
 
-#ifdef TL_TRACE
-// per launch: min/max CTA start, min/max time the dependency wait was passed, min/max CTA end,
-// max time the first weight block had landed
-__device__ unsigned long long g_ring_trace[512][8];
-__device__ __forceinline__ unsigned long long ring_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TL_RT_MIN(id, ev) do { if (threadIdx.x == 0 && (id) < 512) atomicMin(&g_ring_trace[id][ev], ring_now()); } while (0)
-#define TL_RT_MAX(id, ev) do { if (threadIdx.x == 0 && (id) < 512) atomicMax(&g_ring_trace[id][ev], ring_now()); } while (0)
-int g_ring_trace_next = 0;
-#else
-#define TL_RT_MIN(id, ev) do {} while (0)
-#define TL_RT_MAX(id, ev) do {} while (0)
-#endif
 
 // ---------------------------------------------------------------------------
 // 0: scalar fallback.  One warp per output row; lane l walks words l, l+32, ...
@@ -766,11 +747,6 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   const uint32_t ring_base = uint32_t(__cvta_generic_to_shared(ring)) + uint32_t(tid) * 16u;
   const uint32_t slot_bytes = uint32_t(nthreads) * 16u;  // one [blockDim] row of 16-byte words
 
-#ifdef TL_TRACE
-  const int trace_id = p.trace_id;
-#endif
-  TL_RT_MIN(trace_id, 0);
-  TL_RT_MAX(trace_id, 1);
   // let the next kernel in the stream start its own weight prefetch as early as possible
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 #pragma unroll
@@ -783,8 +759,6 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   }
   // weights never depend on the previous kernel; activations (its output) and our own stores do
   asm volatile("griddepcontrol.wait;" ::: "memory");
-  TL_RT_MIN(trace_id, 2);
-  TL_RT_MAX(trace_id, 3);
   if (rin) reduce_in_prologue(*rin);  // the activations are written by CTAs of THIS grid: read them through L2
   uint32_t push2_half = 0, push2_epoch = 0;
   if (PUSH == 2) {
@@ -869,7 +843,6 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
     }
   }
   cp_async_wait<0>();
-  TL_RT_MAX(trace_id, 6);
 
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -965,8 +938,6 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       }
     }
   }
-  TL_RT_MIN(trace_id, 4);
-  TL_RT_MAX(trace_id, 5);
 }
 
 // ---------------------------------------------------------------------------
@@ -1944,9 +1915,6 @@ int32_t tl_launch_qgemv(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   p.scales_dtype = q.scales_dtype; p.out_dtype = out_dtype;
   p.wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
   p.row0 = 0; p.m_total = m;
-#ifdef TL_TRACE
-  p.trace_id = g_ring_trace_next++;
-#endif
   const bool grouped = q.group_size != k;
   int block = v.p0 * 32;
   int grid = 0, launches = 1;
@@ -2195,9 +2163,6 @@ extern "C" int32_t tl_qgemv_nt_static_scratch(tl_ctx* ctx, const void* a, int32_
   p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
   p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
   p.row0 = 0; p.m_total = m;
-#ifdef TL_TRACE
-  p.trace_id = g_ring_trace_next++;
-#endif
   TmaArgs ta{};
   ta.scratch = reinterpret_cast<float*>(base);
   ta.counters = reinterpret_cast<unsigned*>(base + sbytes);
@@ -2321,15 +2286,9 @@ extern "C" int32_t tl_qgemv_nt_batched(tl_ctx* ctx, const void* a, int32_t a_dty
     p.scales_dtype = qdesc->scales_dtype; p.out_dtype = out_dtype;
     p.wscale = qdesc->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
     p.row0 = 0; p.m_total = m;
-#ifdef TL_TRACE
-    p.trace_id = g_ring_trace_next;
-#endif
     tiles += (items[i].n + 15) / 16;
   }
   b.tile_start[kMaxBatchItems] = int32_t(tiles);
-#ifdef TL_TRACE
-  g_ring_trace_next++;
-#endif
   if (ctx->push_pending) {
     if (!tl_push_matches(ctx, a, a_dtype, m, k))
       return tl_set_error(ctx, TL_ERR_INVALID_ARG,
@@ -2485,20 +2444,6 @@ __device__ __forceinline__ ChainFetchRec chain_load_fetch(const ChainTile* t) {
   return r;
 }
 
-#ifdef TL_TRACE
-__device__ unsigned long long g_chain_trace[2][256][6];
-__device__ __forceinline__ unsigned long long chain_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define TL_CTR(ph, ev) do { if (threadIdx.x == 0 && (blockIdx.x == 0 || blockIdx.x == 200) && (ph) < 256) g_chain_trace[blockIdx.x ? 1 : 0][ph][ev] = chain_now(); } while (0)
-__device__ unsigned long long g_chain_iter[4][32][4];
-#define TL_CIT(ph, it, ev) do { if (threadIdx.x == 0 && blockIdx.x == 0 && (ph) >= 4 && (ph) < 8 && (it) < 32) g_chain_iter[(ph) - 4][it][ev] = chain_now(); } while (0)
-#else
-#define TL_CTR(ph, ev) do {} while (0)
-#define TL_CIT(ph, it, ev) do {} while (0)
-#endif
 
 // A whole record, for the consumer side (five 16-byte broadcast loads).
 struct ChainRec {
@@ -2582,7 +2527,6 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
   while (cur.k != 0) {
     const ChainRec nxt = chain_load_rec(my + cj + 1);  // used at the end of this tile
     // ---- gate: the activations of this phase are the stores of the phases before it ----
-    TL_CTR(cur.phase, 0);
     if (cur.wait_for > 0) {
       if (tid == 0) {
         const unsigned want = unsigned(cur.wait_for);
@@ -2600,7 +2544,6 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
       if (s_abort) break;
       __threadfence();
     }
-    TL_CTR(cur.phase, 1);
     const int k = cur.k, n = cur.n;
     const int64_t tile_row = cur.tile_row;
     const AT* a = reinterpret_cast<const AT*>(cur.a);
@@ -2667,9 +2610,7 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
             bq[d][nt][1] = ld_act128(src + 8);
           }
         }
-        TL_CIT(cur.phase, i, 0);
         cp_async_wait<S - 1>();
-        TL_CIT(cur.phase, i, 1);
         const uint4 wl = ring[(2 * slot) * kThreads + tid];
         const uint4 wh = ring[(2 * slot + 1) * kThreads + tid];
         float acc[NT][4];
@@ -2691,9 +2632,7 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
             MmaOps<AT>::mma(acc[nt], a0, a1, a2, a3, b0, b1);
           }
         }
-        TL_CIT(cur.phase, i, 2);
         fetch_into(slot);  // the slot's words are in registers and consumed: refill it
-        TL_CIT(cur.phase, i, 3);
         slot = slot + 1 == S ? 0 : slot + 1;
         if (GROUPED) {
           const int gi = ((warp + i * W) * 64) / group;
@@ -2716,7 +2655,6 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
     }
 
     // ---- the W warps' partial tiles meet in shared memory; scale, epilogue, store ----
-    TL_CTR(cur.phase, 2);
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -2748,13 +2686,10 @@ __global__ void __launch_bounds__(W * 32, MINB) qgemv_chain_kernel(const ChainAr
       }
     }
     __syncthreads();  // the stores above are done, and `red` may be overwritten
-    TL_CTR(cur.phase, 3);
     // ---- leaving a phase = one arrival on its counter ----
     if (cur.arrive && tid == 0) {
       __threadfence();
-      TL_CTR(cur.phase, 4);
       atomicAdd(c.bar + cur.phase, 1u);
-      TL_CTR(cur.phase, 5);
     }
     cur = nxt;
     ++cj;
@@ -2960,24 +2895,6 @@ extern "C" int32_t tl_qgemv_chain_launch(tl_ctx* ctx, tl_chain* chain) {
   return TL_OK;
 }
 
-#ifdef TL_TRACE
-extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_trace(void* dst, size_t bytes) {
-  return cudaMemcpyFromSymbol(dst, g_chain_trace, bytes) == cudaSuccess ? 0 : -1;
-}
-extern "C" __attribute__((visibility("default"))) int32_t tl_debug_ring_trace(void* dst, size_t bytes, int32_t reset) {
-  if (reset) {
-    std::vector<unsigned long long> init(512 * 8);
-    for (int i = 0; i < 512; ++i)
-      for (int e = 0; e < 8; ++e) init[size_t(i) * 8 + e] = (e == 0 || e == 2 || e == 4) ? ~0ull : 0ull;
-    if (reset == 1) g_ring_trace_next = 0;
-    return cudaMemcpyToSymbol(g_ring_trace, init.data(), init.size() * 8) == cudaSuccess ? 0 : -1;
-  }
-  return cudaMemcpyFromSymbol(dst, g_ring_trace, bytes) == cudaSuccess ? 0 : -1;
-}
-extern "C" __attribute__((visibility("default"))) int32_t tl_debug_read_chain_iter(void* dst, size_t bytes) {
-  return cudaMemcpyFromSymbol(dst, g_chain_iter, bytes) == cudaSuccess ? 0 : -1;
-}
-#endif
 
 // ---------------------------------------------------------------------------
 // Fused row-parallel GEMV + all-reduce (host side)
