@@ -241,6 +241,54 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                                        "frac_of_hbm_peak": gbs / hbm_peak, "epilogue": "bias+gelu, f16 out",
                                        "l2": f"rotating over {copies} weight copies (352 MB)"}
     del w, s
+    # the dense (unquantized f16) counterpart through tl_matmul: the tensor-core GEMV at the same
+    # shape (2 bytes per weight, so twice the traffic), and the tiled kernel on a square product
+    copies = 3  # 3 x 117.4 MB = 352 MB
+    wd = (torch.randn(copies, n, k, device=dev) * 0.02).to(torch.float16)
+    for m in (1, 16):
+        x = torch.randn(m, k, device=dev).to(torch.float16)
+        y = torch.empty(m, n, dtype=torch.float16, device=dev)
+
+        def sweep_dense(reps):
+            for _ in range(reps):
+                for c in range(copies):
+                    B.check(ctx, lib.tl_matmul(ctx, x.data_ptr(), wd[c].data_ptr(), y.data_ptr(), m, n, k, 1, 0, 0, m * n, 0, 1,
+                                               1.0, B.TL_F16, B.TL_F16, B.TL_F16, -1, -1, C.byref(e), None))
+        sweep_dense(3)
+        be.sync()
+        reps = 20
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        sweep_dense(reps)
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        us = ms.value * 1e3 / (reps * copies)
+        nbytes = 2 * n * k + n * 4 + m * k * 2 + m * n * 2
+        out[f"dense_gemv_f16_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": nbytes / us / 1e3,
+                                                 "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
+                                                 "l2": f"rotating over {copies} weight copies (352 MB)"}
+    del wd
+    md = 2048
+    xa = (torch.randn(md, md, device=dev) * 0.05).to(torch.float16)
+    xb = (torch.randn(md, md, device=dev) * 0.05).to(torch.float16)
+    yc = torch.empty(md, md, dtype=torch.float16, device=dev)
+
+    def run_dense():
+        B.check(ctx, lib.tl_matmul(ctx, xa.data_ptr(), xb.data_ptr(), yc.data_ptr(), md, md, md, 1, 0, 0, md * md, 0, 0, 1.0,
+                                   B.TL_F16, B.TL_F16, B.TL_F16, -1, -1, None, None))
+    for _ in range(3):
+        run_dense()
+    be.sync()
+    B.check(ctx, lib.tl_event_record(ctx, ev0))
+    for _ in range(5):
+        run_dense()
+    B.check(ctx, lib.tl_event_record(ctx, ev1))
+    ms = C.c_float()
+    B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+    tf = 2.0 * md ** 3 / (ms.value / 5 * 1e-3) / 1e12
+    out["dense_matmul_f16_2048x2048x2048"] = {"ms": ms.value / 5, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak,
+                                              "kernel": "tiled (CUDA cores, f32 accumulate): not a tensor-core kernel"}
+    del xa, xb, yc
     # prefill GEMM, config 3
     for (m, kk, nn) in ((2048, 4096, 14336), (2048, 14336, 4096)):
         w = torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device=dev)
@@ -274,6 +322,66 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
         out[f"qgemm_{m}x{kk}x{nn}"] = {"ms": ms.value / reps, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak,
                                        "epilogue": "gelu, bf16 out"}
         del w, s, x, y
+    # the two small configurations: a 2048 x 2048 f32 GEMV, and the seven 0.6B-shaped decode
+    # projections (q, k, v, gate, up on K=1024; o on K=2048; down on K=3072) replayed as ONE
+    # captured graph.  1-4 MB of weights per launch is under a microsecond of HBM time (and fits
+    # L2), so these are launch-latency figures, not bandwidth figures.
+    def timed_graph(enqueue, reps=200):
+        enqueue()
+        be.sync()
+        B.check(ctx, lib.tl_graph_begin(ctx))
+        enqueue()
+        g = C.c_void_p()
+        B.check(ctx, lib.tl_graph_end(ctx, C.byref(g)))
+        for _ in range(5):
+            B.check(ctx, lib.tl_graph_launch(ctx, g))
+        be.sync()
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        for _ in range(reps):
+            B.check(ctx, lib.tl_graph_launch(ctx, g))
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        B.check(ctx, lib.tl_graph_destroy(ctx, g))
+        return ms.value * 1e3 / reps
+
+    def make_proj(nn, kk):
+        return (torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device=dev),
+                torch.empty(nn, dtype=torch.float32, device=dev).uniform_(0.001, 0.01))
+    w0, s0 = make_proj(2048, 2048)
+    x0 = torch.randn(1, 2048, device=dev)
+    y0 = torch.empty(1, 2048, device=dev)
+    q0 = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, 2048, B.TL_F32, B.TL_SCALE_DIRECT)
+    us0 = timed_graph(lambda: B.check(ctx, lib.tl_qgemv_nt(ctx, x0.data_ptr(), B.TL_F32, w0.data_ptr(), s0.data_ptr(), y0.data_ptr(),
+                                                           B.TL_F32, 1, 2048, 2048, C.byref(q0), 1.0, None)))
+    b0 = 2048 * 2048 + 2048 * 4 * 3
+    out["config0_gemv_2048x2048_f32"] = {"us_per_launch": us0, "algorithmic_bytes": b0, "GBps": b0 / us0 / 1e3,
+                                         "bound": "launch latency (4 MB of weights, L2-resident across replays)"}
+    shapes = [("q", 2048, 1024), ("k", 1024, 1024), ("v", 1024, 1024), ("gate", 3072, 1024), ("up", 3072, 1024),
+              ("o", 1024, 2048), ("down", 1024, 3072)]
+    projs = {nm: make_proj(nn, kk) + (torch.empty(1, nn, dtype=torch.float16, device=dev), nn, kk) for nm, nn, kk in shapes}
+    acts = {kk: torch.randn(1, kk, device=dev).to(torch.float16) for kk in (1024, 2048, 3072)}
+
+    def one(nm):
+        wq, sq, yq, nn, kk = projs[nm]
+        qd = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, kk, B.TL_F32, B.TL_SCALE_DIRECT)
+        B.check(ctx, lib.tl_qgemv_nt(ctx, acts[kk].data_ptr(), B.TL_F16, wq.data_ptr(), sq.data_ptr(), yq.data_ptr(), B.TL_F16,
+                                     1, nn, kk, C.byref(qd), 1.0, None))
+
+    def group(names):
+        items = (B.QGemvItem * len(names))()
+        for i, nm in enumerate(names):
+            wq, sq, yq, nn, kk = projs[nm]
+            items[i] = B.QGemvItem(wq.data_ptr(), sq.data_ptr(), yq.data_ptr(), nn, 1.0, None)
+        kk = projs[names[0]][4]
+        qd = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, kk, B.TL_F32, B.TL_SCALE_DIRECT)
+        B.check(ctx, lib.tl_qgemv_nt_batched(ctx, acts[kk].data_ptr(), B.TL_F16, items, len(names), B.TL_F16, 1, kk, C.byref(qd)))
+    us7 = timed_graph(lambda: [one(nm) for nm, _, _ in shapes])
+    us4 = timed_graph(lambda: (group(["q", "k", "v"]), group(["gate", "up"]), one("o"), one("down")))
+    b1 = sum(nn * kk + nn * 4 + nn * 2 for _, nn, kk in shapes) + 2 * (1024 + 2048 + 3072)
+    out["config1_seven_projections_graph"] = {
+        "us_per_replay_7_launches": us7, "us_per_replay_4_launches_batched": us4, "algorithmic_bytes": b1,
+        "GBps_4_launches": b1 / us4 / 1e3, "bound": "launch latency (12.6 MB of weights per replay, L2-resident)"}
     lib.tl_event_destroy(ctx, ev0)
     lib.tl_event_destroy(ctx, ev1)
     return out
@@ -442,25 +550,29 @@ def run_gpu(args):
     # (3 blocks at least) and the MEDIAN block (of the max over ranks) is reported.  The clock sampler
     # starts before the barrier, and one untimed step right behind the barrier aligns the ranks on
     # the device (it holds all-reduces), so host start-up skew never lands inside a timed block.
+    def timed_blocks(st, min_seconds):
+        blocks, total = [], 0.0
+        while len(blocks) < 3 or (total < min_seconds and len(blocks) < 200):
+            barrier()
+            st.step()
+            B.check(ctx, lib.tl_event_record(ctx, ev0))
+            for _ in range(args.steps):
+                st.step()
+            B.check(ctx, lib.tl_event_record(ctx, ev1))
+            barrier()
+            ms = C.c_float()
+            B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+            blocks.append(max_over_ranks(ms.value))
+            total += blocks[-1] * 1e-3
+        return blocks
+
     for _ in range(args.warmup):
         stack.step()
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     launches0 = be.getKernelLaunchCount()
-    block_ms, timed_s = [], 0.0
-    while len(block_ms) < 3 or (timed_s < 0.5 and len(block_ms) < 200):
-        barrier()
-        stack.step()
-        B.check(ctx, lib.tl_event_record(ctx, ev0))
-        for _ in range(args.steps):
-            stack.step()
-        B.check(ctx, lib.tl_event_record(ctx, ev1))
-        barrier()
-        ms = C.c_float()
-        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-        block_ms.append(max_over_ranks(ms.value))
-        timed_s += block_ms[-1] * 1e-3
+    block_ms = timed_blocks(stack, 0.5)
     launches = (be.getKernelLaunchCount() - launches0) * args.steps // ((args.steps + 1) * len(block_ms))
     dev_ms = statistics.median(block_ms)
     ms_per_step = dev_ms / args.steps
@@ -490,6 +602,27 @@ def run_gpu(args):
     finite = bool(torch.isfinite(hlogits).all().item()) and float(hlogits.abs().max()) > 0
 
     parity = stack_parity(stack, dist if world > 1 else None)
+
+    # ---- the same stack at batch 1, and (N > 1) with the gathered column-parallel layout -------
+    def algorithmic_bytes(st, m):
+        b = sum(p.n * p.k + p.n * 4 + m * p.k * 2 + m * p.n * 2 for p in st.layers[0]) * cfg.layers
+        return b + st.lm_head.n * st.lm_head.k + st.lm_head.n * 4 + m * st.lm_head.k * 2 + m * st.lm_head.n * 4
+
+    def secondary(batch, tp_mode):
+        c2 = StackConfig(**{**QWEN3_8B.__dict__, "batch": batch})
+        st = DecodeStack(be, c2, rank, world, tp_mode, allreduce=stack.allreduce, fuse=not args.no_fuse, chain=False)
+        st.capture()
+        for _ in range(max(3, args.warmup)):
+            st.step()
+        blocks = timed_blocks(st, 0.2)
+        par = stack_parity(st, dist if world > 1 else None)
+        ms_step = statistics.median(blocks) / args.steps
+        res = {"batch": batch, "tp_mode": tp_mode if world > 1 else "none", "ms_per_step": ms_step, "tok_s": batch / (ms_step * 1e-3),
+               "GBps_per_rank": algorithmic_bytes(st, batch) / (ms_step * 1e-3) / 1e9, "timed_blocks": len(blocks), "parity": par}
+        st.destroy()
+        return res
+    stack_m1 = None if (args.no_extras or cfg.batch == 1) else secondary(1, args.tp_mode)
+    stack_gather = None if (args.no_extras or world == 1 or args.tp_mode == "gather") else secondary(cfg.batch, "gather")
 
     hbm_peak, tf_peak, which = measured_peaks()
     # Per rank: the algorithmic bytes of its own shard, summed over the 253 launches of a step.
@@ -550,6 +683,11 @@ def run_gpu(args):
             "parity": parity,
             "weight_GB_per_step": cfg.weight_bytes_per_step() / 1e9,
         }
+        if stack_m1 is not None:
+            stack_m1["frac_of_hbm_peak"] = stack_m1["GBps_per_rank"] / hbm_peak
+            line["stack_m1"] = stack_m1
+        if stack_gather is not None:
+            line["stack_tp_gather"] = stack_gather
         if cpu is not None:
             line["cpu_baseline"] = cpu
         if extras:
