@@ -487,7 +487,7 @@ def run_gpu(args):
             ok = 1
             try:
                 hbuf = (C.c_char * 64)()
-                B.check(ctx, lib.tl_p2p_create(ctx, args.batch * 4096 * 4, hbuf))
+                B.check(ctx, lib.tl_p2p_create(ctx, args.batch * 4096 * 8, hbuf))  # {f32 partial, epoch} per value
                 mine = bytes(hbuf)
             except tb.TlError as ex:
                 ok, mine = 0, bytes(64)

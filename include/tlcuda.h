@@ -286,7 +286,7 @@ typedef struct tl_plan_receipt {
   int32_t grid[3];
   int32_t block;
   int32_t split_k;
-  int32_t from_tuning_cache; /* 1 when a per-shape tuned winner was used */
+  int32_t from_tuning_cache; /* 1: the exact shape's tuned winner was used; 2: its shape class's */
   int32_t epilogue_engaged;
 } tl_plan_receipt;
 /* Pure function of geometry, dtypes and format: what tl_qmatmul_nt would run. */
@@ -337,6 +337,17 @@ TL_API int32_t tl_counters_reset(tl_ctx* ctx);
 /* ---- autotune (src/backend/webgpu/matmul/autotune.ts:97-329;
  * src/backend/webgpu/matmul/dispatch.ts:79-141, 405-578) ---------------------- */
 typedef struct tl_shape { int64_t m, n, k; } tl_shape;
+/* classifyShape (src/backend/webgpu/matmul/types.ts:77-200): the class a geometry falls in.  A shape
+ * tuned by tl_pretune (or imported) also becomes its class's winner; selection order is
+ * forced variant -> exact-shape winner -> class winner -> default, each re-gated on
+ * applicability.  tl_plan_receipt.from_tuning_cache: 0 none, 1 exact shape, 2 shape class. */
+enum {
+  TL_SHAPE_SQUARE_SMALL = 0, TL_SHAPE_SQUARE_MEDIUM = 1, TL_SHAPE_SQUARE_LARGE = 2, TL_SHAPE_TALL_SKINNY = 3,
+  TL_SHAPE_SHORT_WIDE = 4, TL_SHAPE_LARGE_K = 5, TL_SHAPE_SMALL_K = 6, TL_SHAPE_GEMV = 7, TL_SHAPE_GEMV_ROW = 8,
+  TL_SHAPE_BATCHED_SMALL = 9
+};
+TL_API int32_t tl_classify_shape(int64_t m, int64_t n, int64_t k, int64_t batch);
+TL_API const char* tl_shape_class_name(int32_t shape_class);
 TL_API int32_t tl_autotune_set_enabled(tl_ctx* ctx, int32_t enabled);
 TL_API int32_t tl_autotune_is_enabled(tl_ctx* ctx);
 /* pretuneMatmulShapes: time every applicable candidate for each shape on
@@ -414,6 +425,13 @@ TL_API int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int
  * context's stream, then clears flags, call counters and the status word of ITS buffer), and the
  * host must put a barrier between the resets and the next peer collective.  No counterpart in the
  * reference. */
+/* The same exchange for f32 partial sums whose total is stored as dst_dtype (f32, f16 or bf16): the
+ * sum is rounded once, so a row-parallel product is as accurate sharded as unsharded.  (With 16-bit
+ * partials every rank's rounding error, up to half an ulp of a partial that may be much larger than
+ * the total, adds up: measured 1.0e-2 on the metric |x - ref| / max(1, |ref|) at 8 ranks.)
+ * dst may alias src only when dst_dtype is f32.  count * 4 bytes must fit the exchange buffer. */
+TL_API int32_t tl_allreduce_sum_p2p_f32_to(tl_ctx* ctx, const float* src, void* dst, int32_t dst_dtype,
+                                           int64_t count);
 TL_API int32_t tl_p2p_reset(tl_ctx* ctx);
 /* Diagnostic hook: maps this rank's OWN exchange buffer in place of every peer of a `world`-rank
  * group (rank 0), so that a single process can run the peer kernels on local memory only.  The

@@ -265,3 +265,85 @@ def test_binary_ops_and_cast_round_trip(backend):
     np.testing.assert_array_equal(_read_f32(be, back), a_v.astype(np.float16).astype(np.float32))
     for t in (a, b, h, bf, back):
         t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# the tensor-core route (tcgen05, both operands from shared memory)
+# ---------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,k,n", [(128, 64, 128), (256, 256, 512), (130, 72, 200), (33, 200, 201), (512, 1024, 1000)])
+def test_dense_tensor_core_route_nt(backend, dtype, m, k, n):
+    be = backend
+    rng = np.random.default_rng(m + 7 * n + 13 * k)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], dtype)
+    w, w_v = _to_dev(be, rng.uniform(-1, 1, n * k).astype(np.float32), [n, k], dtype)
+    assert be.planMatmul(m, n, k, dtype, dtype, transB=True)["variant"].startswith("matmul.tc")
+    y = be.ops.matmul(x, be.ops.transpose(w))
+    ref = _ref(x_v, w_v.T)
+    assert _rel(_read_f32(be, y), ref) <= 1e-3
+    # the exactly representable pattern inputs give exact sums: bit-equal to the oracle
+    xp, xp_v = _to_dev(be, _pattern(m * k, 0), [m, k], dtype)
+    wp, wp_v = _to_dev(be, _pattern(n * k, 3), [n, k], dtype)
+    yp = be.ops.matmul(xp, be.ops.transpose(wp))
+    np.testing.assert_array_equal(_read_f32(be, yp), _ref(xp_v, wp_v.T))
+    for t in (x, w, y, xp, wp, yp):
+        t.destroy()
+
+
+@pytest.mark.parametrize("trans_a,trans_b", [(False, False), (True, False), (True, True)])
+def test_dense_tensor_core_route_other_layouts(backend, trans_a, trans_b):
+    be = backend
+    m, k, n = 96, 136, 264
+    rng = np.random.default_rng(11)
+    a_t, a_stored = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [k, m] if trans_a else [m, k], "f16")
+    b_t, b_stored = _to_dev(be, rng.uniform(-1, 1, k * n).astype(np.float32), [n, k] if trans_b else [k, n], "f16")
+    a_view = be.ops.transpose(a_t) if trans_a else a_t
+    b_view = be.ops.transpose(b_t) if trans_b else b_t
+    assert be.planMatmul(m, n, k, "f16", "f16", transA=trans_a, transB=trans_b)["variant"].startswith("matmul.tc")
+    y = be.ops.matmul(a_view, b_view)
+    ref = _ref(a_stored.T if trans_a else a_stored, b_stored.T if trans_b else b_stored)
+    assert _rel(_read_f32(be, y), ref) <= 1e-3
+    for t in (a_t, b_t, y):
+        t.destroy()
+
+
+@pytest.mark.parametrize("out_dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("epi", [("bias", None), ("bias", "gelu"), (None, "silu"), ("bias", "relu"), "residual"])
+def test_dense_tensor_core_epilogues(backend, out_dtype, epi):
+    be = backend
+    m, k, n = 160, 128, 272
+    rng = np.random.default_rng(2)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "bf16")
+    w, w_v = _to_dev(be, (rng.uniform(-1, 1, n * k) * 0.2).astype(np.float32), [n, k], "bf16")
+    bias_v = rng.uniform(-1, 1, n).astype(np.float32)
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    res_v = rng.uniform(-1, 1, (m, n)).astype(np.float32)
+    res_t = be.ops.tensorFromArray(res_v, [m, n], "f32")
+    if epi == "residual":
+        chain = [("add", res_t), ("relu", None)]
+        ref = orc.unary("relu", (_ref(x_v, w_v.T) + res_v).astype(np.float32))
+    else:
+        chain = ([("add", bias_t)] if epi[0] else []) + ([(epi[1], None)] if epi[1] else [])
+        ref = _ref(x_v, w_v.T, bias_v if epi[0] else None, epi[1])
+    if out_dtype != "f32":
+        chain.append(("cast", out_dtype))
+    plan = tb.detectMatmulEpilogue(chain)
+    y = be.ops.matmul(x, be.ops.transpose(w), {"epilogue": plan[0], "epilogueInputs": plan[1]})
+    assert y.dtype == out_dtype
+    assert _rel(_read_f32(be, y), ref) <= (1e-3 if out_dtype == "f32" else 1e-2)
+    for t in (x, w, bias_t, res_t, y):
+        t.destroy()
+
+
+def test_dense_tensor_core_batched(backend):
+    be = backend
+    bs, m, k, n = 3, 64, 128, 128
+    rng = np.random.default_rng(4)
+    a, a_v = _to_dev(be, rng.uniform(-1, 1, bs * m * k).astype(np.float32), [bs, m, k], "f16")
+    b, b_v = _to_dev(be, rng.uniform(-1, 1, bs * k * n).astype(np.float32), [bs, k, n], "f16")
+    y = be.ops.matmul(a, b)
+    g = _read_f32(be, y)
+    for i in range(bs):
+        assert _rel(g[i], _ref(a_v[i], b_v[i])) <= 1e-3
+    for t in (a, b, y):
+        t.destroy()

@@ -76,6 +76,26 @@ def _rank_main(rank, world, port, q):
             assert np.allclose(be.ops.read(t).astype(np.float32), expect, rtol=2e-3, atol=2e-3)
             call += 1
             t.destroy()
+        # f32 partial sums, 16-bit result: the sum is rounded once (ragged count: scalar tail)
+        for dst_dtype, count in [("f16", 8 * 4096), ("bf16", 1003)]:
+            src = be.ops.empty([count], "f32")
+            dst = be.ops.empty([count], dst_dtype)
+            for _ in range(3):
+                be._upload(src.buffer, _data(rank, call, count, "f32"))
+                B.check(ctx, lib.tl_allreduce_sum_p2p_f32_to(ctx, src.buffer, dst.buffer, B.DTYPE_ID[dst_dtype], count))
+                total = np.zeros(count, np.float32)
+                for r in range(world):  # rank order, f32, like the kernel
+                    total = total + _data(r, call, count, "f32")
+                got = be.ops.read(dst)
+                if dst_dtype == "f16":
+                    assert np.array_equal(got.view(np.uint16), total.astype(np.float16).view(np.uint16)), (dst_dtype, call)
+                else:
+                    from oracle import oracle as orc
+                    assert np.array_equal(got.reshape(-1), orc.bf16_bits_rne(total)), (dst_dtype, call)
+                results[call] = np.ascontiguousarray(got).tobytes()
+                call += 1
+            src.destroy()
+            dst.destroy()
         # replay: two all-reduces captured once, replayed three times with fresh inputs
         count = 4096
         a, b = be.ops.empty([count], "f32"), be.ops.empty([count], "f32")
@@ -214,7 +234,7 @@ def _stack_rank_main(rank, world, port, q):
         dist.broadcast_object_list(ident, src=0)
         B.check(ctx, lib.tl_comm_init(ctx, rank, world, (C.c_char * B.TL_COMM_ID_BYTES).from_buffer_copy(ident[0])))
         hbuf = (C.c_char * 64)()
-        B.check(ctx, lib.tl_p2p_create(ctx, TINY.batch * TINY.hidden * 4, hbuf))
+        B.check(ctx, lib.tl_p2p_create(ctx, TINY.batch * TINY.hidden * 8, hbuf))
         handles = [None] * world
         dist.all_gather_object(handles, bytes(hbuf))
         B.check(ctx, lib.tl_p2p_attach(ctx, (C.c_char * (64 * world)).from_buffer_copy(b"".join(handles))))

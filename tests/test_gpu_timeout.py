@@ -95,7 +95,7 @@ def test_push_and_reduce_on_read_on_one_gpu():
     try:
         m, n1, k1, n2 = 8, 512, 256, 320
         handle = (C.c_char * 64)()
-        B.check(ctx, lib.tl_p2p_create(ctx, m * n1 * 4, handle))
+        B.check(ctx, lib.tl_p2p_create(ctx, m * n1 * 8, handle))
         B.check(ctx, lib.tl_p2p_attach_loopback(ctx, 1))
         c1 = cases.per_channel_case(n1, k1, m, seed=41, act_dtype="f16")
         c2 = cases.per_channel_case(n2, n1, m, seed=42, act_dtype="f16")

@@ -81,6 +81,10 @@ def detectMatmulEpilogue(chain: Sequence[tuple], matmulDtype: str = "f32"):
     """The lazy graph's epilogue-fusion decision for the ops that follow a matmul
     (matmul-epilogue.ts:131-262), applied to a linear chain description.
 
+    The decision itself is ``epilogue_fusion.detectMatmulEpilogueCore`` (consumer counts, outside
+    references, reshape skips); this adapter feeds it a straight chain.  In a chain the name "gelu"
+    means the tanh form unless the operand says {"approximate": "none"}.
+
     ``chain`` is a list of (opName, operand) where operand is a CudaTensor for
     add/sub/mul, a dtype name for cast, a dict of options for gelu
     ({"approximate": "none"} selects gelu_erf, matmul-epilogue.ts:52-56) and
@@ -88,40 +92,25 @@ def detectMatmulEpilogue(chain: Sequence[tuple], matmulDtype: str = "f32"):
     four ops, or None when nothing fuses.  Unlike the reference
     (graph-compiler.ts:150-152) a quantized B operand does not veto the fusion.
     """
-    ops, inputs = [], []
-    out_dtype = matmulDtype
-    consumed = 0
-    for name, operand in chain:
-        if consumed >= 4:
-            break
+    from .epilogue_fusion import PlanNode, detectMatmulEpilogueCore
+
+    # the chain as a plan: every op consumes the one before it
+    nodes = [PlanNode(0, "matmul", [], [], matmulDtype)]
+    for i, (name, operand) in enumerate(chain):
+        prev = nodes[-1]
         if name == "cast":
-            ops.append({"kind": "cast", "toDtype": operand})
-            out_dtype = operand
-        elif name == "add":
-            if len(inputs) >= 4:
-                break
-            kind = "bias" if len(operand.shape) == 1 else "binary"
-            op = {"kind": kind, "inputIndex": len(inputs)}
-            if kind == "binary":
-                op["op"] = "add"
-            ops.append(op)
-            inputs.append(operand)
-        elif name in ("mul", "sub"):
-            if len(inputs) >= 4:
-                break
-            ops.append({"kind": "binary", "op": name, "inputIndex": len(inputs)})
-            inputs.append(operand)
-        elif name in _FUSIBLE_UNARY:
-            opname = name
-            if name == "gelu" and isinstance(operand, dict) and operand.get("approximate") == "none":
-                opname = "gelu_erf"
-            ops.append({"kind": "unary", "op": opname})
+            nodes.append(PlanNode(i + 1, "cast", [prev], [], operand, {"dtype": operand}))
+        elif name in ("add", "mul", "sub"):
+            nodes.append(PlanNode(i + 1, name, [prev, operand]))
+        elif name in ("gelu", "gelu_tanh", "gelu_erf"):
+            erf = name == "gelu_erf" or (isinstance(operand, dict) and operand.get("approximate") == "none")
+            nodes.append(PlanNode(i + 1, "gelu", [prev], [], None, None if erf else {"approximate": "tanh"}))
         else:
-            break
-        consumed += 1
-    if consumed == 0:
+            nodes.append(PlanNode(i + 1, name, [prev]))
+    plan = detectMatmulEpilogueCore(nodes, 0)
+    if plan is None:
         return None
-    return EpilogueConfig(ops, len(inputs), out_dtype), inputs, consumed
+    return EpilogueConfig(plan.epilogueOps, len(plan.epilogueInputs), plan.outputDtype), plan.epilogueInputs, plan.consumedCount - 1
 
 
 # ---------------------------------------------------------------------------
@@ -629,7 +618,12 @@ class CudaBackend:
         name = self._lib.tl_variant_name(C.byref(r.choice)).decode()
         return {"family": "gemv" if r.choice.family == B.TL_FAMILY_QGEMV else "gemm", "variant": name,
                 "choice": r.choice.as_tuple(), "grid": list(r.grid), "block": r.block, "splitK": r.split_k,
-                "fromTuningCache": bool(r.from_tuning_cache)}
+                "fromTuningCache": bool(r.from_tuning_cache),
+                "tuningCacheLevel": {0: None, 1: "shape", 2: "shapeClass"}[r.from_tuning_cache]}
+
+    def classifyShape(self, m: int, n: int, k: int, batchSize: int = 1) -> str:
+        """classifyShape (src/backend/webgpu/matmul/types.ts:146-200)."""
+        return self._lib.tl_shape_class_name(self._lib.tl_classify_shape(m, n, k, batchSize)).decode()
 
     def forceVariant(self, choice: Optional[tuple]):
         if choice is None:

@@ -120,6 +120,8 @@ SIGNATURES = {
     "tl_force_variant": (_I32, [_P, C.POINTER(Variant)]),
     "tl_counter_get": (_I64, [_P, _I32]),
     "tl_counters_reset": (_I32, [_P]),
+    "tl_classify_shape": (_I32, [_I64, _I64, _I64, _I64]),
+    "tl_shape_class_name": (C.c_char_p, [_I32]),
     "tl_autotune_set_enabled": (_I32, [_P, _I32]),
     "tl_autotune_is_enabled": (_I32, [_P]),
     "tl_pretune": (_I32, [_P, C.POINTER(Shape), _I32, _I32, _I32, C.POINTER(QuantDesc)]),
@@ -146,6 +148,7 @@ SIGNATURES = {
     "tl_p2p_create": (_I32, [_P, _SZ, _P]),
     "tl_p2p_attach": (_I32, [_P, _P]),
     "tl_allreduce_sum_p2p": (_I32, [_P, _P, _P, _I64, _I32]),
+    "tl_allreduce_sum_p2p_f32_to": (_I32, [_P, _P, _P, _I32, _I64]),
     "tl_p2p_reset": (_I32, [_P]),
     "tl_qgemv_nt_push": (_I32, _QARGS + [_I32, _I64, _I64, C.POINTER(QuantDesc), _F]),
     "tl_reduce_pending": (_I32, [_P]),

@@ -560,6 +560,8 @@ FN(ForceVariant) {
   if (!read_variant(env, argv[1], &v)) return undef(env);
   return check(env, c, tl_force_variant(c, &v));
 }
+FN(ClassifyShape) { ARGS(4); return num(env, tl_classify_shape(i64(env, argv[0]), i64(env, argv[1]), i64(env, argv[2]), i64(env, argv[3]))); }
+FN(ShapeClassName) { ARGS(1); return str(env, tl_shape_class_name(i32(env, argv[0]))); }
 FN(CounterGet) { ARGS(2); CTX(0); return num(env, (double)tl_counter_get(c, i32(env, argv[1]))); }
 FN(CountersReset) { ARGS(1); CTX(0); return check(env, c, tl_counters_reset(c)); }
 FN(AutotuneSetEnabled) { ARGS(2); CTX(0); return check(env, c, tl_autotune_set_enabled(c, i32(env, argv[1]))); }
@@ -652,6 +654,9 @@ FN(P2pAttachLoopback) { ARGS(2); CTX(0); return check(env, c, tl_p2p_attach_loop
 FN(P2pReset) { ARGS(1); CTX(0); return check(env, c, tl_p2p_reset(c)); }
 FN(AllreduceSumP2p) { ARGS(5); CTX(0); return check(env, c, tl_allreduce_sum_p2p(c, dptr(env, argv[1]), dptr(env, argv[2]), i64(env, argv[3]), i32(env, argv[4]))); }
 
+/* allreduceSumP2pF32To(ctx, srcF32, dst, dstDtype, count) */
+FN(AllreduceSumP2pF32To) { ARGS(5); CTX(0); return check(env, c, tl_allreduce_sum_p2p_f32_to(c, (const float*)dptr(env, argv[1]), dptr(env, argv[2]), i32(env, argv[3]), i64(env, argv[4]))); }
+
 #define EXPORT(js, fn) {js, 0, fn, 0, 0, 0, 0, 0}
 napi_value napi_register_module_v1(napi_env env, napi_value exports) {
   const napi_property_descriptor props[] = {
@@ -669,6 +674,7 @@ napi_value napi_register_module_v1(napi_env env, napi_value exports) {
       EXPORT("dequantInt8", DequantInt8), EXPORT("unpackInt8", UnpackInt8), EXPORT("matmul", Matmul),
       EXPORT("unaryOp", UnaryOp), EXPORT("binaryOp", BinaryOp), EXPORT("transpose2d", Transpose2d),
       EXPORT("planQmatmul", PlanQmatmul), EXPORT("variantName", VariantName), EXPORT("forceVariant", ForceVariant),
+      EXPORT("classifyShape", ClassifyShape), EXPORT("shapeClassName", ShapeClassName),
       EXPORT("counterGet", CounterGet), EXPORT("countersReset", CountersReset),
       EXPORT("autotuneSetEnabled", AutotuneSetEnabled), EXPORT("autotuneIsEnabled", AutotuneIsEnabled), EXPORT("pretune", Pretune),
       EXPORT("tuneSeed", TuneSeed), EXPORT("tuneGet", TuneGet), EXPORT("tuneClear", TuneClear), EXPORT("tuneRunCount", TuneRunCount),
@@ -679,7 +685,7 @@ napi_value napi_register_module_v1(napi_env env, napi_value exports) {
       EXPORT("commUniqueId", CommUniqueId), EXPORT("commInit", CommInit), EXPORT("commDestroy", CommDestroy),
       EXPORT("allgatherCols", AllgatherCols), EXPORT("allreduceSum", AllreduceSum), EXPORT("p2pCreate", P2pCreate),
       EXPORT("p2pAttach", P2pAttach), EXPORT("p2pAttachLoopback", P2pAttachLoopback), EXPORT("p2pReset", P2pReset),
-      EXPORT("allreduceSumP2p", AllreduceSumP2p), EXPORT("qgemvNtAllreduce", QgemvNtAllreduce), EXPORT("qgemvNtPush", QgemvNtPush),
+      EXPORT("allreduceSumP2p", AllreduceSumP2p), EXPORT("allreduceSumP2pF32To", AllreduceSumP2pF32To), EXPORT("qgemvNtAllreduce", QgemvNtAllreduce), EXPORT("qgemvNtPush", QgemvNtPush),
       EXPORT("reducePending", ReducePending),
   };
   napi_define_properties(env, exports, sizeof(props) / sizeof(props[0]), props);

@@ -522,6 +522,27 @@ int32_t tl_make_epi(tl_ctx* ctx, const tl_epilogue* e, float alpha, EpiParams* o
 }
 
 // ---------------------------------------------------------------------------
+// Shape classes (classifyShape, src/backend/webgpu/matmul/types.ts:146-200)
+// ---------------------------------------------------------------------------
+extern "C" int32_t tl_classify_shape(int64_t m, int64_t n, int64_t k, int64_t batch) {
+  if (m == 1 && n > 1) return TL_SHAPE_GEMV_ROW;
+  if (m == 1 || n == 1) return TL_SHAPE_GEMV;
+  if (batch > 1 && m * n < 512 * 512) return TL_SHAPE_BATCHED_SMALL;
+  if (k < 64 && m * n > 100000) return TL_SHAPE_SMALL_K;
+  if (double(k) / double(std::max(m, n)) > 4.0) return TL_SHAPE_LARGE_K;
+  if (double(m) / double(std::max(k, n)) > 4.0) return TL_SHAPE_TALL_SKINNY;
+  if (double(n) / double(std::max(k, m)) > 4.0) return TL_SHAPE_SHORT_WIDE;
+  const int64_t mx = std::max(m, std::max(n, k));
+  return mx < 512 ? TL_SHAPE_SQUARE_SMALL : mx < 2048 ? TL_SHAPE_SQUARE_MEDIUM : TL_SHAPE_SQUARE_LARGE;
+}
+
+extern "C" const char* tl_shape_class_name(int32_t cls) {
+  static const char* const names[] = {"square_small", "square_medium", "square_large", "tall_skinny", "short_wide",
+                                      "large_k", "small_k", "gemv", "gemv_row", "batched_small"};
+  return cls >= 0 && cls < int(sizeof(names) / sizeof(names[0])) ? names[cls] : "?";
+}
+
+// ---------------------------------------------------------------------------
 // Selection + the seam
 // ---------------------------------------------------------------------------
 static TuneKey make_key(int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q) {
@@ -536,12 +557,25 @@ bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dty
   return true;
 }
 
+static TuneKey make_class_key(int fam, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q) {
+  return TuneKey{tl_classify_shape(m, n, k, 1), fam, 0, a_dtype, q.group_size == k ? 0 : q.group_size, q.scales_dtype,
+                 q.scale_convention};
+}
+
+// A tuned winner also becomes its shape class's entry (the last shape tuned in a class wins), the
+// analogue of the reference's tuningCache keyed `${shapeClass}_${dtype}_...`
+// (src/backend/webgpu/matmul/dispatch.ts:146-160, autotune.ts:276-300).
+void tl_record_class_winner(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, const tl_variant& v) {
+  ctx->class_tuned[make_class_key(v.family, m, n, k, a_dtype, q)] = v;
+}
+
 // Order of precedence follows selectMatmulChoice
 // (src/backend/webgpu/matmul/dispatch.ts:171-192): explicit (forced) variant ->
-// per-shape tuned winner (re-gated on applicability) -> heuristic default.
+// per-shape tuned winner (re-gated on applicability) -> the shape class's tuned winner
+// (re-gated too) -> heuristic default.  *from_cache: 0 none, 1 exact shape, 2 shape class.
 static int32_t select_variant(tl_ctx* ctx, bool gemv, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
-                              const tl_quant_desc& q, tl_variant* v, bool* from_cache) {
-  *from_cache = false;
+                              const tl_quant_desc& q, tl_variant* v, int* from_cache) {
+  *from_cache = 0;
   const int fam = gemv ? TL_FAMILY_QGEMV : TL_FAMILY_QGEMM;
   if (ctx->has_forced && ctx->forced.family == fam) {
     if (!tl_variant_applicable(ctx, ctx->forced, m, n, k, a_dtype, q))
@@ -555,7 +589,13 @@ static int32_t select_variant(tl_ctx* ctx, bool gemv, int64_t m, int64_t n, int6
   if (it != ctx->tuned.end() && it->second.family == fam &&
       tl_variant_applicable(ctx, it->second, m, n, k, a_dtype, q)) {
     *v = it->second;
-    *from_cache = true;
+    *from_cache = 1;
+    return TL_OK;
+  }
+  auto ct = ctx->class_tuned.find(make_class_key(fam, m, n, k, a_dtype, q));
+  if (ct != ctx->class_tuned.end() && tl_variant_applicable(ctx, ct->second, m, n, k, a_dtype, q)) {
+    *v = ct->second;
+    *from_cache = 2;
     return TL_OK;
   }
   return gemv ? tl_qgemv_default_variant(ctx, (int32_t)m, n, k, a_dtype, q, v)
@@ -584,12 +624,12 @@ static int32_t qmatmul_impl(tl_ctx* ctx, const char* who, int route /*0 auto,1 g
   }
   DeviceGuard guard(ctx->device);
   tl_variant v;
-  bool from_cache = false;
+  int from_cache = 0;
   rc = select_variant(ctx, gemv, m, n, k, a_dtype, *qdesc, &v, &from_cache);
   if (rc != TL_OK) return rc;
   if (receipt_only) {
     memset(receipt_only, 0, sizeof(*receipt_only));
-    receipt_only->from_tuning_cache = from_cache ? 1 : 0;
+    receipt_only->from_tuning_cache = from_cache;
     receipt_only->epilogue_engaged = has_ops ? 1 : 0;
   }
   if (gemv) {

@@ -38,7 +38,7 @@ const char* tl_variant_name(const tl_variant* v) {
   const char* kern = "?";
   if (v->family == TL_FAMILY_QGEMV) kern = v->kernel == 0 ? "scalar" : v->kernel == 1 ? "simt" : v->kernel == 2 ? "mma" : v->kernel == 3 ? "sk" : v->kernel == 4 ? "ring" : v->kernel == 5 ? "tma" : v->kernel == 6 ? "bulk" : v->kernel == 7 ? "chain" : v->kernel == 8 ? "stream" : "?";
   if (v->family == TL_FAMILY_QGEMM) kern = v->kernel == 0 ? "tcgen05" : v->kernel == 1 ? "sliced" : "?";
-  if (v->family == TL_FAMILY_MATMUL) kern = v->kernel == 0 ? "tiled" : v->kernel == 1 ? "gemv" : "?";
+  if (v->family == TL_FAMILY_MATMUL) kern = v->kernel == 0 ? "tiled" : v->kernel == 1 ? "gemv" : v->kernel == 2 ? "tc" : "?";
   snprintf(buf, sizeof(buf), "%s.%s[%d,%d,%d,%d]", fam, kern, v->p0, v->p1, v->p2, v->p3);
   return buf;
 }
@@ -72,6 +72,7 @@ int32_t tl_tune_get(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtyp
 int32_t tl_tune_clear(tl_ctx* ctx) {
   TL_CHECK_CTX(ctx);
   ctx->tuned.clear();
+  ctx->class_tuned.clear();
   return TL_OK;
 }
 
@@ -165,6 +166,7 @@ int32_t tl_pretune(tl_ctx* ctx, const tl_shape* shapes, int32_t n_shapes, int32_
     cleanup();
     cudaGetLastError();
     ctx->tuned[key] = any ? best : cands[0];
+    if (any) tl_record_class_winner(ctx, m, n, k, a_dtype, *q, best);
     ctx->tune_runs++;
   }
   return TL_OK;
@@ -254,7 +256,11 @@ int32_t tl_tune_import_json(tl_ctx* ctx, const char* json) {
   ok = ok && c.lit("}");
   if (ok) { c.ws(); ok = *c.p == 0; }
   if (!ok) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_tune_import_json: invalid tuning-cache JSON near offset %zu", size_t(c.p - json));
-  for (const auto& kv : parsed) ctx->tuned[kv.first] = kv.second;
+  for (const auto& kv : parsed) {
+    ctx->tuned[kv.first] = kv.second;
+    const tl_quant_desc q{TL_SCHEME_INT8_GROUPED, kv.first.group, kv.first.scales_dtype, kv.first.convention};
+    tl_record_class_winner(ctx, kv.first.m, kv.first.n, kv.first.k, kv.first.a_dtype, q, kv.second);  // classes follow the shapes
+  }
   return TL_OK;
 }
 

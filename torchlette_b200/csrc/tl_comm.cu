@@ -186,6 +186,7 @@ struct P2PArgs {
   void* dst;
   int* status;
   int spin_limit;  // polls of one wait before it gives up (the context's wait_limit_polls)
+  int dst_dtype;   // f32 exchange only: the type the sums are stored as (one rounding)
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
@@ -279,6 +280,26 @@ __global__ void __launch_bounds__(kP2PThreads) p2p_allreduce_kernel(P2PArgs a) {
         acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
       }
       out = *reinterpret_cast<uint4*>(&acc);
+      if (a.dst_dtype != TL_F32) {
+        // f32 partial sums, 16-bit result: the sum is rounded ONCE, so the sharded product is as
+        // accurate as the unsharded one (16-bit partials lose up to half an ulp of each partial)
+        const float o[4] = {acc.x, acc.y, acc.z, acc.w};
+        const int64_t e0 = int64_t(i) * 4;
+        if (e0 + 4 <= a.count) {
+          uint32_t w0, w1;
+          if (a.dst_dtype == TL_F16) {
+            const __half2 h0 = __floats2half2_rn(o[0], o[1]), h1 = __floats2half2_rn(o[2], o[3]);
+            w0 = *reinterpret_cast<const uint32_t*>(&h0); w1 = *reinterpret_cast<const uint32_t*>(&h1);
+          } else {
+            const __nv_bfloat162 h0 = __floats2bfloat162_rn(o[0], o[1]), h1 = __floats2bfloat162_rn(o[2], o[3]);
+            w0 = *reinterpret_cast<const uint32_t*>(&h0); w1 = *reinterpret_cast<const uint32_t*>(&h1);
+          }
+          reinterpret_cast<uint2*>(a.dst)[i] = make_uint2(w0, w1);
+        } else {
+          for (int j = 0; e0 + j < a.count; ++j) tl_store_out(a.dst, a.dst_dtype, e0 + j, o[j]);
+        }
+        continue;
+      }
     } else {
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (int r = 0; r < a.world; ++r)
@@ -391,27 +412,32 @@ int32_t tl_p2p_reset(tl_ctx* ctx) {
   return TL_OK;
 }
 
-int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype) {
+static int32_t p2p_allreduce_impl(tl_ctx* ctx, const char* who, const void* src, int32_t dtype, void* dst, int32_t dst_dtype,
+                                  int64_t count) {
   TL_CHECK_CTX(ctx);
-  if (!src || !dst) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: null pointer");
-  if (count < 0 || !tl_dtype_valid(dtype)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: bad count or dtype");
+  if (!src || !dst) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: null pointer", who);
+  if (count < 0 || !tl_dtype_valid(dtype) || !tl_dtype_valid(dst_dtype)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: bad count or dtype", who);
+  if (dst_dtype != dtype && dtype != TL_F32)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "%s: a result type other than the exchange type needs f32 partial sums", who);
   if (count == 0) return TL_OK;
   const size_t bytes = size_t(count) * tl_dtype_size(dtype);
+  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: pointers must be 16-byte aligned", who);
   if (ctx->world == 1) {
     DeviceGuard guard(ctx->device);
+    if (dst_dtype != dtype) return tl_unary_op(ctx, 0, src, dtype, dst, dst_dtype, count);  // the cast alone
     if (src != dst) TL_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
     return TL_OK;
   }
-  if (!ctx->p2p_attached) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: peers not attached");
+  if (!ctx->p2p_attached) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: peers not attached", who);
   if (((bytes + 15) & ~size_t(15)) > ctx->p2p_max_bytes)
-    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_allreduce_sum_p2p: %zu bytes exceed the exchange buffer (%zu)", bytes, ctx->p2p_max_bytes);
-  if ((reinterpret_cast<uintptr_t>(src) & 15) || (reinterpret_cast<uintptr_t>(dst) & 15))
-    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_allreduce_sum_p2p: pointers must be 16-byte aligned");
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "%s: %zu bytes exceed the exchange buffer (%zu)", who, bytes, ctx->p2p_max_bytes);
   DeviceGuard guard(ctx->device);
   P2PArgs a{};
   for (int r = 0; r < ctx->world; ++r) a.base[r] = ctx->p2p_peer[r];
   a.rank = ctx->rank; a.world = ctx->world; a.max_bytes = ctx->p2p_max_bytes; a.count = count;
   a.src = src; a.dst = dst; a.status = ctx->dev_status; a.spin_limit = ctx->wait_limit_polls;
+  a.dst_dtype = dtype == TL_F32 ? dst_dtype : TL_F32;  // read by the f32 instantiation only
   cudaLaunchConfig_t cfg{};
   cfg.gridDim = dim3(kP2PCtas);
   cfg.blockDim = dim3(kP2PThreads);
@@ -427,6 +453,14 @@ int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t co
   TL_CUDA(ctx, cudaGetLastError());
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   return TL_OK;
+}
+
+int32_t tl_allreduce_sum_p2p(tl_ctx* ctx, const void* src, void* dst, int64_t count, int32_t dtype) {
+  return p2p_allreduce_impl(ctx, "tl_allreduce_sum_p2p", src, dtype, dst, dtype, count);
+}
+
+int32_t tl_allreduce_sum_p2p_f32_to(tl_ctx* ctx, const float* src, void* dst, int32_t dst_dtype, int64_t count) {
+  return p2p_allreduce_impl(ctx, "tl_allreduce_sum_p2p_f32_to", src, TL_F32, dst, dst_dtype, count);
 }
 
 }  // extern "C"

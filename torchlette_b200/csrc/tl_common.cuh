@@ -71,6 +71,9 @@ struct tl_ctx {
   bool autotune_enabled = false;
   int64_t tune_runs = 0;
   std::map<TuneKey, tl_variant> tuned;
+  // shape-class winners: the TuneKey's m carries the class id, n the kernel family, k is 0, and a
+  // per-channel format (group == K) is recorded as group 0 so that shapes of different K share it
+  std::map<TuneKey, tl_variant> class_tuned;
   std::map<int, int> ring_occupancy;  // resident CTAs per SM of each ring kernel shape (queried once)
   bool capturing = false;
   // multi-GPU
@@ -184,6 +187,7 @@ inline size_t tl_p2p_total_bytes(size_t max_bytes) {
   return tl_p2p_push_slots_offset(max_bytes) + 2 * size_t(tl_ctx::kMaxPeers) * max_bytes;
 }
 
+void tl_record_class_winner(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, const tl_variant& v);
 bool tl_lookup_tuned(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype, const tl_quant_desc& q, tl_variant* v);
 
 // Common argument validation of the quantized entry points.
@@ -200,6 +204,11 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
                         const void* packed, const void* scales, void* out, int32_t out_dtype,
                         int64_t m, int64_t n, int64_t k, const tl_quant_desc& q,
                         const EpiParams& epi, tl_plan_receipt* receipt_only);
+// Dense tensor-core matmul (tl_matmul_tc.cu): NT layout, both operands f16 or both bf16.
+bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, int64_t k, int32_t dtype_a, int32_t dtype_b);
+void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid);
+int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
+                           int32_t out_dtype, const struct EpiParams& epi);
 bool tl_qgemv_stream_applicable(const tl_variant& v, int64_t m, int64_t k, int32_t a_dtype, const tl_quant_desc& q);
 void tl_qgemv_stream_geometry(tl_ctx* ctx, const tl_variant& v, int32_t m, int64_t tiles, int64_t k, int* grid, int* block,
                               size_t* smem);

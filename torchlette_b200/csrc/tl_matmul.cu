@@ -4,7 +4,7 @@
 // tiled body src/schedule/matmul-skeleton.ts:738-908, read-wider-cast-on-load
 // src/backend/webgpu/matmul/variants.ts:170-175, batch broadcast strides dispatch.ts:1411-1510).
 //
-// Two kernels of family TL_FAMILY_MATMUL:
+// Three kernels of family TL_FAMILY_MATMUL:
 //   0 "tiled"  the always-applicable one (the reference's `tiled` variant): 64 x 64 output tiles,
 //              16 x 16 threads with 4 x 4 register tiles, operands staged through shared memory
 //              16 k at a time, any of NN / NT / TN / TT, f32 / f16 / bf16 operands in any
@@ -15,8 +15,10 @@
 //              the small-batch tensor-core tile of the quantized path without the converter --
 //              16 rows per CTA, warps interleaved over 32-wide k blocks, mma.sync.m16n8k16 with the
 //              weight rows as the A operand and the batch as the B operand.  HBM-bound.
-// The tcgen05 pipeline of the quantized GEMM is not reused here yet: large dense products run
-// on the tiled kernel, far from the tensor roofline (stated where the numbers are reported).
+//   2 "tc"     m >= 32, n >= 64, k >= 64, k % 8 == 0, both operands f16 or both bf16, no cast prologue: the
+//              tcgen05 kernel of tl_matmul_tc.cu.  It computes the NT layout; an A stored [K, M] or a
+//              B stored [K, N] is first transposed into library scratch (one extra HBM pass over
+//              that operand).  Batches run as one launch each.
 #include <algorithm>
 
 #include "tl_common.cuh"
@@ -24,7 +26,7 @@
 
 namespace {
 
-constexpr int kTiled = 0, kGemv = 1;
+constexpr int kTiled = 0, kGemv = 1, kTc = 2;
 
 struct MatmulArgs {
   const void* a;
@@ -226,14 +228,29 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     const int kblocks = int(k / 32);
     warps = kblocks >= 16 ? 16 : kblocks >= 8 ? 8 : kblocks >= 4 ? 4 : kblocks >= 2 ? 2 : 1;
   }
+  const bool forced_tc = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == kTc;
+  const size_t esz_ab = 2;
+  const bool batch_aligned = batch == 1 || ((stride_a * esz_ab) % 16 == 0 && (stride_b * esz_ab) % 16 == 0);
+  const bool use_tc = !use_gemv && !forced_tiled && cast_a < 0 && cast_b < 0 && batch_aligned &&
+                      tl_dense_tc_applicable(a, b, m, n, k, dtype_a, dtype_b);
+  if (forced_tc && !use_tc)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_matmul: the tensor-core kernel cannot run m=%lld n=%lld k=%lld with these dtypes / casts",
+                        (long long)m, (long long)n, (long long)k);
   if (receipt_only) {
     tl_variant v{};
-    v.family = TL_FAMILY_MATMUL; v.kernel = use_gemv ? kGemv : kTiled; v.p0 = use_gemv ? warps : 8;
+    v.family = TL_FAMILY_MATMUL; v.kernel = use_gemv ? kGemv : use_tc ? kTc : kTiled; v.p0 = use_gemv ? warps : 8;
     receipt_only->choice = v;
     receipt_only->grid[0] = use_gemv ? int32_t((n + 15) / 16) : int32_t((n + kTN - 1) / kTN);
     receipt_only->grid[1] = use_gemv ? 1 : int32_t((m + kTM - 1) / kTM);
     receipt_only->grid[2] = use_gemv ? 1 : int32_t(batch);
     receipt_only->block = use_gemv ? warps * 32 : 256;
+    if (use_tc) {
+      int bn, stages, grid;
+      tl_dense_tc_shape(m, n, ctx->sm_count, &bn, &stages, &grid);
+      receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages;
+      receipt_only->grid[0] = grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
+      receipt_only->block = 320;
+    }
     receipt_only->split_k = 1;
     receipt_only->from_tuning_cache = 0;
     receipt_only->epilogue_engaged = has_ops ? 1 : 0;
@@ -254,6 +271,34 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     }
     ctx->counters[TL_COUNTER_GEMV]++;
     if (has_ops) ctx->counters[TL_COUNTER_QGEMV_EPILOGUE]++;
+  } else if (use_tc) {
+    // bring the operands to the NT layout (A [M, K], B [N, K]) in scratch where they are stored transposed
+    const size_t a_elems = p.trans_a ? size_t(m) * k : 0, b_elems = p.trans_b ? 0 : size_t(n) * k;
+    uint8_t* scratch = nullptr;
+    if (a_elems + b_elems) {
+      void* sp = nullptr;
+      rc = tl_ensure_scratch(ctx, (a_elems + b_elems) * 2 + 256, &sp);
+      if (rc != TL_OK) return rc;
+      scratch = static_cast<uint8_t*>(sp);
+    }
+    for (int64_t bi = 0; bi < batch; ++bi) {
+      const uint8_t* ab = static_cast<const uint8_t*>(a) + size_t(bi) * stride_a * 2;
+      const uint8_t* bb = static_cast<const uint8_t*>(b) + size_t(bi) * stride_b * 2;
+      uint8_t* ob = static_cast<uint8_t*>(out) + size_t(bi) * stride_c * tl_dtype_size(out_dtype);
+      if (p.trans_a && (bi == 0 || stride_a != 0)) {
+        rc = tl_transpose2d(ctx, ab, scratch, 1, k, m, 2);  // stored [K, M] -> [M, K]
+        if (rc != TL_OK) return rc;
+      }
+      uint8_t* bt = scratch + ((a_elems * 2 + 255) & ~size_t(255));
+      if (!p.trans_b && (bi == 0 || stride_b != 0)) {
+        rc = tl_transpose2d(ctx, bb, bt, 1, k, n, 2);       // stored [K, N] -> [N, K]
+        if (rc != TL_OK) return rc;
+      }
+      rc = tl_launch_dense_tc(ctx, p.trans_a ? scratch : ab, p.trans_b ? bb : bt, ob, m, n, k, dtype_a, out_dtype, epi);
+      if (rc != TL_OK) return rc;
+    }
+    ctx->counters[TL_COUNTER_MATMUL]++;
+    return TL_OK;
   } else {
     dim3 grid(unsigned((n + kTN - 1) / kTN), unsigned((m + kTM - 1) / kTM), unsigned(batch));
     matmul_tiled_kernel<<<grid, 256, 0, ctx->stream>>>(p, epi);

@@ -608,9 +608,11 @@ __device__ __forceinline__ float push_load(const void* base, int dtype, int64_t 
 // ---------------------------------------------------------------------------
 // Push / reduce-on-read: the row-parallel sum of tensor parallelism without a collective launch.
 //
-// tl_qgemv_nt_push (ring tile, PUSH == 2): every CTA rounds its 16-row tile of the LOCAL partial
-// product to the output type, stages it in shared memory and stores it into slot (half, rank) of
-// EVERY rank's exchange buffer as 8-byte words {two output values, epoch}.  An 8-byte store arrives
+// tl_qgemv_nt_push (ring tile, PUSH == 2): every CTA stages its 16-row tile of the LOCAL partial
+// product in shared memory, in f32, and stores it into slot (half, rank) of EVERY rank's exchange
+// buffer as 8-byte words {f32 partial sum, epoch}.  (f32, not the 16-bit output type: a 16-bit partial
+// loses up to half an ulp of a value that may be far larger than the total, and eight of them add up
+// to 1e-2 on the parity metric; the sum of f32 partials is rounded once.)  An 8-byte store arrives
 // whole, so the epoch that travels with the data is the arrival signal: the producer needs no fence,
 // no atomic and no flag (a system-scope release per CTA, 256 per launch, cost 8 us; fences from
 // every thread 12 us), and it waits for nobody.
@@ -630,7 +632,7 @@ __device__ __forceinline__ float push_load(const void* base, int dtype, int64_t 
 // the producer reads epoch_p and publishes epoch_c = epoch_p + 1, the consumer reads epoch_c and
 // publishes epoch_p = epoch_c.  A producer clears done[] of the OTHER half when it starts (its own
 // previous consumer has finished with it).  Slots are [2 halves][kMaxPeers][max_bytes] with
-// max_bytes >= m * n * 4 (every pair of 2-byte values carries a 4-byte epoch).
+// max_bytes >= m * n * 8 (every f32 partial sum carries a 4-byte epoch).
 // ---------------------------------------------------------------------------
 struct ReduceIn {
   uint8_t* base;        // this rank's exchange buffer
@@ -659,28 +661,26 @@ __device__ __forceinline__ void reduce_in_prologue(const ReduceIn& r) {
       const int per = (r.count_vec + r.nsum - 1) / r.nsum;
       const int v0 = int(blockIdx.x) * per, v1 = min(v0 + per, r.count_vec);
       for (int i = v0 + tid; i < v1; i += nthreads) {
-        // output vector i = 8 values = four {pair, epoch} words (32 bytes) of every rank's slot
+        // output vector i = 8 values = eight {f32, epoch} words (64 bytes) of every rank's slot
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int rr = 0; rr < r.world; ++rr) {
-          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 2 * i;
-          uint4 u0, u1;
+          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 4 * i;
+          uint4 u[4];
           int spins = 0;
           for (;;) {
-            u0 = __ldcv(src);
-            u1 = __ldcv(src + 1);
-            if (u0.y == epoch && u0.w == epoch && u1.y == epoch && u1.w == epoch) break;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) u[j] = __ldcv(src + j);
+            bool all = true;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) all = all && u[j].y == epoch && u[j].w == epoch;
+            if (all) break;
             if (++spins > r.spin_limit) { atomicExch(r.status, TL_ERR_TIMEOUT); break; }
             __nanosleep(200);  // thousands of threads poll lines that a peer is writing: leave the L2 slice room
           }
-          const uint32_t w[4] = {u0.x, u0.z, u1.x, u1.z};
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            if (r.dtype == TL_F16) {
-              const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-              acc[2 * j] += f.x; acc[2 * j + 1] += f.y;
-            } else {
-              acc[2 * j] += __uint_as_float(w[j] << 16); acc[2 * j + 1] += __uint_as_float(w[j] & 0xffff0000u);
-            }
+            acc[2 * j] += __uint_as_float(u[j].x);
+            acc[2 * j + 1] += __uint_as_float(u[j].z);
           }
         }
         uint32_t o[4];
@@ -853,7 +853,7 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
   // into slot (half, rank) of EVERY rank's exchange buffer instead of into p.out.
   uint32_t push_epoch = 0;
   uint32_t* push_words = nullptr;
-  __shared__ __align__(16) uint16_t push_stage[16][16];  // PUSH == 2: [batch column][row of the tile], output type bits
+  __shared__ __align__(16) float push_stage[PUSH == 2 ? 16 : 8][16];  // PUSH == 2: [batch column][row of the tile], f32 partial sums
   if (PUSH == 1) {
     push_words = reinterpret_cast<uint32_t*>(q->base[q->rank] + tl_p2p_fused_offset(q->max_bytes));
     push_epoch = push_words[tile_index];  // owner-only counter; every thread reads it before thread 0 bumps it
@@ -875,25 +875,24 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
           tl_store_out(q->base[rr] + tl_p2p_fused_slots_offset(q->max_bytes) + (size_t(push_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes, p.out_dtype,
                        int64_t(col) * p.n + row, r);
       } else if (PUSH == 2) {
-        push_stage[col][row - tile_row] = p.out_dtype == TL_F16 ? __half_as_ushort(__float2half_rn(r))
-                                                                : __bfloat16_as_ushort(__float2bfloat16_rn(r));
+        push_stage[col][row - tile_row] = r;
       } else {
         tl_store_out(p.out, p.out_dtype, int64_t(p.row0 + col) * p.n + row, r);
       }
     }
   }
   if (PUSH == 2) {
-    // the tile [m columns][16 rows] leaves as 8-byte words {two values, epoch}, one copy per peer
+    // the tile [m columns][16 rows] leaves as 8-byte words {f32 value, epoch}, one copy per peer
     __syncthreads();
-    const int per_peer = p.m * 8;
+    const int per_peer = p.m * 16;
     for (int idx = tid; idx < per_peer * q->world; idx += nthreads) {
-      const int peer = idx / per_peer, v = idx - peer * per_peer, col = v >> 3, rp = v & 7;
-      const uint32_t pair = *reinterpret_cast<const uint32_t*>(&push_stage[col][2 * rp]);
+      const int peer = idx / per_peer, v = idx - peer * per_peer, col = v >> 4, rw = v & 15;
+      const uint32_t bits = __float_as_uint(push_stage[col][rw]);
       uint8_t* slot = q->base[peer] + tl_p2p_push_slots_offset(q->max_bytes) +
                       (size_t(push2_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes;
-      uint2* dst = reinterpret_cast<uint2*>(slot) + ((int64_t(col) * p.n + tile_row) >> 1) + rp;
+      uint2* dst = reinterpret_cast<uint2*>(slot) + (int64_t(col) * p.n + tile_row) + rw;
       // volatile (relaxed at system scope): a weak store to peer memory may be held back indefinitely
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(pair), "r"(push2_epoch) : "memory");
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(bits), "r"(push2_epoch) : "memory");
     }
   }
   if (PUSH == 1) {
@@ -3103,8 +3102,8 @@ extern "C" int32_t tl_qgemv_nt_push(tl_ctx* ctx, const void* a, int32_t a_dtype,
       (reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
                         "tl_qgemv_nt_push: needs f16/bf16 activations and outputs, K %% 64 == 0, group %% 64 == 0, N %% 16 == 0, 16-byte aligned operands");
-  if (size_t(m) * size_t(n) * 4 > ctx->p2p_max_bytes)  // every 2-byte pair travels with a 4-byte epoch
-    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_push: %zu bytes exceed the exchange buffer (%zu)", size_t(m) * size_t(n) * 4,
+  if (size_t(m) * size_t(n) * 8 > ctx->p2p_max_bytes)  // every f32 partial sum travels with a 4-byte epoch
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_push: %zu bytes exceed the exchange buffer (%zu)", size_t(m) * size_t(n) * 8,
                         ctx->p2p_max_bytes);
   EpiParams epi;
   bool has_ops = false;

@@ -86,6 +86,7 @@ class DecodeStack:
         # one rank with a loopback exchange attached (tl_p2p_attach_loopback(ctx, 1)): the row-parallel
         # projections still go through tl_qgemv_nt_push and its reduce-on-read consumer
         self.loopback_push = loopback_push
+        self._partials = {}
         self._chain = None
         self._chain_keep = []
         self.be, self.cfg, self.rank, self.world, self.tp_mode = be, cfg, rank, world, tp_mode
@@ -146,7 +147,7 @@ class DecodeStack:
         return p
 
     # -- one projection through the C ABI ------------------------------------
-    def _run(self, p: _Proj, x: torch.Tensor, out: torch.Tensor):
+    def _run(self, p: _Proj, x: torch.Tensor, out: torch.Tensor, out_dtype: Optional[str] = None):
         q = B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, p.k, B.TL_F32, B.TL_SCALE_DIRECT)
         e = None
         if p.act:
@@ -155,7 +156,7 @@ class DecodeStack:
             e.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY[p.act], 0, 0)
         B.check(self.ctx, self.lib.tl_qmatmul_nt(
             self.ctx, x.data_ptr(), self.adt, p.w.data_ptr(), p.s.data_ptr(), out.data_ptr(),
-            B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha,
+            B.DTYPE_ID[out_dtype or p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha,
             C.byref(e) if e is not None else None))
 
     def _run_batched(self, projs, x: torch.Tensor, outs):
@@ -197,15 +198,26 @@ class DecodeStack:
                 self.ctx, x.data_ptr(), self.adt, p.w.data_ptr(), p.s.data_ptr(), out.data_ptr(),
                 B.DTYPE_ID[p.out_dtype], self.cfg.batch, p.n, p.k, C.byref(q), p.alpha))
             return
-        self._run(p, x, out)
-        self._allreduce(out)
+        if self.world == 1:
+            self._run(p, x, out)
+            return
+        # The partial products are exchanged in f32 and their sum is rounded ONCE to the activation
+        # type: 16-bit partials lose up to half an ulp of a partial that can be far larger than the
+        # total, and at 8 ranks that alone reaches the 1e-2 parity bound.
+        part = self._partial_f32(out)
+        self._run(p, x, part, out_dtype="f32")
+        if self.allreduce in ("p2p", "fused", "push"):
+            B.check(self.ctx, self.lib.tl_allreduce_sum_p2p_f32_to(self.ctx, part.data_ptr(), out.data_ptr(), self.adt, part.numel()))
+        else:
+            B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, part.data_ptr(), part.numel(), B.TL_F32))
+            B.check(self.ctx, self.lib.tl_unary_op(self.ctx, 0, part.data_ptr(), B.TL_F32, out.data_ptr(), self.adt, part.numel()))
 
-    def _allreduce(self, t: torch.Tensor):
-        if self.world > 1:
-            if self.allreduce in ("p2p", "fused", "push"):
-                B.check(self.ctx, self.lib.tl_allreduce_sum_p2p(self.ctx, t.data_ptr(), t.data_ptr(), t.numel(), self.adt))
-            else:
-                B.check(self.ctx, self.lib.tl_allreduce_sum(self.ctx, t.data_ptr(), t.numel(), self.adt))
+    def _partial_f32(self, like: torch.Tensor) -> torch.Tensor:
+        """One f32 buffer per output shape for the row-parallel partial products."""
+        key = tuple(like.shape)
+        if key not in self._partials:
+            self._partials[key] = torch.empty(like.shape, dtype=torch.float32, device=like.device)
+        return self._partials[key]
 
     def _allgather(self, local: torch.Tensor, full: torch.Tensor, dtype_id: int):
         B.check(self.ctx, self.lib.tl_allgather_cols(self.ctx, local.data_ptr(), full.data_ptr(), local.shape[0],

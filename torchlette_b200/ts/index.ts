@@ -219,7 +219,7 @@ const defaultQdesc = (groupSize: number, scalesDtype: string): Int32Array => Int
 function receipt(r: Int32Array): CudaPlanReceipt {
   const choice = Array.from(r.subarray(0, 6)) as CudaVariantChoice;
   return { family: FAMILY_NAME[r[0]] ?? "?", variant: addon.variantName(Int32Array.from(choice)), choice, grid: [r[6], r[7], r[8]],
-           block: r[9], splitK: r[10], fromTuningCache: r[11] === 1, epilogueEngaged: r[12] === 1 };
+           block: r[9], splitK: r[10], fromTuningCache: r[11] !== 0, epilogueEngaged: r[12] === 1 };
 }
 
 export interface MatmulOptions {
@@ -344,6 +344,9 @@ export function getPerShapeMatmulChoice(m: number, n: number, k: number, dtype: 
 export function seedPerShapeMatmulChoice(m: number, n: number, k: number, dtype: string, format: any, choice: CudaVariantChoice): void {
   addon.tuneSeed(need(), m, n, k, DTYPE_ID[dtype], qdesc(format), Int32Array.from(choice));
 }
+/** classifyShape (matmul/types.ts:146-200): the class whose tuned winner a shape falls back to. */
+export const classifyShape = (m: number, n: number, k: number, batchSize = 1): string =>
+  addon.shapeClassName(addon.classifyShape(m, n, k, batchSize));
 export const clearPerShapeMatmulChoices = (): void => addon.tuneClear(need());
 export const exportTuningCache = (): string => addon.tuneExportJson(need());
 export const importTuningCache = (json: string): void => addon.tuneImportJson(need(), json);
