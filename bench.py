@@ -268,27 +268,41 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                                                  "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
                                                  "l2": f"rotating over {copies} weight copies (352 MB)"}
     del wd
-    md = 2048
-    xa = (torch.randn(md, md, device=dev) * 0.05).to(torch.float16)
-    xb = (torch.randn(md, md, device=dev) * 0.05).to(torch.float16)
-    yc = torch.empty(md, md, dtype=torch.float16, device=dev)
+    # dense products on the tensor cores (tl_matmul's tcgen05 kernel): the prefill shape in the NT layout
+    # `linear` produces, a square NN product (B is transposed into scratch first), and the tiled
+    # CUDA-core kernel forced on the same square for reference
+    def time_dense(m_, n_, k_, trans_b, dt, tdt, epi_ptr, reps=10):
+        xa = (torch.randn(m_, k_, device=dev) * 0.05).to(tdt)
+        xb = (torch.randn(*((n_, k_) if trans_b else (k_, n_)), device=dev) * 0.05).to(tdt)
+        yc = torch.empty(m_, n_, dtype=tdt, device=dev)
 
-    def run_dense():
-        B.check(ctx, lib.tl_matmul(ctx, xa.data_ptr(), xb.data_ptr(), yc.data_ptr(), md, md, md, 1, 0, 0, md * md, 0, 0, 1.0,
-                                   B.TL_F16, B.TL_F16, B.TL_F16, -1, -1, None, None))
-    for _ in range(3):
-        run_dense()
-    be.sync()
-    B.check(ctx, lib.tl_event_record(ctx, ev0))
-    for _ in range(5):
-        run_dense()
-    B.check(ctx, lib.tl_event_record(ctx, ev1))
-    ms = C.c_float()
-    B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-    tf = 2.0 * md ** 3 / (ms.value / 5 * 1e-3) / 1e12
-    out["dense_matmul_f16_2048x2048x2048"] = {"ms": ms.value / 5, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak,
-                                              "kernel": "tiled (CUDA cores, f32 accumulate): not a tensor-core kernel"}
-    del xa, xb, yc
+        def run():
+            B.check(ctx, lib.tl_matmul(ctx, xa.data_ptr(), xb.data_ptr(), yc.data_ptr(), m_, n_, k_, 1, 0, 0, m_ * n_, 0,
+                                       1 if trans_b else 0, 1.0, dt, dt, dt, -1, -1, epi_ptr, None))
+        for _ in range(3):
+            run()
+        be.sync()
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        for _ in range(reps):
+            run()
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        tf = 2.0 * m_ * n_ * k_ / (ms.value / reps * 1e-3) / 1e12
+        return {"ms": ms.value / reps, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak}
+    eg = B.Epilogue()
+    eg.n_ops = 1
+    eg.ops[0] = B.EpilogueOp(B.TL_EPI_UNARY, B.TL_UNARY["gelu"], 0, 0)
+    out["dense_tc_bf16_2048x4096x14336_nt_gelu"] = dict(time_dense(2048, 14336, 4096, True, B.TL_BF16, torch.bfloat16, C.byref(eg)),
+                                                        kernel="tcgen05, A and B from shared memory")
+    out["dense_tc_f16_2048x2048x2048_nn"] = dict(time_dense(2048, 2048, 2048, False, B.TL_F16, torch.float16, None),
+                                                 kernel="tcgen05 after one transposition pass over B")
+    be.forceVariant((B.TL_FAMILY_MATMUL, 0, 0, 0, 0, 0))
+    try:
+        out["dense_tiled_f16_2048x2048x2048"] = dict(time_dense(2048, 2048, 2048, False, B.TL_F16, torch.float16, None, reps=3),
+                                                     kernel="tiled (CUDA cores): the always-applicable kernel, forced")
+    finally:
+        be.forceVariant(None)
     # prefill GEMM, config 3
     for (m, kk, nn) in ((2048, 4096, 14336), (2048, 14336, 4096)):
         w = torch.randint(-127, 128, (nn, kk), dtype=torch.int8, device=dev)
@@ -712,9 +726,11 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tp-mode", default="chained", choices=["chained", "gather"])
     ap.add_argument("--autotune", action="store_true")
-    ap.add_argument("--allreduce", default="p2p", choices=["p2p", "fused", "push", "nccl"],
-                    help="row-parallel sums: the library's one-shot peer-memory kernel (default, fastest measured), "
-                         "the GEMV fused with its all-reduce (tl_qgemv_nt_allreduce), or NCCL")
+    ap.add_argument("--allreduce", default="push", choices=["p2p", "fused", "push", "nccl"],
+                    help="row-parallel sums: push = the projection pushes f32 partial sums to every rank and the next "
+                         "launch reduces them on read (no collective launch; default, fastest measured at 2, 4 and 8 GPUs); "
+                         "p2p = the library's one-shot peer-memory all-reduce kernel; fused = the GEMV fused with its "
+                         "all-reduce (tl_qgemv_nt_allreduce); nccl")
     ap.add_argument("--step-launch", default="graph", choices=["chain", "graph"],
                     help="graph: a replayed CUDA graph of per-projection launches (the measured-faster default); "
                          "chain: the whole step as one persistent cooperative launch (one GPU, batch <= 16)")
