@@ -60,7 +60,7 @@ enum { TL_F32 = 0, TL_F16 = 1, TL_BF16 = 2 };
  *   scale_convention TL_SCALE_SNORM127: w = (q/127) * s   (quantize.ts:138-156)
  *   scale_convention TL_SCALE_DIRECT  : w = q * s
  * group_size divides K; group_size == K is per-output-channel. */
-enum { TL_SCHEME_INT8_GROUPED = 1 };
+enum { TL_SCHEME_INT8_GROUPED = 1, TL_SCHEME_INT4_GROUPED = 2 };
 enum { TL_SCALE_SNORM127 = 0, TL_SCALE_DIRECT = 1 };
 typedef struct tl_quant_desc {
   int32_t scheme;
@@ -293,6 +293,21 @@ typedef struct tl_plan_receipt {
 TL_API int32_t tl_plan_qmatmul(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
                                int32_t out_dtype, const tl_quant_desc* qdesc,
                                const tl_epilogue* epilogue, tl_plan_receipt* out_receipt);
+/* ---- int4-grouped: the scheme the reference plans as "a new value on the format axis"
+ * (docs/quantization-design.md:69-75, 386-396; no code there).  Packed u32 [N, K/8], eight int4 per
+ * word, nibble j = k & 7 in bits 4j..4j+3, two's complement in [-7, 7]; scales [N, K/G] as for int8
+ * (f16 abs-max with w = (q/7)*scale when the convention is TL_SCALE_SNORM127, or f32 direct scales).
+ * K % 8 == 0, G % 8 == 0.  tl_qmatmul_nt / tl_qgemv_nt / tl_qgemm_nt / tl_plan_qmatmul accept a
+ * descriptor with scheme TL_SCHEME_INT4_GROUPED: m <= 16 runs the fused-dequant int4 GEMV, larger m
+ * dequantizes into library scratch and runs tl_matmul (the reference's explicit-dequant fallback).
+ * The batched / chain / push / static-scratch entry points are int8 only. */
+TL_API int32_t tl_quantize_linear_weight_int4(const float* weight, int64_t n, int64_t k, int32_t group_size,
+                                              uint32_t* packed, uint16_t* scales);
+TL_API int32_t tl_dequant_int4(tl_ctx* ctx, const void* packed, const void* scales, void* out,
+                               int32_t out_dtype, int64_t n, int64_t k, const tl_quant_desc* qdesc);
+/* Debug op: the signed nibbles as int8 [n,k]. */
+TL_API int32_t tl_unpack_int4(tl_ctx* ctx, const void* packed, void* out_i8, int64_t n, int64_t k);
+
 /* ---- dense matmul: dispatchTiledMatmul / dispatchMatmul for an unquantized B
  * (src/backend/webgpu/matmul/dispatch.ts:1331-1700; dense GEMV builders
  *  src/backend/webgpu/matmul/gemv.ts:430-532; tiled body

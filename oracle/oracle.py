@@ -56,6 +56,10 @@ def lib():
         L.orc_quantize_linear_weight.argtypes = [p, i64, i64, i64, p, p]
         L.orc_quantize_linear_weight.restype = C.c_int
         L.orc_unpack_int8.argtypes = [p, i64, i64, p]
+        L.orc_quantize_linear_weight_int4.argtypes = [p, i64, i64, i64, p, p]
+        L.orc_quantize_linear_weight_int4.restype = C.c_int
+        L.orc_unpack_int4.argtypes = [p, i64, i64, p]
+        L.orc_dequantize_int4_to_f32.argtypes = [p, p, i64, i64, i64, p]
         L.orc_dequantize_to_f32.argtypes = [p, p, i64, i64, i64, p]
         L.orc_dequantize_direct_f32.argtypes = [p, p, i64, i64, i64, p]
         L.orc_matmul_nt.argtypes = [p, p, p, i64, i64, i64, C.c_int]
@@ -106,6 +110,36 @@ def quantize_linear_weight(weight: np.ndarray, group: int = 64):
     if rc != 0:
         raise ValueError(f"quantize: K={k} must be divisible by 4 and by groupSize={group}")
     return packed, scales
+
+
+def quantize_linear_weight_int4(weight: np.ndarray, group: int = 32):
+    """The planned int4-grouped scheme (docs/quantization-design.md:69-75), by analogy with
+    quantize.ts:77-131 -> (packed u32 [N,K/8], scales u16 [N,K/G])."""
+    w = _c(weight, np.float32)
+    n, k = w.shape
+    packed = np.zeros((n, k // 8), dtype=np.uint32)
+    scales = np.zeros((n, k // group), dtype=np.uint16)
+    rc = lib().orc_quantize_linear_weight_int4(_ptr(w), n, k, group, _ptr(packed), _ptr(scales))
+    if rc != 0:
+        raise ValueError(f"quantize int4: K={k} must be divisible by 8 and by groupSize={group}")
+    return packed, scales
+
+
+def unpack_int4(packed: np.ndarray, k: int) -> np.ndarray:
+    pk = _c(packed, np.uint32)
+    n = pk.size * 8 // k
+    out = np.empty((n, k), dtype=np.int8)
+    lib().orc_unpack_int4(_ptr(pk), n, k, _ptr(out))
+    return out
+
+
+def dequantize_int4_to_f32(packed, scales_f16_bits, k: int, group: int) -> np.ndarray:
+    pk = _c(packed, np.uint32)
+    sc = _c(scales_f16_bits, np.uint16)
+    n = pk.size * 8 // k
+    out = np.empty((n, k), dtype=np.float32)
+    lib().orc_dequantize_int4_to_f32(_ptr(pk), _ptr(sc), n, k, group, _ptr(out))
+    return out
 
 
 def unpack_int8(packed: np.ndarray, k: int) -> np.ndarray:

@@ -131,6 +131,69 @@ ORC_API int orc_quantize_linear_weight(const float* weight, int64_t n, int64_t k
 }
 
 /* ------------------------------------------------------------------------- */
+/* int4-grouped: the planned second scheme (docs/quantization-design.md:69-75)  */
+/* ------------------------------------------------------------------------- */
+
+/* The reference only DESCRIBES this scheme: "8 int4 per u32 word, packed 8-along-K into [N, K/8]
+ * u32 ... unpacks a nibble ((word >> (4*j)) & 0xF, sign-extend from 4 bits)".  It holds no code and
+ * no vectors for it, so this restatement follows the int8 quantizer above line for line with the
+ * range [-7, 7] in place of [-127, 127] (symmetric, -8 never emitted) and nibble j = k & 7 in bits
+ * 4j..4j+3; scales are the f16 bits of the group abs-max and w = (q / 7) * scale.  Parity for
+ * int4 is therefore pinned to nothing but this text. */
+ORC_API int orc_quantize_linear_weight_int4(const float* weight, int64_t n, int64_t k, int64_t group,
+                                            uint32_t* packed, uint16_t* scales) {
+  if (k % 8 != 0 || group <= 0 || k % group != 0) return -1;
+  int64_t groups_per_row = k / group;
+  int64_t words_per_row = k / 8;
+  memset(packed, 0, (size_t)(n * words_per_row) * sizeof(uint32_t));
+  for (int64_t row = 0; row < n; row++) {
+    for (int64_t g = 0; g < groups_per_row; g++) {
+      double abs_max = 0.0;
+      int64_t g_base = row * k + g * group;
+      for (int64_t j = 0; j < group; j++) {
+        double a = fabs((double)weight[g_base + j]);
+        if (a > abs_max) abs_max = a;
+      }
+      uint32_t scale_bits = orc_f32_to_f16_bits((float)abs_max);
+      scales[row * groups_per_row + g] = (uint16_t)scale_bits;
+      double scale = orc_f16_bits_to_f64(scale_bits);
+      double inv = scale > 0 ? 7.0 / scale : 0.0;
+      for (int64_t j = 0; j < group; j++) {
+        double r = js_math_round((double)weight[g_base + j] * inv);
+        double q = isnan(r) ? 0.0 : fmax(-7.0, fmin(7.0, r));
+        int32_t qi = (int32_t)q;
+        int64_t k_idx = g * group + j;
+        packed[row * words_per_row + (k_idx >> 3)] |= ((uint32_t)qi & 0xfu) << ((k_idx & 7) * 4);
+      }
+    }
+  }
+  return 0;
+}
+
+static inline int32_t unpack_nibble(uint32_t word, int j) {
+  int32_t qi = (int32_t)((word >> (j * 4)) & 0xfu);
+  if (qi >= 8) qi -= 16;
+  return qi;
+}
+
+/* signed nibbles as int8 [n,k] */
+ORC_API void orc_unpack_int4(const uint32_t* packed, int64_t n, int64_t k, int8_t* out) {
+  for (int64_t i = 0; i < n * k; i++) out[i] = (int8_t)unpack_nibble(packed[i >> 3], (int)(i & 7));
+}
+
+/* out[n,k] = (q / 7) * f16(scale[n, k / G]) in f64, one rounding to f32 (the int8 dequantizer's form) */
+ORC_API void orc_dequantize_int4_to_f32(const uint32_t* packed, const uint16_t* scales, int64_t n, int64_t k,
+                                        int64_t group, float* out) {
+  int64_t groups_per_row = k / group;
+  for (int64_t row = 0; row < n; row++)
+    for (int64_t c = 0; c < k; c++) {
+      int64_t e = row * k + c;
+      double scale = orc_f16_bits_to_f64(scales[row * groups_per_row + c / group]);
+      out[e] = (float)(((double)unpack_nibble(packed[e >> 3], (int)(e & 7)) / 7.0) * scale);
+    }
+}
+
+/* ------------------------------------------------------------------------- */
 /* Host dequantizer: src/backend/quantize.ts:138-156                          */
 /* ------------------------------------------------------------------------- */
 

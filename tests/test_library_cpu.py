@@ -126,8 +126,10 @@ def test_weight_format_names():
     f = tb.resolveWeightFormat("int8-64")
     assert f.packing.groupSize == 64 and f.packing.scalesDtype == "f16" and f.elementType == "f16"
     assert tb.resolveWeightFormat("int8-128", "f32").packing.groupSize == 128
+    f4 = tb.resolveWeightFormat("int4-32")
+    assert f4.packing.scheme == "int4-grouped" and f4.packing.groupSize == 32 and f4.packing.scalesDtype == "f16"
     with pytest.raises(ValueError):
-        tb.resolveWeightFormat("int4-32")
+        tb.resolveWeightFormat("int2-32")
     pc = tb.perChannelFormat(4096)
     assert pc.packing.groupSize == 4096 and pc.packing.scaleConvention == "direct"
 
@@ -167,3 +169,41 @@ def test_case_generator_is_deterministic():
         assert np.array_equal(a[k], b[k])
     assert a["q"].min() >= -127 and a["scales"].min() >= 0.001 and a["scales"].max() <= 0.01
     assert np.array_equal(a["x_bits"].view(np.float16).astype(np.float32), a["x"])
+
+
+def test_int4_host_quantizer_matches_the_oracle_bit_for_bit():
+    """tl_quantize_linear_weight_int4 against the oracle's restatement of the planned scheme
+    (docs/quantization-design.md:69-75), including NaN / Inf / all-zero groups and ties."""
+    from oracle import oracle as orc
+    from torchlette_b200 import binding as B
+    import ctypes as C
+    lib = B.load()
+    rng = np.random.default_rng(12)
+    for n, k, g in [(3, 64, 32), (17, 256, 128), (5, 40, 8), (2, 32, 32)]:
+        w = rng.uniform(-2, 2, (n, k)).astype(np.float32)
+        w[0, :g] = 0.0
+        w[1, 3] = np.nan
+        w[min(2, n - 1), 5] = np.inf
+        w[-1, :8] = np.array([0.5, -0.5, 1.5, -1.5, 2.5, -2.5, 3.5, -3.5], np.float32) * (w[-1, :g].max() / 7.0)  # near ties
+        packed = np.zeros((n, k // 8), np.uint32)
+        scales = np.zeros((n, k // g), np.uint16)
+        assert lib.tl_quantize_linear_weight_int4(w.ctypes.data_as(C.c_void_p), n, k, g, packed.ctypes.data_as(C.c_void_p),
+                                                  scales.ctypes.data_as(C.c_void_p)) == 0
+        op, os_ = orc.quantize_linear_weight_int4(w, g)
+        assert np.array_equal(packed, op) and np.array_equal(scales, os_)
+        q = orc.unpack_int4(packed, k)
+        assert q.min() >= -7 and q.max() <= 7
+    assert lib.tl_quantize_linear_weight_int4(w.ctypes.data_as(C.c_void_p), 1, 12, 4, packed.ctypes.data_as(C.c_void_p),
+                                              scales.ctypes.data_as(C.c_void_p)) == B.TL_ERR_INVALID_ARG  # K % 8
+
+
+def test_int4_oracle_round_trips_every_nibble_in_every_lane():
+    from oracle import oracle as orc
+    for lane in range(8):
+        for q in range(-8, 8):
+            word = np.array([[(q & 0xF) << (4 * lane)]], dtype=np.uint32)
+            un = orc.unpack_int4(word, 8)
+            assert un[0, lane] == q and np.count_nonzero(un) == (1 if q else 0)
+            scales = np.array([[int(orc.f32_to_f16_bits(np.float32([3.5]))[0])]], dtype=np.uint16)
+            d = orc.dequantize_int4_to_f32(word, scales, 8, 8)
+            assert d[0, lane] == np.float32((q / 7.0) * 3.5)

@@ -44,6 +44,9 @@ class QuantPacking:
     scaleConvention: str = "snorm127"  # "snorm127": w=(q/127)*s ; "direct": w=q*s
 
 
+_VALUES_PER_WORD = {"int8-grouped": 4, "int4-grouped": 8}
+
+
 @dataclass(frozen=True)
 class StorageFormat:
     elementType: str = "f16"
@@ -51,7 +54,10 @@ class StorageFormat:
 
 
 def resolveWeightFormat(name: str, elementType: str = "f16") -> StorageFormat:
-    """"int8-64" | "int8-128" -> StorageFormat (types.ts:57-67)."""
+    """"int8-64" | "int8-128" -> StorageFormat (types.ts:57-67); "int4-32" | "int4-128" name the
+    scheme the reference plans next (docs/quantization-design.md:69-75)."""
+    if name in ("int4-32", "int4-128"):
+        return StorageFormat(elementType, QuantPacking("int4-grouped", int(name.split("-")[1]), "f16"))
     if name not in ("int8-64", "int8-128"):
         raise ValueError(f"unknown weight format {name}")
     return StorageFormat(elementType, QuantPacking("int8-grouped", 64 if name == "int8-64" else 128, "f16"))
@@ -309,22 +315,24 @@ class CudaBackend:
         self.sync()
 
     # -- quantized weights --------------------------------------------------
-    def quantizeLinearWeight(self, weight: np.ndarray, groupSize: int = 64):
+    def quantizeLinearWeight(self, weight: np.ndarray, groupSize: int = 64, scheme: str = "int8-grouped"):
         """quantizeLinearWeight (quantize.ts:77-131) through the library's host
-        quantizer.  Returns (packed u32 [N,K/4], scales u16 [N,K/G])."""
+        quantizer.  Returns (packed u32 [N,K/4], scales u16 [N,K/G]); with
+        ``scheme="int4-grouped"`` the packed words are [N,K/8]."""
         w = np.ascontiguousarray(weight, dtype=np.float32)
         if w.ndim != 2:
             raise ValueError("quantize: weight must be [N, K]")
         n, k = w.shape
-        if k % 4 != 0:
-            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by 4")
+        per_word = _VALUES_PER_WORD[scheme]
+        if k % per_word != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by {per_word}")
         if groupSize <= 0 or k % groupSize != 0:
             raise TlError(B.TL_ERR_INVALID_ARG, f"quantize: K={k} must be divisible by groupSize={groupSize}")
-        packed = np.zeros((n, k // 4), dtype=np.uint32)
+        packed = np.zeros((n, k // per_word), dtype=np.uint32)
         scales = np.zeros((n, k // groupSize), dtype=np.uint16)
-        B.check(None, self._lib.tl_quantize_linear_weight(w.ctypes.data_as(C.c_void_p), n, k, groupSize,
-                                                          packed.ctypes.data_as(C.c_void_p),
-                                                          scales.ctypes.data_as(C.c_void_p)))
+        fn = self._lib.tl_quantize_linear_weight if per_word == 4 else self._lib.tl_quantize_linear_weight_int4
+        B.check(None, fn(w.ctypes.data_as(C.c_void_p), n, k, groupSize, packed.ctypes.data_as(C.c_void_p),
+                         scales.ctypes.data_as(C.c_void_p)))
         return packed, scales
 
     def quantizeLinearWeightOnDevice(self, weight: CudaTensor, format: StorageFormat) -> CudaTensor:
@@ -357,11 +365,14 @@ class CudaBackend:
         packing = format.packing
         if packing is None:
             raise TlError(B.TL_ERR_INVALID_ARG, "createQuantizedWeight: format.packing is required")
-        if k % 4 != 0:
-            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: K={k} must be divisible by 4")
+        per_word = _VALUES_PER_WORD.get(packing.scheme)
+        if per_word is None:
+            raise TlError(B.TL_ERR_UNSUPPORTED, f"createQuantizedWeight: unsupported scheme {packing.scheme}")
+        if k % per_word != 0:
+            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: K={k} must be divisible by {per_word}")
         packed = np.ascontiguousarray(packed, dtype=np.uint32)
-        if packed.size != n * (k // 4):
-            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: packed length {packed.size} != {n * (k // 4)}")
+        if packed.size != n * (k // per_word):
+            raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: packed length {packed.size} != {n * (k // per_word)}")
         if packing.groupSize <= 0 or k % packing.groupSize != 0:
             raise TlError(B.TL_ERR_INVALID_ARG,
                           f"createQuantizedWeight: K={k} must be divisible by groupSize={packing.groupSize}")
@@ -374,8 +385,8 @@ class CudaBackend:
         if scales.size != n * groups:
             raise TlError(B.TL_ERR_INVALID_ARG, f"createQuantizedWeight: scales length {scales.size} != {n * groups}")
         st = self.ops.tensorFromArray(scales, [n, groups], "u16" if packing.scalesDtype == "f16" else "f32")
-        wt = self.ops.tensorFromArray(packed, [n, k // 4], "u32")
-        wt.shape = [n, k]  # logical shape; the buffer stays u32 [N, K/4]
+        wt = self.ops.tensorFromArray(packed, [n, k // per_word], "u32")
+        wt.shape = [n, k]  # logical shape; the buffer stays u32 [N, K/4] (int8) or [N, K/8] (int4)
         wt.dtype = format.elementType
         wt.format = format
         wt.scales = st
@@ -384,9 +395,9 @@ class CudaBackend:
     # -- descriptors ----------------------------------------------------------
     @staticmethod
     def _qdesc(packing: QuantPacking) -> B.QuantDesc:
-        if packing.scheme != "int8-grouped":
+        if packing.scheme not in _VALUES_PER_WORD:
             raise TlError(B.TL_ERR_UNSUPPORTED, f"matmulQuantizedB: unsupported scheme {packing.scheme}")
-        return B.QuantDesc(B.TL_SCHEME_INT8_GROUPED, packing.groupSize, B.DTYPE_ID[packing.scalesDtype],
+        return B.QuantDesc(B.TL_SCHEME_INT8_GROUPED if packing.scheme == "int8-grouped" else B.TL_SCHEME_INT4_GROUPED, packing.groupSize, B.DTYPE_ID[packing.scalesDtype],
                            B.TL_SCALE_SNORM127 if packing.scaleConvention == "snorm127" else B.TL_SCALE_DIRECT)
 
     @staticmethod
@@ -489,6 +500,23 @@ class CudaBackend:
         q = self._qdesc(packing)
         B.check(self._ctx, self._lib.tl_dequant_int8(self._ctx, packedWeight.buffer, scales.buffer, outBuffer.buffer,
                                                      B.DTYPE_ID[outBuffer.dtype], n, k, C.byref(q)))
+
+    def dequantize(self, weight: CudaTensor, outDtype: str = "f32") -> CudaTensor:
+        """Explicit dequant of a packed weight of either scheme to [N, K] (dispatch.ts:949-1037)."""
+        packing = weight.format.packing
+        n, k = weight.shape
+        out = self.ops.empty([n, k], outDtype)
+        q = self._qdesc(packing)
+        fn = self._lib.tl_dequant_int8 if packing.scheme == "int8-grouped" else self._lib.tl_dequant_int4
+        B.check(self._ctx, fn(self._ctx, weight.buffer, weight.scales.buffer, out.buffer, B.DTYPE_ID[outDtype], n, k, C.byref(q)))
+        return out
+
+    def unpackInt4(self, packedWeight: CudaTensor, n: int, k: int) -> np.ndarray:
+        out = self.ops.empty([n, k], "i8")
+        B.check(self._ctx, self._lib.tl_unpack_int4(self._ctx, packedWeight.buffer, out.buffer, n, k))
+        r = self.ops.read(out)
+        out.destroy()
+        return r
 
     def unpackInt8(self, packedWeight: CudaTensor, n: int, k: int) -> np.ndarray:
         out = self.ops.empty([n, k], "i8")

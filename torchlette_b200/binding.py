@@ -16,7 +16,7 @@ TL_OK = 0
 TL_ERR_INVALID_ARG, TL_ERR_UNSUPPORTED, TL_ERR_CUDA, TL_ERR_NCCL = -1, -2, -3, -4
 TL_ERR_TIMEOUT, TL_ERR_OOM, TL_ERR_UNIMPLEMENTED = -5, -6, -7
 TL_F32, TL_F16, TL_BF16 = 0, 1, 2
-TL_SCHEME_INT8_GROUPED = 1
+TL_SCHEME_INT8_GROUPED, TL_SCHEME_INT4_GROUPED = 1, 2
 TL_SCALE_SNORM127, TL_SCALE_DIRECT = 0, 1
 TL_EPI_NONE, TL_EPI_BIAS, TL_EPI_UNARY, TL_EPI_BINARY, TL_EPI_CAST = 0, 1, 2, 3, 4
 TL_UNARY = {"relu": 1, "silu": 2, "sigmoid": 3, "tanh": 4, "gelu": 5, "gelu_tanh": 5, "gelu_erf": 6}
@@ -109,6 +109,9 @@ SIGNATURES = {
     "tl_qmatmul_nt": (_I32, _QARGS + [_I64, _I64, _I64, C.POINTER(QuantDesc), _F, C.POINTER(Epilogue)]),
     "tl_matmul": (_I32, [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I32, _I32, _F, _I32, _I32, _I32,
                          _I32, _I32, C.POINTER(Epilogue), C.POINTER(PlanReceipt)]),
+    "tl_quantize_linear_weight_int4": (_I32, [_P, _I64, _I64, _I32, _P, _P]),
+    "tl_dequant_int4": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),
+    "tl_unpack_int4": (_I32, [_P, _P, _P, _I64, _I64]),
     "tl_unary_op": (_I32, [_P, _I32, _P, _I32, _P, _I32, _I64]),
     "tl_binary_op": (_I32, [_P, _I32, _P, _I32, _P, _I32, _P, _I32, _I64, _I64, _I32]),
     "tl_transpose2d": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32]),

@@ -513,6 +513,25 @@ FN(DequantInt8) {
   return check(env, c, tl_dequant_int8(c, dptr(env, argv[1]), dptr(env, argv[2]), dptr(env, argv[3]), i32(env, argv[4]), i64(env, argv[5]),
                                        i64(env, argv[6]), &q));
 }
+/* quantizeLinearWeightInt4(weightF32, n, k, group, packedU32 [n, k/8], scalesU16) */
+FN(QuantizeLinearWeightInt4) {
+  ARGS(6); size_t wb = 0, pb = 0, sb = 0;
+  const float* w = (const float*)host_ptr(env, argv[0], &wb); uint32_t* p = (uint32_t*)host_ptr(env, argv[4], &pb);
+  uint16_t* s = (uint16_t*)host_ptr(env, argv[5], &sb);
+  int64_t n = i64(env, argv[1]), k = i64(env, argv[2]); int32_t g = i32(env, argv[3]);
+  if (g <= 0 || n < 0 || k < 0 || wb != (size_t)(n * k) * 4 || pb != (size_t)(n * k) / 2 || sb != (size_t)(n * (k / g)) * 2) {
+    napi_throw_error(env, NULL, "quantizeLinearWeightInt4: array lengths do not match n, k and the group size");
+    return undef(env);
+  }
+  return check(env, NULL, tl_quantize_linear_weight_int4(w, n, k, g, p, s));
+}
+FN(DequantInt4) {
+  ARGS(8); CTX(0); tl_quant_desc q;
+  if (!read_qdesc(env, argv[7], &q)) return undef(env);
+  return check(env, c, tl_dequant_int4(c, dptr(env, argv[1]), dptr(env, argv[2]), dptr(env, argv[3]), i32(env, argv[4]), i64(env, argv[5]),
+                                       i64(env, argv[6]), &q));
+}
+FN(UnpackInt4) { ARGS(5); CTX(0); return check(env, c, tl_unpack_int4(c, dptr(env, argv[1]), dptr(env, argv[2]), i64(env, argv[3]), i64(env, argv[4]))); }
 FN(UnpackInt8) { ARGS(5); CTX(0); return check(env, c, tl_unpack_int8(c, dptr(env, argv[1]), dptr(env, argv[2]), i64(env, argv[3]), i64(env, argv[4]))); }
 
 /* ---- companion ops ---------------------------------------------------------------- */
@@ -671,7 +690,8 @@ napi_value napi_register_module_v1(napi_env env, napi_value exports) {
       EXPORT("qgemvNt", QgemvNt), EXPORT("qgemvNtBatched", QgemvNtBatched), EXPORT("qgemvChainCreate", QgemvChainCreate),
       EXPORT("qgemvChainLaunch", QgemvChainLaunch), EXPORT("qgemvChainDestroy", QgemvChainDestroy),
       EXPORT("qgemvNtStaticScratch", QgemvNtStaticScratch), EXPORT("qgemmNt", QgemmNt), EXPORT("qmatmulNt", QmatmulNt),
-      EXPORT("dequantInt8", DequantInt8), EXPORT("unpackInt8", UnpackInt8), EXPORT("matmul", Matmul),
+      EXPORT("dequantInt8", DequantInt8), EXPORT("unpackInt8", UnpackInt8), EXPORT("quantizeLinearWeightInt4", QuantizeLinearWeightInt4),
+      EXPORT("dequantInt4", DequantInt4), EXPORT("unpackInt4", UnpackInt4), EXPORT("matmul", Matmul),
       EXPORT("unaryOp", UnaryOp), EXPORT("binaryOp", BinaryOp), EXPORT("transpose2d", Transpose2d),
       EXPORT("planQmatmul", PlanQmatmul), EXPORT("variantName", VariantName), EXPORT("forceVariant", ForceVariant),
       EXPORT("classifyShape", ClassifyShape), EXPORT("shapeClassName", ShapeClassName),

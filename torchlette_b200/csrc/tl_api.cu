@@ -607,6 +607,8 @@ static int32_t qmatmul_impl(tl_ctx* ctx, const char* who, int route /*0 auto,1 g
                             int32_t out_dtype, int64_t m, int64_t n, int64_t k, const tl_quant_desc* qdesc,
                             float alpha, const tl_epilogue* epilogue, tl_plan_receipt* receipt_only) {
   TL_CHECK_CTX(ctx);
+  if (qdesc && qdesc->scheme == TL_SCHEME_INT4_GROUPED)  // the second value on the format axis: its own kernels
+    return tl_int4_matmul(ctx, who, route, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc, alpha, epilogue, receipt_only);
   int32_t rc = tl_check_qargs(ctx, who, receipt_only ? (const void*)16 : a, a_dtype,
                               receipt_only ? (const void*)16 : packed, receipt_only ? (const void*)16 : scales,
                               receipt_only ? (const void*)16 : out, out_dtype, m, n, k, qdesc);

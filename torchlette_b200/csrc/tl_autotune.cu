@@ -36,8 +36,8 @@ const char* tl_variant_name(const tl_variant* v) {
   if (!v) return "(null)";
   const char* fam = v->family == TL_FAMILY_QGEMV ? "qgemv" : v->family == TL_FAMILY_QGEMM ? "qgemm" : v->family == TL_FAMILY_MATMUL ? "matmul" : "?";
   const char* kern = "?";
-  if (v->family == TL_FAMILY_QGEMV) kern = v->kernel == 0 ? "scalar" : v->kernel == 1 ? "simt" : v->kernel == 2 ? "mma" : v->kernel == 3 ? "sk" : v->kernel == 4 ? "ring" : v->kernel == 5 ? "tma" : v->kernel == 6 ? "bulk" : v->kernel == 7 ? "chain" : v->kernel == 8 ? "stream" : "?";
-  if (v->family == TL_FAMILY_QGEMM) kern = v->kernel == 0 ? "tcgen05" : v->kernel == 1 ? "sliced" : "?";
+  if (v->family == TL_FAMILY_QGEMV) kern = v->kernel == 0 ? "scalar" : v->kernel == 1 ? "simt" : v->kernel == 2 ? "mma" : v->kernel == 3 ? "sk" : v->kernel == 4 ? "ring" : v->kernel == 5 ? "tma" : v->kernel == 6 ? "bulk" : v->kernel == 7 ? "chain" : v->kernel == 8 ? "stream" : v->kernel == 9 ? "int4" : "?";
+  if (v->family == TL_FAMILY_QGEMM) kern = v->kernel == 0 ? "tcgen05" : v->kernel == 1 ? "sliced" : v->kernel == 2 ? "dequant+dense" : "?";
   if (v->family == TL_FAMILY_MATMUL) kern = v->kernel == 0 ? "tiled" : v->kernel == 1 ? "gemv" : v->kernel == 2 ? "tc" : "?";
   snprintf(buf, sizeof(buf), "%s.%s[%d,%d,%d,%d]", fam, kern, v->p0, v->p1, v->p2, v->p3);
   return buf;

@@ -204,6 +204,10 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
                         const void* packed, const void* scales, void* out, int32_t out_dtype,
                         int64_t m, int64_t n, int64_t k, const tl_quant_desc& q,
                         const EpiParams& epi, tl_plan_receipt* receipt_only);
+// int4-grouped branch of the seam (tl_int4.cu)
+int32_t tl_int4_matmul(tl_ctx* ctx, const char* who, int route, const void* a, int32_t a_dtype, const void* packed, const void* scales,
+                       void* out, int32_t out_dtype, int64_t m, int64_t n, int64_t k, const tl_quant_desc* q, float alpha,
+                       const tl_epilogue* epilogue, tl_plan_receipt* receipt_only);
 // Dense tensor-core matmul (tl_matmul_tc.cu): NT layout, both operands f16 or both bf16.
 bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, int64_t k, int32_t dtype_a, int32_t dtype_b);
 void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid);

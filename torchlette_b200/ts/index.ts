@@ -176,8 +176,9 @@ export function createQuantizedWeight(packed: Uint32Array, scalesBits: Uint16Arr
                                       format: StorageFormat & { scaleConvention?: "snorm127" | "direct" }): CudaTensor {
   const packing = format.packing;
   if (!packing) throw new Error("createQuantizedWeight: format.packing is required");
-  if (k % 4 !== 0) throw new Error(`createQuantizedWeight: K=${k} must be divisible by 4`);
-  if (packed.length !== n * (k / 4)) throw new Error(`createQuantizedWeight: packed length ${packed.length} != ${n * (k / 4)}`);
+  const perWord = (packing.scheme as string) === "int4-grouped" ? 8 : 4; // int4: the reference's planned second scheme
+  if (k % perWord !== 0) throw new Error(`createQuantizedWeight: K=${k} must be divisible by ${perWord}`);
+  if (packed.length !== n * (k / perWord)) throw new Error(`createQuantizedWeight: packed length ${packed.length} != ${n * (k / perWord)}`);
   const groups = k / packing.groupSize;
   if (scalesBits.length !== n * groups) throw new Error(`createQuantizedWeight: scales length ${scalesBits.length} != ${n * groups}`);
   const buf: Handle = addon.alloc(need(), packed.byteLength);
@@ -188,10 +189,11 @@ export function createQuantizedWeight(packed: Uint32Array, scalesBits: Uint16Arr
   return w;
 }
 /** quantizeLinearWeight (src/backend/quantize.ts:77-131) through the library's host quantizer. */
-export function quantizeLinearWeight(weight: Float32Array, n: number, k: number, groupSize = 64) {
-  const packed = new Uint32Array(n * (k / 4));
+export function quantizeLinearWeight(weight: Float32Array, n: number, k: number, groupSize = 64, scheme: "int8-grouped" | "int4-grouped" = "int8-grouped") {
+  const packed = new Uint32Array(n * (k / (scheme === "int4-grouped" ? 8 : 4)));
   const scales = new Uint16Array(n * (k / groupSize));
-  addon.quantizeLinearWeight(weight, n, k, groupSize, packed, scales);
+  if (scheme === "int4-grouped") addon.quantizeLinearWeightInt4(weight, n, k, groupSize, packed, scales);
+  else addon.quantizeLinearWeight(weight, n, k, groupSize, packed, scales);
   return { packed, scales, n, k, groupSize };
 }
 
@@ -211,8 +213,8 @@ function encodeEpilogue(epilogue?: EpilogueConfig, inputs: CudaTensor[] = []) {
 /** tl_quant_desc as the addon takes it: Int32Array [scheme, groupSize, scalesDtype, scaleConvention]. */
 function qdesc(format: any): Int32Array {
   const p = format.packing;
-  if (p.scheme !== "int8-grouped") throw new Error(`matmulQuantizedB: unsupported scheme ${p.scheme}`);
-  return Int32Array.of(1, p.groupSize, DTYPE_ID[p.scalesDtype], format.scaleConvention === "direct" ? 1 : 0);
+  if (p.scheme !== "int8-grouped" && p.scheme !== "int4-grouped") throw new Error(`matmulQuantizedB: unsupported scheme ${p.scheme}`);
+  return Int32Array.of(p.scheme === "int4-grouped" ? 2 : 1, p.groupSize, DTYPE_ID[p.scalesDtype], format.scaleConvention === "direct" ? 1 : 0);
 }
 const defaultQdesc = (groupSize: number, scalesDtype: string): Int32Array => Int32Array.of(1, groupSize, scalesDtype === "f32" ? 0 : 1, 0);
 
