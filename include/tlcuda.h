@@ -474,15 +474,15 @@ TL_API int32_t tl_qgemv_nt_allreduce(tl_ctx* ctx, const void* a, int32_t a_dtype
 
 /* Row-parallel sum WITHOUT a collective launch (tensor parallelism; no counterpart in the
  * reference).  tl_qgemv_nt_push computes this rank's partial product alpha * a_r . W_r^T exactly as
- * tl_qgemv_nt would and, instead of storing it, pushes it -- in f32, so that the sum over ranks is
- * rounded to out_dtype only once -- into every rank's exchange buffer over NVLink; it waits for nobody.  `out` names the local [m, n] buffer
+ * tl_qgemv_nt would and, instead of storing it, pushes it -- as 24-bit floats (15 mantissa bits; 16-bit
+ * partials measured 1e-2 off at 8 ranks), two of them and an arrival tag per 8-byte word -- into every
+ * rank's exchange buffer over NVLink; it waits for nobody.  `out` names the local [m, n] buffer
  * that is to hold the sum over ranks.  The NEXT small-batch launch on the context (tl_qgemv_nt,
  * tl_qgemv_nt_batched or tl_qmatmul_nt with m <= 16) must be the one that reads `out` as its
  * activations: after its weight prefetch it waits (bounded, TL_ERR_TIMEOUT at tl_sync) for all
  * ranks' partials, sums them in rank order into `out` (identical bits on every rank) and then runs
  * its own product.  Any other consumer calls tl_reduce_pending first, which does the same sum in a
- * small launch of its own.  Needs tl_p2p_create / tl_p2p_attach with max_bytes >= m*n*8 (every f32 partial
- * sum travels in an 8-byte word with its epoch); m in
+ * small launch of its own.  Needs tl_p2p_create / tl_p2p_attach with max_bytes >= m*n*4; m in
  * [1,16]; f16/bf16 activations and outputs; K % 64 == 0; N % 16 == 0; no epilogue ops (alpha only:
  * anything non-linear would have to follow the sum).  Collective: every rank makes the same calls
  * in the same order.  With one rank (and no loopback exchange attached) it is tl_qgemv_nt. */

@@ -120,3 +120,28 @@ def test_int4_argument_errors(backend):
         be.createQuantizedWeight(np.zeros(10, np.uint32), np.zeros(4, np.uint16), 4, 36, fmt)  # K % 8
     with pytest.raises(tb.TlError):
         be.quantizeLinearWeight(np.zeros((2, 36), np.float32), 12, scheme="int4-grouped")
+
+
+@pytest.mark.parametrize("m", [1, 8, 16])
+@pytest.mark.parametrize("g", [128, 256, 1024])
+def test_int4_tensor_core_and_simt_forms_agree(backend, m, g):
+    """K and the group multiples of 128 take the mma.sync form; forcing {QGEMV, simt} takes the f32
+    form.  Both against the oracle, and against each other within f32 summation-order noise."""
+    be = backend
+    n, k = 264, 1024
+    w, wref, _ = _weight(be, n, k, g, seed=g + m)
+    rng = np.random.default_rng(g)
+    xv = rng.uniform(-1, 1, (m, k)).astype(np.float16)
+    x = be.ops.tensorFromArray(xv, [m, k], "f16")
+    y1 = be.linear(x, w, None, None, "f32")
+    be.forceVariant((1, 1, 8, 1, 1, 0))
+    try:
+        y2 = be.linear(x, w, None, None, "f32")
+    finally:
+        be.forceVariant(None)
+    ref = orc.linear_reference(xv.astype(np.float32), wref)
+    a, b = be.ops.read(y1), be.ops.read(y2)
+    assert cases.rel_err(a, ref) <= 1e-3 and cases.rel_err(b, ref) <= 1e-3
+    assert cases.rel_err(a, b) <= 1e-4
+    for t in (x, y1, y2, w.scales, w):
+        t.destroy()

@@ -765,3 +765,57 @@ def test_wide_ring_tiles_grouped_scales_and_batched_launch(backend):
     for t in [xt] + outs + [w.scales for w in ws] + ws:
         t.destroy()
     assert be.getGpuUncapturedErrorCount() == 0
+
+
+# ---------------------------------------------------------------------------
+# How each KERNEL unpacks: every byte value (-128 included: the dequantizer does not clamp,
+# quantize.ts:138-156) in every byte lane, read back through the product with one-hot activations.
+# One non-zero term per output and a power-of-two scale: the result is exact in every kernel.
+# ---------------------------------------------------------------------------
+def _lane_matrix(n, k):
+    q = ((np.arange(n)[:, None] + 37 * np.arange(k)[None, :]) % 256 - 128).astype(np.int8)
+    for lane in range(4):
+        assert len(np.unique(q[:, lane::4])) == 256
+    return q
+
+
+def _one_hot_products(be, fn_name, variant, n, k, act_dtype):
+    lib, ctx = be._lib, be._ctx
+    q = _lane_matrix(n, k)
+    packed = np.ascontiguousarray(q).view(np.uint32).reshape(n, k // 4)
+    scales = np.full((n,), 0.5, np.float32)
+    w = be.createQuantizedWeight(packed, scales, n, k, tb.perChannelFormat(k))
+    qd = be._qdesc(w.format.packing)
+    out = be.ops.empty([16, n], "f32")
+    be.forceVariant(variant)
+    try:
+        for k0 in range(0, k, 16):
+            x = np.zeros((16, k), np.float32)
+            x[np.arange(16), k0 + np.arange(16)] = 1.0
+            xt = be.ops.tensorFromArray(x.astype(np.float16) if act_dtype == "f16" else orc.bf16_bits_rne(x.reshape(-1)), [16, k], act_dtype)
+            rc = getattr(lib, fn_name)(ctx, xt.buffer, B.DTYPE_ID[act_dtype], w.buffer, w.scales.buffer, out.buffer, B.TL_F32, 16, n, k,
+                                       C.byref(qd), 1.0, None)
+            if rc == B.TL_ERR_UNSUPPORTED:
+                xt.destroy()
+                pytest.skip(f"variant {variant} does not run m=16 n={n} k={k}: {lib.tl_last_error(ctx).decode()}")
+            B.check(ctx, rc)
+            got = be.ops.read(out)
+            expect = q[:, k0:k0 + 16].T.astype(np.float32) * 0.5
+            assert np.array_equal(got, expect), (variant, k0)
+            xt.destroy()
+    finally:
+        be.forceVariant(None)
+        for t in (out, w.scales, w):
+            t.destroy()
+
+
+@pytest.mark.parametrize("act_dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("variant", [None] + GEMV_VARIANTS_HALF)
+def test_gemv_kernels_unpack_every_byte_in_every_lane(backend, variant, act_dtype):
+    _one_hot_products(backend, "tl_qgemv_nt", variant, 256, 128, act_dtype)
+
+
+@pytest.mark.parametrize("act_dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("variant", [None, (2, 0, 16, 128, 8, 8), (2, 0, 128, 64, 8, 4), (2, 0, 192, 128, 3, 8)])
+def test_tcgen05_converter_unpacks_every_byte_in_every_lane(backend, variant, act_dtype):
+    _one_hot_products(backend, "tl_qgemm_nt", variant, 256, 128, act_dtype)

@@ -90,3 +90,33 @@ def test_full_size_stack_properties(backend):
     s1.destroy()
     s8.destroy()
     assert backend.getGpuUncapturedErrorCount() == 0
+
+
+@pytest.mark.parametrize("li", [0, 35])
+def test_full_size_first_and_last_layer_projections_against_oracle(backend, li):
+    """BASELINE config 4 at full size: the seven projections of layer 0 and of the last layer, each
+    against the oracle on 48 sampled output columns, computed from the stack's own inputs to that
+    projection (so an error cannot hide behind the next one).  f16 outputs: 1e-2."""
+    cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": 8})
+    s = DecodeStack(backend, cfg, seed=0)
+    try:
+        gen = torch.Generator(device=s.dev)
+        gen.manual_seed(100 + li)
+        xin = torch.randn(8, cfg.hidden, device=s.dev, generator=gen).to(s.tdt)
+        (s.x if li == 0 else s.h2).copy_(xin)
+        torch.cuda.synchronize()
+        s.run_layer(li)
+        backend.sync()
+        pq, pk, pv, po, pg, pu, pd = s.layers[li]
+        checks = [(pq, xin, s.q), (pk, xin, s.kk), (pv, xin, s.v), (po, s.q, s.h1), (pg, s.h1, s.g), (pu, s.h1, s.u), (pd, s.g, s.h2)]
+        for p, inp, out in checks:
+            rows = np.unique(np.concatenate([np.arange(0, 16), np.arange(p.n // 2, p.n // 2 + 16), np.arange(p.n - 16, p.n)]))
+            idx = torch.as_tensor(rows, device=s.dev)
+            w = p.w[idx].cpu().numpy().astype(np.float32) * p.s[idx].cpu().numpy().astype(np.float32)[:, None]
+            ref = orc.linear_reference(inp.float().cpu().numpy(), w, None, p.act, alpha=p.alpha)
+            got = out[:, idx].float().cpu().numpy()
+            err = cases.rel_err(got, ref)
+            assert err <= 1e-2, (li, p.name, err)
+    finally:
+        s.destroy()
+    assert backend.getGpuUncapturedErrorCount() == 0

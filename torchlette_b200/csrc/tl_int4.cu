@@ -7,7 +7,9 @@
 //
 //   host quantizer        tl_quantize_linear_weight_int4 (same arithmetic as the int8 quantizer)
 //   explicit dequant      tl_dequant_int4 (f64 through a 16-entry table, one rounding: bit-exact)
-//   small batch, m <= 16  qgemv_int4_kernel: warp per R rows, one packed word (8 weights) per lane and
+//   small batch, m <= 16  qgemv_int4_mma_kernel (f16 / bf16 activations, K and the group multiples of
+//                         128): mma.sync with the nibbles converted pairwise, see below; else
+//                         qgemv_int4_kernel: warp per R rows, one packed word (8 weights) per lane and
 //                         step -- a warp reads 128 contiguous bytes of each row per step -- nibbles to
 //                         f32 by exponent stuffing, f32 FMA, group scale applied to the group's partial
 //                         sum, warp-shuffle reduction, the common epilogue.  HBM-bound at m <= 2
@@ -23,6 +25,7 @@
 #include <vector>
 
 #include "tl_common.cuh"
+#include "tl_mma_frag.cuh"
 
 namespace {
 
@@ -209,6 +212,127 @@ void launch_int4_m(tl_ctx* ctx, Int4Args p, const EpiParams& epi, int m) {
   }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core form (f16 / bf16 activations, K % 128 == 0, group % 128 == 0): CTA per 16 weight rows,
+// warps interleaved over 128-wide k blocks.  Lane (g, t) loads 16 bytes = 32 nibbles of rows g and
+// g + 8 and the matching 32 activations of batch row g.  (w ^ 0x88888888) turns every nibble into
+// q + 8; ((u >> 4x) & 0x000F000F) | magic is the pair (q_x + 8, q_{x+4} + 8) as 16-bit floats
+// 1024 + . (f16) or 128 + . (bf16), one subtraction gives (q_x, q_{x+4}) exactly.  A word of eight
+// nibbles feeds two mma.sync.m16n8k16; the activations are paired the same way with two byte
+// permutes per MMA.  One group per k block: the block's accumulators are folded into the totals
+// with the rows' scales (per-channel scales once at the end).
+// ---------------------------------------------------------------------------
+template <typename AT> struct Nib;
+template <> struct Nib<__half> {
+  __device__ static uint32_t pair(uint32_t u, int x) {
+    const uint32_t v = ((u >> (4 * x)) & 0x000F000Fu) | 0x64006400u;
+    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&v), __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408)));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+};
+template <> struct Nib<__nv_bfloat16> {
+  __device__ static uint32_t pair(uint32_t u, int x) {
+    const uint32_t v = ((u >> (4 * x)) & 0x000F000Fu) | 0x43004300u;
+    const uint32_t m = 0x43084308u;  // 136 | 136
+    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&m));
+    return *reinterpret_cast<const uint32_t*>(&r);
+  }
+};
+
+template <typename AT, int NT, bool GROUPED>
+__global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiParams epi) {
+  extern __shared__ float red4[];  // [warps][NT][4][32]
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int64_t tile_row = int64_t(blockIdx.x) * 16;
+  const int64_t r_lo = min(tile_row + g, int64_t(p.n) - 1), r_hi = min(tile_row + g + 8, int64_t(p.n) - 1);
+  const uint8_t* wb = reinterpret_cast<const uint8_t*>(p.packed);
+  const int64_t row_bytes = p.k >> 1;
+  const uint8_t* w_lo = wb + r_lo * row_bytes + 16 * t;
+  const uint8_t* w_hi = wb + r_hi * row_bytes + 16 * t;
+  const AT* a = reinterpret_cast<const AT*>(p.a);
+  const AT* x_row[NT];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) x_row[nt] = a + int64_t(min(g + 8 * nt, p.m - 1)) * p.k + 32 * t;
+  float total[NT][4];
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
+  const int kblocks = p.k >> 7;
+  for (int kb = warp; kb < kblocks; kb += warps) {
+    const uint4 wl4 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
+    const uint4 wh4 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+    const uint32_t wl[4] = {wl4.x ^ 0x88888888u, wl4.y ^ 0x88888888u, wl4.z ^ 0x88888888u, wl4.w ^ 0x88888888u};
+    const uint32_t wh[4] = {wh4.x ^ 0x88888888u, wh4.y ^ 0x88888888u, wh4.z ^ 0x88888888u, wh4.w ^ 0x88888888u};
+    float c[NT][4];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) c[nt][i] = GROUPED ? 0.f : total[nt][i];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t a00 = Nib<AT>::pair(wl[j], 0), a01 = Nib<AT>::pair(wh[j], 0), a02 = Nib<AT>::pair(wl[j], 1), a03 = Nib<AT>::pair(wh[j], 1);
+      const uint32_t a10 = Nib<AT>::pair(wl[j], 2), a11 = Nib<AT>::pair(wh[j], 2), a12 = Nib<AT>::pair(wl[j], 3), a13 = Nib<AT>::pair(wh[j], 3);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x_row[nt] + int64_t(kb) * 128) + j);  // x0..x7 of this word
+        MmaOps<AT>::mma(c[nt], a00, a01, a02, a03, __byte_perm(xv.x, xv.z, 0x5410), __byte_perm(xv.x, xv.z, 0x7632));
+        MmaOps<AT>::mma(c[nt], a10, a11, a12, a13, __byte_perm(xv.y, xv.w, 0x5410), __byte_perm(xv.y, xv.w, 0x7632));
+      }
+    }
+    if (GROUPED) {
+      const int grp = (kb * 128) / p.group;
+      const float s_lo = tl_load_scale(p.scales, p.scales_dtype, r_lo * p.groups_per_row + grp);
+      const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + grp);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        total[nt][0] = fmaf(s_lo, c[nt][0], total[nt][0]); total[nt][1] = fmaf(s_lo, c[nt][1], total[nt][1]);
+        total[nt][2] = fmaf(s_hi, c[nt][2], total[nt][2]); total[nt][3] = fmaf(s_hi, c[nt][3], total[nt][3]);
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total[nt][i] = c[nt][i];
+    }
+  }
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) red4[((warp * NT + nt) * 4 + i) * 32 + lane] = total[nt][i];
+  __syncthreads();
+  for (int o = threadIdx.x; o < NT * 128; o += blockDim.x) {
+    const int nt = o >> 7, i = (o >> 5) & 3, ln = o & 31;
+    float v = 0.f;
+    for (int w = 0; w < warps; ++w) v += red4[((w * NT + nt) * 4 + i) * 32 + ln];
+    const int64_t row = tile_row + (ln >> 2) + ((i & 2) ? 8 : 0);
+    const int col = 8 * nt + 2 * (ln & 3) + (i & 1);
+    if (row < p.n && col < p.m) {
+      float sc = p.wscale;
+      if (!GROUPED) sc *= tl_load_scale(p.scales, p.scales_dtype, row);
+      const float r = tl_apply_epilogue(epi, v * sc, col, row, p.n);
+      tl_store_out(p.out, p.out_dtype, int64_t(col) * p.n + row, r);
+    }
+  }
+}
+
+template <typename AT>
+void launch_int4_mma(tl_ctx* ctx, const Int4Args& p, const EpiParams& e, bool grouped) {
+  const int kblocks = p.k >> 7;
+  const int warps = kblocks >= 16 ? 16 : kblocks >= 8 ? 8 : kblocks >= 4 ? 4 : kblocks >= 2 ? 2 : 1;
+  const int grid = (p.n + 15) / 16, nt = p.m > 8 ? 2 : 1;
+  const size_t smem = size_t(warps) * nt * 128 * sizeof(float);
+  if (nt == 2) {
+    if (grouped) qgemv_int4_mma_kernel<AT, 2, true><<<grid, warps * 32, smem, ctx->stream>>>(p, e);
+    else qgemv_int4_mma_kernel<AT, 2, false><<<grid, warps * 32, smem, ctx->stream>>>(p, e);
+  } else {
+    if (grouped) qgemv_int4_mma_kernel<AT, 1, true><<<grid, warps * 32, smem, ctx->stream>>>(p, e);
+    else qgemv_int4_mma_kernel<AT, 1, false><<<grid, warps * 32, smem, ctx->stream>>>(p, e);
+  }
+  ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+}
+
 int32_t check_int4(tl_ctx* ctx, const char* who, const void* packed, const void* scales, int64_t n, int64_t k, const tl_quant_desc* q) {
   if (!packed || !scales) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: missing packing/scales on B operand", who);
   if (n < 0 || k < 0 || n > 0x7fffffffLL || k > 0x7fffffffLL) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "%s: bad shape n=%lld k=%lld", who, (long long)n, (long long)k);
@@ -332,7 +456,14 @@ int32_t tl_int4_matmul(tl_ctx* ctx, const char* who, int route, const void* a, i
     p.group = q->group_size; p.groups_per_row = int32_t(k / q->group_size);
     p.scales_dtype = q->scales_dtype; p.out_dtype = out_dtype;
     p.wscale = q->scale_convention == TL_SCALE_SNORM127 ? 1.0f / 7.0f : 1.0f;
-    if (a_dtype == TL_F32) launch_int4_m<float>(ctx, p, epi, int(m));
+    // the tensor-core form when its layout conditions hold (and it is not switched off for A/B tests)
+    const bool forced_simt = ctx->has_forced && ctx->forced.family == TL_FAMILY_QGEMV && ctx->forced.kernel == 1;
+    const bool mma_ok = !forced_simt && a_dtype != TL_F32 && k % 128 == 0 && q->group_size % 128 == 0 &&
+                        (reinterpret_cast<uintptr_t>(packed) & 15) == 0;
+    p.m = int32_t(m); p.row0 = 0;
+    if (mma_ok && a_dtype == TL_F16) launch_int4_mma<__half>(ctx, p, epi, q->group_size != k);
+    else if (mma_ok) launch_int4_mma<__nv_bfloat16>(ctx, p, epi, q->group_size != k);
+    else if (a_dtype == TL_F32) launch_int4_m<float>(ctx, p, epi, int(m));
     else if (a_dtype == TL_F16) launch_int4_m<__half>(ctx, p, epi, int(m));
     else launch_int4_m<__nv_bfloat16>(ctx, p, epi, int(m));
     TL_CUDA(ctx, cudaGetLastError());

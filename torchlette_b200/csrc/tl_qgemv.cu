@@ -610,9 +610,10 @@ __device__ __forceinline__ float push_load(const void* base, int dtype, int64_t 
 //
 // tl_qgemv_nt_push (ring tile, PUSH == 2): every CTA stages its 16-row tile of the LOCAL partial
 // product in shared memory, in f32, and stores it into slot (half, rank) of EVERY rank's exchange
-// buffer as 8-byte words {f32 partial sum, epoch}.  (f32, not the 16-bit output type: a 16-bit partial
-// loses up to half an ulp of a value that may be far larger than the total, and eight of them add up
-// to 1e-2 on the parity metric; the sum of f32 partials is rounded once.)  An 8-byte store arrives
+// buffer as 8-byte words {two partial sums of 24 bits each, 16-bit tag} (push_pack).  (Not the 16-bit
+// output type: a 16-bit partial loses up to half an ulp of a value that may be far larger than the
+// total, and eight of them add up to 1e-2 on the parity metric.  Whole f32 values would double the
+// NVLink bytes: measured +0.14 ms per step at 8 ranks.)  An 8-byte store arrives
 // whole, so the epoch that travels with the data is the arrival signal: the producer needs no fence,
 // no atomic and no flag (a system-scope release per CTA, 256 per launch, cost 8 us; fences from
 // every thread 12 us), and it waits for nobody.
@@ -632,8 +633,28 @@ __device__ __forceinline__ float push_load(const void* base, int dtype, int64_t 
 // the producer reads epoch_p and publishes epoch_c = epoch_p + 1, the consumer reads epoch_c and
 // publishes epoch_p = epoch_c.  A producer clears done[] of the OTHER half when it starts (its own
 // previous consumer has finished with it).  Slots are [2 halves][kMaxPeers][max_bytes] with
-// max_bytes >= m * n * 8 (every f32 partial sum carries a 4-byte epoch).
+// max_bytes >= m * n * 4 (two partial sums and a tag per 8-byte word).
 // ---------------------------------------------------------------------------
+// One 8-byte word of the push protocol carries TWO partial sums and the arrival tag: each f32 is
+// rounded (to nearest even) to 24 bits -- sign, exponent, 15 mantissa bits: 32 times finer than an
+// f16 partial, so the sum of eight of them still rounds to the right 16-bit result -- and the last
+// 16 bits hold (epoch % 65535) + 1, never 0, so zero-filled memory never looks like an arrival.
+//   lo = v0[31:8] | v1[31:24]      hi = v1[23:8] << 16 | tag
+__device__ __forceinline__ uint32_t push_round24(float v) {
+  const uint32_t b = __float_as_uint(v);
+  if ((b & 0x7f800000u) == 0x7f800000u) return b & 0xffffff00u;  // Inf / NaN: truncate, never carry into the sign
+  return (b + 0x7fu + ((b >> 8) & 1u)) & 0xffffff00u;
+}
+__device__ __forceinline__ uint32_t push_tag(uint32_t epoch) { return epoch % 65535u + 1u; }
+__device__ __forceinline__ uint2 push_pack(float v0, float v1, uint32_t tag) {
+  const uint32_t b0 = push_round24(v0), b1 = push_round24(v1);
+  return make_uint2(b0 | (b1 >> 24), ((b1 << 8) & 0xffff0000u) | tag);
+}
+__device__ __forceinline__ void push_unpack(uint32_t lo, uint32_t hi, float& v0, float& v1) {
+  v0 = __uint_as_float(lo & 0xffffff00u);
+  v1 = __uint_as_float(((lo & 0xffu) << 24) | ((hi >> 8) & 0x00ffff00u));
+}
+
 struct ReduceIn {
   uint8_t* base;        // this rank's exchange buffer
   uint64_t max_bytes;
@@ -661,27 +682,27 @@ __device__ __forceinline__ void reduce_in_prologue(const ReduceIn& r) {
       const int per = (r.count_vec + r.nsum - 1) / r.nsum;
       const int v0 = int(blockIdx.x) * per, v1 = min(v0 + per, r.count_vec);
       for (int i = v0 + tid; i < v1; i += nthreads) {
-        // output vector i = 8 values = eight {f32, epoch} words (64 bytes) of every rank's slot
+        // output vector i = 8 values = four {two partial sums, tag} words (32 bytes) of every rank's slot
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const uint32_t tag = push_tag(epoch);
         for (int rr = 0; rr < r.world; ++rr) {
-          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 4 * i;
-          uint4 u[4];
+          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 2 * i;
+          uint4 u0, u1;
           int spins = 0;
           for (;;) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) u[j] = __ldcv(src + j);
-            bool all = true;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) all = all && u[j].y == epoch && u[j].w == epoch;
-            if (all) break;
+            u0 = __ldcv(src);
+            u1 = __ldcv(src + 1);
+            if ((u0.y & 0xffffu) == tag && (u0.w & 0xffffu) == tag && (u1.y & 0xffffu) == tag && (u1.w & 0xffffu) == tag) break;
             if (++spins > r.spin_limit) { atomicExch(r.status, TL_ERR_TIMEOUT); break; }
             __nanosleep(200);  // thousands of threads poll lines that a peer is writing: leave the L2 slice room
           }
+          float v[8];
+          push_unpack(u0.x, u0.y, v[0], v[1]);
+          push_unpack(u0.z, u0.w, v[2], v[3]);
+          push_unpack(u1.x, u1.y, v[4], v[5]);
+          push_unpack(u1.z, u1.w, v[6], v[7]);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            acc[2 * j] += __uint_as_float(u[j].x);
-            acc[2 * j + 1] += __uint_as_float(u[j].z);
-          }
+          for (int j = 0; j < 8; ++j) acc[j] += v[j];
         }
         uint32_t o[4];
 #pragma unroll
@@ -882,17 +903,18 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
     }
   }
   if (PUSH == 2) {
-    // the tile [m columns][16 rows] leaves as 8-byte words {f32 value, epoch}, one copy per peer
+    // the tile [m columns][16 rows] leaves as 8-byte words {two partial sums, tag}, one copy per peer
     __syncthreads();
-    const int per_peer = p.m * 16;
+    const int per_peer = p.m * 8;
+    const uint32_t tag = push_tag(push2_epoch);
     for (int idx = tid; idx < per_peer * q->world; idx += nthreads) {
-      const int peer = idx / per_peer, v = idx - peer * per_peer, col = v >> 4, rw = v & 15;
-      const uint32_t bits = __float_as_uint(push_stage[col][rw]);
+      const int peer = idx / per_peer, v = idx - peer * per_peer, col = v >> 3, rp = v & 7;
+      const uint2 word = push_pack(push_stage[col][2 * rp], push_stage[col][2 * rp + 1], tag);
       uint8_t* slot = q->base[peer] + tl_p2p_push_slots_offset(q->max_bytes) +
                       (size_t(push2_half) * tl_ctx::kMaxPeers + q->rank) * q->max_bytes;
-      uint2* dst = reinterpret_cast<uint2*>(slot) + (int64_t(col) * p.n + tile_row) + rw;
+      uint2* dst = reinterpret_cast<uint2*>(slot) + ((int64_t(col) * p.n + tile_row) >> 1) + rp;
       // volatile (relaxed at system scope): a weak store to peer memory may be held back indefinitely
-      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(bits), "r"(push2_epoch) : "memory");
+      asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(dst), "r"(word.x), "r"(word.y) : "memory");
     }
   }
   if (PUSH == 1) {
@@ -3102,8 +3124,8 @@ extern "C" int32_t tl_qgemv_nt_push(tl_ctx* ctx, const void* a, int32_t a_dtype,
       (reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(out) & 15))
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED,
                         "tl_qgemv_nt_push: needs f16/bf16 activations and outputs, K %% 64 == 0, group %% 64 == 0, N %% 16 == 0, 16-byte aligned operands");
-  if (size_t(m) * size_t(n) * 8 > ctx->p2p_max_bytes)  // every f32 partial sum travels with a 4-byte epoch
-    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_push: %zu bytes exceed the exchange buffer (%zu)", size_t(m) * size_t(n) * 8,
+  if (size_t(m) * size_t(n) * 4 > ctx->p2p_max_bytes)  // two 24-bit partial sums and a 16-bit tag per 8-byte word
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_qgemv_nt_push: %zu bytes exceed the exchange buffer (%zu)", size_t(m) * size_t(n) * 4,
                         ctx->p2p_max_bytes);
   EpiParams epi;
   bool has_ops = false;
