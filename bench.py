@@ -280,6 +280,34 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                                                  "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
                                                  "l2": f"rotating over {copies} weight copies (352 MB)"}
     del wd
+    # int4-grouped (G = 128, f16 abs-max scales): half a byte per weight
+    copies4 = 12  # 12 x 29.4 MB = 352 MB
+    w4 = torch.randint(-2 ** 31, 2 ** 31 - 1, (copies4, n, k // 8), dtype=torch.int32, device=dev)
+    s4 = torch.empty(n, k // 128, device=dev).uniform_(0.01, 0.1).to(torch.float16)
+    q4 = B.QuantDesc(B.TL_SCHEME_INT4_GROUPED, 128, B.TL_F16, B.TL_SCALE_SNORM127)
+    for m in (1, 16):
+        x = torch.randn(m, k, device=dev).to(torch.float16)
+        y = torch.empty(m, n, dtype=torch.float16, device=dev)
+
+        def sweep4(reps):
+            for _ in range(reps):
+                for c in range(copies4):
+                    B.check(ctx, lib.tl_qmatmul_nt(ctx, x.data_ptr(), B.TL_F16, w4[c].data_ptr(), s4.data_ptr(), y.data_ptr(), B.TL_F16,
+                                                   m, n, k, C.byref(q4), 1.0, C.byref(e)))
+        sweep4(2)
+        be.sync()
+        reps = 10
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        sweep4(reps)
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        us = ms.value * 1e3 / (reps * copies4)
+        nbytes = n * k // 2 + n * (k // 128) * 2 + n * 4 + m * k * 2 + m * n * 2
+        out[f"int4_gemv_g128_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": nbytes / us / 1e3,
+                                                  "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
+                                                  "l2": f"rotating over {copies4} weight copies (352 MB)"}
+    del w4, s4
     # dense products on the tensor cores (tl_matmul's tcgen05 kernel): the prefill shape in the NT layout
     # `linear` produces, a square NN product (B is transposed into scratch first), and the tiled
     # CUDA-core kernel forced on the same square for reference

@@ -819,3 +819,26 @@ def test_gemv_kernels_unpack_every_byte_in_every_lane(backend, variant, act_dtyp
 @pytest.mark.parametrize("variant", [None, (2, 0, 16, 128, 8, 8), (2, 0, 128, 64, 8, 4), (2, 0, 192, 128, 3, 8)])
 def test_tcgen05_converter_unpacks_every_byte_in_every_lane(backend, variant, act_dtype):
     _one_hot_products(backend, "tl_qgemm_nt", variant, 256, 128, act_dtype)
+
+
+@pytest.mark.parametrize("m", [1, 8, 64])
+def test_gated_mlp_first_half_rides_in_the_epilogue(backend, m):
+    """silu(x Wg^T) * (x Wu^T) with the multiply fused into the gate projection's epilogue
+    (packages/qwen3-browser/src/model.ts:360-364) against the oracle's unfused sequence."""
+    be = backend
+    n, k = 768, 512
+    cg = cases.per_channel_case(n, k, m, seed=61, act_dtype="f16")
+    cu = cases.per_channel_case(n, k, m, seed=62, act_dtype="f16")
+    wg = be.createQuantizedWeight(cg["packed"], cg["scales"], n, k, tb.perChannelFormat(k))
+    wu = be.createQuantizedWeight(cu["packed"], cu["scales"], n, k, tb.perChannelFormat(k))
+    x = be.ops.tensorFromArray(cg["x_bits"], [m, k], "f16")
+    be.resetCounters()
+    h = be.swiglu(x, wg, wu, "f32")
+    launches = be.getKernelLaunchCount()
+    assert launches == 2, launches  # two products, no element-wise kernel
+    g_ref = orc.linear_reference(cg["x"], orc.dequantize_direct_f32(cg["packed"], cg["scales"], k, k), None, "silu")
+    u_ref = orc.linear_reference(cg["x"], orc.dequantize_direct_f32(cu["packed"], cu["scales"], k, k))
+    ref = (g_ref.astype(np.float64) * u_ref.astype(np.float64)).astype(np.float32)
+    assert cases.rel_err(be.ops.read(h), ref) <= 1e-3
+    for t in (h, x, wg.scales, wg, wu.scales, wu):
+        t.destroy()

@@ -632,6 +632,19 @@ class CudaBackend:
             opts["epilogue"], opts["epilogueInputs"], _ = plan
         return self.ops.matmul(x, wT, opts)
 
+    def swiglu(self, x: CudaTensor, gate: CudaTensor, up: CudaTensor, outputDtype: str = "f16") -> CudaTensor:
+        """h = silu(x @ gate^T) * (x @ up^T), the gated MLP's first half
+        (packages/qwen3-browser/src/model.ts:360-364), as two launches with NO element-wise kernel:
+        the up projection stores f32, and the gate projection's epilogue is [silu, mul by that
+        result, cast] -- the multiply rides in the second product's store loop.  Both weights may be
+        packed (either scheme) or dense."""
+        u = self.linear(x, up, None, None, "f32")
+        chain = [("silu", None), ("mul", u)] + ([("cast", outputDtype)] if outputDtype != "f32" else [])
+        plan = detectMatmulEpilogue(chain)
+        h = self.ops.matmul(x, self.ops.transpose(gate), {"epilogue": plan[0], "epilogueInputs": plan[1], "outputDtype": outputDtype})
+        u.destroy()
+        return h
+
     # -- selection / counters / autotune --------------------------------------
     def planQuantizedMatmul(self, m, n, k, aDtype, outDtype, packing: QuantPacking,
                             epilogue: Optional[EpilogueConfig] = None):

@@ -260,16 +260,15 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
 #pragma unroll
     for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
   const int kblocks = p.k >> 7;
-  for (int kb = warp; kb < kblocks; kb += warps) {
-    const uint4 wl4 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
-    const uint4 wh4 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+  // one 128-wide k block: 8 MMAs per batch tile, on two accumulators so that only four are dependent
+  auto block = [&](const uint4& wl4, const uint4& wh4, int kb) {
     const uint32_t wl[4] = {wl4.x ^ 0x88888888u, wl4.y ^ 0x88888888u, wl4.z ^ 0x88888888u, wl4.w ^ 0x88888888u};
     const uint32_t wh[4] = {wh4.x ^ 0x88888888u, wh4.y ^ 0x88888888u, wh4.z ^ 0x88888888u, wh4.w ^ 0x88888888u};
-    float c[NT][4];
+    float c[NT][4], d[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) c[nt][i] = GROUPED ? 0.f : total[nt][i];
+      for (int i = 0; i < 4; ++i) { c[nt][i] = GROUPED ? 0.f : total[nt][i]; d[nt][i] = 0.f; }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const uint32_t a00 = Nib<AT>::pair(wl[j], 0), a01 = Nib<AT>::pair(wh[j], 0), a02 = Nib<AT>::pair(wl[j], 1), a03 = Nib<AT>::pair(wh[j], 1);
@@ -278,7 +277,7 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
       for (int nt = 0; nt < NT; ++nt) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x_row[nt] + int64_t(kb) * 128) + j);  // x0..x7 of this word
         MmaOps<AT>::mma(c[nt], a00, a01, a02, a03, __byte_perm(xv.x, xv.z, 0x5410), __byte_perm(xv.x, xv.z, 0x7632));
-        MmaOps<AT>::mma(c[nt], a10, a11, a12, a13, __byte_perm(xv.y, xv.w, 0x5410), __byte_perm(xv.y, xv.w, 0x7632));
+        MmaOps<AT>::mma(d[nt], a10, a11, a12, a13, __byte_perm(xv.y, xv.w, 0x5410), __byte_perm(xv.y, xv.w, 0x7632));
       }
     }
     if (GROUPED) {
@@ -287,15 +286,31 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
       const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + grp);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        total[nt][0] = fmaf(s_lo, c[nt][0], total[nt][0]); total[nt][1] = fmaf(s_lo, c[nt][1], total[nt][1]);
-        total[nt][2] = fmaf(s_hi, c[nt][2], total[nt][2]); total[nt][3] = fmaf(s_hi, c[nt][3], total[nt][3]);
+        total[nt][0] = fmaf(s_lo, c[nt][0] + d[nt][0], total[nt][0]); total[nt][1] = fmaf(s_lo, c[nt][1] + d[nt][1], total[nt][1]);
+        total[nt][2] = fmaf(s_hi, c[nt][2] + d[nt][2], total[nt][2]); total[nt][3] = fmaf(s_hi, c[nt][3] + d[nt][3], total[nt][3]);
       }
     } else {
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) total[nt][i] = c[nt][i];
+        for (int i = 0; i < 4; ++i) total[nt][i] = c[nt][i] + d[nt][i];
     }
+  };
+  // two blocks' weights are requested before the first is used: with 16 warps a 4096-wide row is
+  // exactly two blocks per warp, so all of a CTA's weight bytes are in flight at once
+  int kb = warp;
+  for (; kb + warps < kblocks; kb += 2 * warps) {
+    const uint4 l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
+    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+    const uint4 l1 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb + warps) * 64));
+    const uint4 h1 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb + warps) * 64));
+    block(l0, h0, kb);
+    block(l1, h1, kb + warps);
+  }
+  if (kb < kblocks) {
+    const uint4 l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
+    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+    block(l0, h0, kb);
   }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)

@@ -5,7 +5,8 @@
 // tiled matmul body + epilogue (src/schedule/matmul-skeleton.ts:738-966) for the NT layout that
 // `linear` produces (other layouts are brought to it by one transposition pass, see tl_matmul).
 //
-//   tile: 128 rows of A (tokens, = TMEM lanes) x BN rows of B (output columns, = TMEM columns),
+//   tile: 128 rows of A (tokens, = TMEM lanes) x BN rows of B (output columns, = TMEM columns; BN is 128,
+//         160, 192, 224 or 256, whichever leaves the fewest idle SMs in the last round),
 //         64 k per pipeline stage (one 128-byte swizzled row per operand row), 4 MMAs of K = 16 per stage;
 //   warp 0: TMA producer (one elected lane); warp 1: TMEM allocation + MMA issue (one elected lane);
 //   warps 2..9: epilogue, two warps per TMEM lane quarter, each taking half of the tile's columns;
@@ -15,6 +16,7 @@
 // Every wait is bounded; a wait that runs out raises the context's status word, all roles drain,
 // TMEM is released and the kernel returns.
 #include <algorithm>
+#include <climits>
 
 #include "tl_common.cuh"
 #include "tl_tcgen05.cuh"
@@ -232,19 +234,22 @@ bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, 
   return true;
 }
 
-// p0 of the receipt: BN (columns per tile); p1: stages.
+// p0 of the receipt: BN (columns per tile); p1: stages.  A tile's time grows with BN (the MMA is the
+// long pole), so the cost of a choice is rounds x BN with rounds = ceil(tiles / SMs): e.g. n = 14336,
+// m = 2048 on 148 SMs is 7 rounds at BN = 256 but also 7 rounds at BN = 224 (6.92 full), 12 % less work.
 void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid) {
   const int64_t m_tiles = (m + kBM - 1) / kBM;
-  // 256-column tiles halve the A traffic per flop; take them unless the narrower tile fills the
-  // machine better (fewer idle SMs in the last wave)
-  auto waste = [&](int b) {
+  int64_t best_cost = INT64_MAX;
+  int best = 128;
+  for (int b : {256, 224, 192, 160, 128}) {
+    if (b > 128 && n < b) continue;
     const int64_t t = m_tiles * ((n + b - 1) / b);
-    const int64_t waves = (t + sms - 1) / sms;
-    return double(waves * sms * b) / double(t * b) * double(((n + b - 1) / b) * b) / double(n);
-  };
-  *bn = (n >= 256 && waste(256) <= waste(128) * 1.08) ? 256 : 128;
-  *stages = *bn == 256 ? 4 : 6;
-  const int64_t t = m_tiles * ((n + *bn - 1) / *bn);
+    const int64_t cost = ((t + sms - 1) / sms) * b;
+    if (cost < best_cost) { best_cost = cost; best = b; }
+  }
+  *bn = best;
+  *stages = best == 256 ? 4 : best >= 192 ? 5 : 6;
+  const int64_t t = m_tiles * ((n + best - 1) / best);
   *grid = int(std::min<int64_t>(sms, t));
 }
 
@@ -263,13 +268,17 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
       !tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3))
     return tl_set_error(ctx, TL_ERR_CUDA, "tl_matmul: cuTensorMapEncodeTiled failed (m=%lld n=%lld k=%lld)", (long long)m,
                         (long long)n, (long long)k);
-  cudaError_t e;
-  if (dtype == TL_F16)
-    e = bn == 256 ? launch_dense<__half, 256, 4>(grid, ctx->stream, amap, bmap, p, epi)
-                  : launch_dense<__half, 128, 6>(grid, ctx->stream, amap, bmap, p, epi);
-  else
-    e = bn == 256 ? launch_dense<__nv_bfloat16, 256, 4>(grid, ctx->stream, amap, bmap, p, epi)
-                  : launch_dense<__nv_bfloat16, 128, 6>(grid, ctx->stream, amap, bmap, p, epi);
+  cudaError_t e = cudaErrorInvalidValue;
+#define TL_DENSE_CASE(BN_, ST_)                                                                              \
+  if (bn == BN_)                                                                                             \
+    e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_>(grid, ctx->stream, amap, bmap, p, epi)              \
+                        : launch_dense<__nv_bfloat16, BN_, ST_>(grid, ctx->stream, amap, bmap, p, epi);
+  TL_DENSE_CASE(256, 4)
+  TL_DENSE_CASE(224, 5)
+  TL_DENSE_CASE(192, 5)
+  TL_DENSE_CASE(160, 6)
+  TL_DENSE_CASE(128, 6)
+#undef TL_DENSE_CASE
   if (e != cudaSuccess) {
     ctx->async_errors++;
     return tl_set_error(ctx, TL_ERR_CUDA, "tl_matmul: tensor-core launch failed: %s", cudaGetErrorString(e));
