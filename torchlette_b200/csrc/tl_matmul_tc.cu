@@ -6,7 +6,7 @@
 // `linear` produces (other layouts are brought to it by one transposition pass, see tl_matmul).
 //
 //   tile: 128 rows of A (tokens, = TMEM lanes) x BN rows of B (output columns, = TMEM columns; BN is 128,
-//         160, 192, 224 or 256, whichever leaves the fewest idle SMs in the last round),
+//         160, 192, 224 or 256, whichever leaves the fewest idle SMs in the last wave),
 //         64 k per pipeline stage (one 128-byte swizzled row per operand row), 4 MMAs of K = 16 per stage;
 //   warp 0: TMA producer (one elected lane); warp 1: TMEM allocation + MMA issue (one elected lane);
 //   warps 2..9: epilogue, two warps per TMEM lane quarter, each taking half of the tile's columns;
@@ -235,8 +235,8 @@ bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, 
 }
 
 // p0 of the receipt: BN (columns per tile); p1: stages.  A tile's time grows with BN (the MMA is the
-// long pole), so the cost of a choice is rounds x BN with rounds = ceil(tiles / SMs): e.g. n = 14336,
-// m = 2048 on 148 SMs is 7 rounds at BN = 256 but also 7 rounds at BN = 224 (6.92 full), 12 % less work.
+// long pole), so the cost of a choice is waves x BN with waves = ceil(tiles / SMs): e.g. n = 14336,
+// m = 2048 on 148 SMs is 7 waves at BN = 256 but also 7 waves at BN = 224 (6.92 full), 12 % less work.
 void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid) {
   const int64_t m_tiles = (m + kBM - 1) / kBM;
   int64_t best_cost = INT64_MAX;
