@@ -563,6 +563,8 @@ def run_gpu(args):
                 args.allreduce = "nccl (peer buffers could not be mapped)"
             dist.barrier()
 
+    if args.push_poll_ranks:
+        be.setOption("push_poll_ranks", args.push_poll_ranks)
     cfg = StackConfig(**{**QWEN3_8B.__dict__, "batch": args.batch})
     stack = DecodeStack(be, cfg, rank, world, args.tp_mode, allreduce=args.allreduce if (world > 1 and args.allreduce in ("p2p", "fused", "push")) else "nccl",
                         fuse=not args.no_fuse, chain=args.step_launch == "chain")
@@ -771,6 +773,7 @@ def main():
                          "launch reduces them on read (no collective launch; default, fastest measured at 2, 4 and 8 GPUs); "
                          "p2p = the library's one-shot peer-memory all-reduce kernel; fused = the GEMV fused with its "
                          "all-reduce (tl_qgemv_nt_allreduce); nccl")
+    ap.add_argument("--push-poll-ranks", type=int, default=0, help="reduce-on-read: ranks polled together (1..4; 0 = the library's default)")
     ap.add_argument("--step-launch", default="graph", choices=["chain", "graph"],
                     help="graph: a replayed CUDA graph of per-projection launches (the measured-faster default); "
                          "chain: the whole step as one persistent cooperative launch (one GPU, batch <= 16)")

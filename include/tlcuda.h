@@ -119,7 +119,10 @@ TL_API int32_t tl_device_sm_count(tl_ctx* ctx, int32_t* out_sms);
  * (src/core/env.ts:14-26).  Unknown names return TL_ERR_INVALID_ARG.
  *   "wait_limit_polls"       upper bound of the polls of one bounded device-side wait of the
  *                            peer collectives (default 2^26; the fused GEMV + all-reduce caps it
- *                            at 2^22). */
+ *                            at 2^22).
+ *   "push_poll_ranks"        reduce-on-read (tl_qgemv_nt_push's consumer): how many ranks' words a
+ *                            summing thread requests together before it checks them, 1..4
+ *                            (default 4; 1 polls the ranks one after the other). */
 TL_API int32_t tl_set_option(tl_ctx* ctx, const char* name, int64_t value);
 TL_API int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value);
 

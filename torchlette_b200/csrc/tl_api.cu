@@ -180,6 +180,9 @@ int32_t tl_set_option(tl_ctx* ctx, const char* name, int64_t value) {
     if (value < 1 || value > (int64_t(1) << 30))
       return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: wait_limit_polls outside [1, 2^30]");
     ctx->wait_limit_polls = int(value);
+  } else if (!strcmp(name, "push_poll_ranks")) {
+    if (value < 1 || value > 4) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: push_poll_ranks outside [1, 4]");
+    ctx->push_poll_ranks = int(value);
   } else {
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_set_option: unknown option '%s'", name);
   }
@@ -190,6 +193,7 @@ int32_t tl_get_option(tl_ctx* ctx, const char* name, int64_t* out_value) {
   TL_CHECK_CTX(ctx);
   if (!name || !out_value) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: null argument");
   if (!strcmp(name, "wait_limit_polls")) *out_value = ctx->wait_limit_polls;
+  else if (!strcmp(name, "push_poll_ranks")) *out_value = ctx->push_poll_ranks;
   else if (!strcmp(name, "p2p_buffer_address")) *out_value = int64_t(reinterpret_cast<uintptr_t>(ctx->p2p_local));
   else if (!strcmp(name, "p2p_slot_bytes")) *out_value = int64_t(ctx->p2p_max_bytes);
   else return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_get_option: unknown option '%s'", name);

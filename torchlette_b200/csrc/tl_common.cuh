@@ -65,6 +65,7 @@ struct tl_ctx {
   int pf_last_grid = 0;
   void* stream_scratch = nullptr;
   int wait_limit_polls = 1 << 26;  // bound of one device-side wait of the peer collectives
+  int push_poll_ranks = 4;         // reduce-on-read: ranks polled together (1 = one after the other)
   // selection
   bool has_forced = false;
   tl_variant forced{};

@@ -663,6 +663,7 @@ struct ReduceIn {
   int32_t dtype;        // TL_F16 or TL_BF16
   int* status;
   int32_t spin_limit;
+  int32_t poll_ranks;   // ranks whose words are requested together (1..4; the context's push_poll_ranks)
 };
 __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
   uint32_t v;
@@ -685,24 +686,43 @@ __device__ __forceinline__ void reduce_in_prologue(const ReduceIn& r) {
         // output vector i = 8 values = four {two partial sums, tag} words (32 bytes) of every rank's slot
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         const uint32_t tag = push_tag(epoch);
-        for (int rr = 0; rr < r.world; ++rr) {
-          const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(rr) * r.max_bytes) + 2 * i;
-          uint4 u0, u1;
+        // four ranks' words are requested together (eight 16-byte loads in flight), then checked: polling
+        // the ranks one after the other costs an L2 round trip per rank, 5 us per exchange at 8 ranks
+        for (int r0 = 0; r0 < r.world; r0 += r.poll_ranks) {
+          const int nb = min(r.poll_ranks, r.world - r0);
+          uint4 u[4][2];
           int spins = 0;
           for (;;) {
-            u0 = __ldcv(src);
-            u1 = __ldcv(src + 1);
-            if ((u0.y & 0xffffu) == tag && (u0.w & 0xffffu) == tag && (u1.y & 0xffffu) == tag && (u1.w & 0xffffu) == tag) break;
+            bool all = true;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (j < nb) {
+                const uint4* src = reinterpret_cast<const uint4*>(slots + size_t(r0 + j) * r.max_bytes) + 2 * i;
+                u[j][0] = __ldcv(src);
+                u[j][1] = __ldcv(src + 1);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              if (j < nb)
+                all = all && (u[j][0].y & 0xffffu) == tag && (u[j][0].w & 0xffffu) == tag && (u[j][1].y & 0xffffu) == tag &&
+                      (u[j][1].w & 0xffffu) == tag;
+            if (all) break;
             if (++spins > r.spin_limit) { atomicExch(r.status, TL_ERR_TIMEOUT); break; }
             __nanosleep(200);  // thousands of threads poll lines that a peer is writing: leave the L2 slice room
           }
-          float v[8];
-          push_unpack(u0.x, u0.y, v[0], v[1]);
-          push_unpack(u0.z, u0.w, v[2], v[3]);
-          push_unpack(u1.x, u1.y, v[4], v[5]);
-          push_unpack(u1.z, u1.w, v[6], v[7]);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += v[j];
+          for (int j = 0; j < 4; ++j) {  // rank order: every rank computes the same bits
+            if (j < nb) {
+              float v[8];
+              push_unpack(u[j][0].x, u[j][0].y, v[0], v[1]);
+              push_unpack(u[j][0].z, u[j][0].w, v[2], v[3]);
+              push_unpack(u[j][1].x, u[j][1].y, v[4], v[5]);
+              push_unpack(u[j][1].z, u[j][1].w, v[6], v[7]);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) acc[e] += v[e];
+            }
+          }
         }
         uint32_t o[4];
 #pragma unroll
@@ -3045,7 +3065,7 @@ cudaError_t launch_push(tl_ctx* ctx, bool two, bool grouped, int grid, const Gem
 }
 template <typename AT>
 cudaError_t launch_rin(tl_ctx* ctx, bool two, bool grouped, int grid, const GemvArgs& p, const EpiParams& e, ReduceIn r) {
-  r.nsum = std::min(grid, 16);
+  r.nsum = std::min(grid, 32);
   if (two) {
     if (grouped) TL_TP_GO((qgemv_ring_rin_kernel<AT, 2, true, kTpStages>), 2, p, e, r);
     TL_TP_GO((qgemv_ring_rin_kernel<AT, 2, false, kTpStages>), 2, p, e, r);
@@ -3055,7 +3075,7 @@ cudaError_t launch_rin(tl_ctx* ctx, bool two, bool grouped, int grid, const Gemv
 }
 template <typename AT>
 cudaError_t launch_rin_batched(tl_ctx* ctx, bool two, bool grouped, int grid, const RingBatchArgs& b, ReduceIn r) {
-  r.nsum = std::min(grid, 16);
+  r.nsum = std::min(grid, 32);
   if (two) {
     if (grouped) TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 2, true, kTpStages>), 2, b, r);
     TL_TP_GO((qgemv_ring_rin_batched_kernel<AT, 2, false, kTpStages>), 2, b, r);
@@ -3093,11 +3113,12 @@ ReduceIn make_reduce_in(tl_ctx* ctx, void* dst, int grid) {
   r.dst = dst;
   r.world = ctx->world;
   r.expected = 0;
-  r.nsum = std::min(grid, 16);
+  r.nsum = std::min(grid, 32);
   r.count_vec = int32_t(int64_t(ctx->push_m) * ctx->push_n * 2 / 16);
   r.dtype = ctx->push_dtype;
   r.status = ctx->dev_status;
   r.spin_limit = ctx->wait_limit_polls;
+  r.poll_ranks = ctx->push_poll_ranks;
   return r;
 }
 }  // namespace
