@@ -275,6 +275,31 @@ TL_API int32_t tl_binary_op(tl_ctx* ctx, int32_t op, const void* a, int32_t a_dt
 TL_API int32_t tl_transpose2d(tl_ctx* ctx, const void* in, void* out, int64_t batch, int64_t rows,
                               int64_t cols, int32_t elem_bytes);
 
+/* ---- the other ops of one decode step (packages/qwen3-browser/src/model.ts:220-420), so that a step
+ * runs on this backend end to end.  f32 arithmetic; storage f32 / f16 / bf16.
+ * tl_rmsnorm: out[r,c] = x[r,c] * rsqrt(mean_c(x[r,:]^2) + eps) * weight[c]
+ *   (src/ops/semantic/composite.ts:156-170; rows x cols, also the per-head q / k norm with cols = headDim).
+ * tl_rope: the half-split rotation of fusedRoPE (src/backend/webgpu/rope-kernel.ts:1-93,
+ *   src/backend/types.ts:593-598): qk is [outer, seq_len, head_dim], cos / sin are f32 [.., head_dim/2]
+ *   tables read at row s from the given element offsets (a narrow() view of a persistent table);
+ *   first half  out[d] = qk[d] cos - qk[d + D/2] sin, second half out[d] = qk[d] cos + qk[d - D/2] sin;
+ *   sin_scale -1 is the inverse rotation.  Not in place.
+ * tl_decode_attention: one query token per sequence against a KV cache (model.ts:292-312): q is
+ *   [batch, n_heads, head_dim], the caches are [batch, n_kv_heads, kv_capacity, head_dim] of which the
+ *   first kv_len positions are read; query head h reads kv head h / (n_heads / n_kv_heads) (the order of
+ *   expandKV, model.ts:171-180); out[b,h,:] = softmax_j(q . k_j * scale + mask[j]) . v; mask is f32
+ *   [kv_len] or NULL.  kv_len <= 51200 per launch.  (Appending this step's k / v at a position is
+ *   tl_copy2d; the residual adds are tl_binary_op; silu(gate) * up rides in an epilogue.) */
+TL_API int32_t tl_rmsnorm(tl_ctx* ctx, const void* x, int32_t x_dtype, const void* weight, int32_t weight_dtype,
+                          void* out, int32_t out_dtype, int64_t rows, int64_t cols, float eps);
+TL_API int32_t tl_rope(tl_ctx* ctx, const void* qk, int32_t dtype, const float* cos_table, const float* sin_table,
+                       void* out, int64_t outer, int64_t seq_len, int64_t head_dim, float sin_scale,
+                       int64_t cos_offset, int64_t sin_offset);
+TL_API int32_t tl_decode_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out,
+                                   int32_t dtype, int64_t batch, int64_t n_heads, int64_t n_kv_heads,
+                                   int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,
+                                   const float* mask);
+
 /* ---- selection: planTiledMatmul / selectMatmulChoice / SelectionReceipt
  * (src/backend/webgpu/matmul/dispatch.ts:171-192, 1130-1329;
  *  src/backend/webgpu/matmul/variants.ts:54-260) ------------------------------ */

@@ -14,7 +14,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(CSRC, "libtlcuda.so")
-SOURCES = ["tl_api.cu", "tl_quantize.cu", "tl_qgemv.cu", "tl_qgemv_stream.cu", "tl_qgemm.cu", "tl_matmul.cu", "tl_matmul_tc.cu", "tl_elementwise.cu", "tl_int4.cu", "tl_autotune.cu", "tl_comm.cu"]
+SOURCES = ["tl_api.cu", "tl_quantize.cu", "tl_qgemv.cu", "tl_qgemv_stream.cu", "tl_qgemm.cu", "tl_matmul.cu", "tl_matmul_tc.cu", "tl_elementwise.cu", "tl_decode_ops.cu", "tl_int4.cu", "tl_autotune.cu", "tl_comm.cu"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -194,6 +194,12 @@ class CudaOps:
             host = host.view(np.float16)
         return host.reshape(t.shape)
 
+    def reshape(self, t: CudaTensor, shape) -> CudaTensor:
+        """A view of a contiguous tensor under another shape (no copy; the buffer stays the owner's)."""
+        if t.transposed or int(np.prod(shape)) != int(np.prod(t.shape)):
+            raise ValueError("reshape: needs a contiguous tensor and the same element count")
+        return CudaTensor(self._b, list(shape), t.dtype, t.buffer, t.nbytes, ownsBuffer=False, format=t.format, scales=t.scales)
+
     def transpose(self, t: CudaTensor, dim0: int = -2, dim1: int = -1) -> CudaTensor:
         nd = len(t.shape)
         if nd < 2 or {dim0 % nd, dim1 % nd} != {nd - 2, nd - 1}:
@@ -252,6 +258,48 @@ class CudaOps:
         rows, cols = t.shape[-1], t.shape[-2]  # of the stored buffer
         B.check(self._b._ctx, self._b._lib.tl_transpose2d(self._b._ctx, t.buffer, out.buffer, 1, rows, cols, itemsize))
         return out
+
+    # -- the other ops of a decode step (packages/qwen3-browser/src/model.ts:220-420) ----------
+    def rmsnorm(self, x: CudaTensor, weight: CudaTensor, eps: float = 1e-5, outputDtype: Optional[str] = None) -> CudaTensor:
+        """x * rsqrt(mean(x^2) + eps) * weight over the last dim (src/frontend/tensor.ts:363-367)."""
+        cols = x.shape[-1]
+        if list(weight.shape) != [cols]:
+            raise TlError(B.TL_ERR_INVALID_ARG, "rmsnorm: weight must be [lastDim]")
+        rows = int(np.prod(x.shape[:-1])) if len(x.shape) > 1 else 1
+        out = self.empty(x.shape, outputDtype or x.dtype)
+        B.check(self._b._ctx, self._b._lib.tl_rmsnorm(self._b._ctx, x.buffer, B.DTYPE_ID[x.dtype], weight.buffer, B.DTYPE_ID[weight.dtype],
+                                                      out.buffer, B.DTYPE_ID[out.dtype], rows, cols, float(eps)))
+        return out
+
+    def fusedRoPE(self, qk: CudaTensor, cos: CudaTensor, sin: CudaTensor, config: Optional[dict] = None) -> CudaTensor:
+        """fusedRoPE (src/backend/types.ts:593-598): qk [*, S, D], cos / sin f32 [S, D/2]; config may carry
+        sinScale (-1: the inverse rotation), cosOffset / sinOffset (element offsets into larger tables)."""
+        config = config or {}
+        seq, hd = qk.shape[-2], qk.shape[-1]
+        outer = int(np.prod(qk.shape[:-2])) if len(qk.shape) > 2 else 1
+        if cos.dtype != "f32" or sin.dtype != "f32":
+            raise TlError(B.TL_ERR_UNSUPPORTED, "fusedRoPE: cos / sin tables are f32")
+        out = self.empty(qk.shape, qk.dtype)
+        B.check(self._b._ctx, self._b._lib.tl_rope(self._b._ctx, qk.buffer, B.DTYPE_ID[qk.dtype], cos.buffer, sin.buffer, out.buffer, outer, seq, hd,
+                                                   float(config.get("sinScale", 1.0)), int(config.get("cosOffset", 0)), int(config.get("sinOffset", 0))))
+        return out
+
+    def decodeAttention(self, q: CudaTensor, kCache: CudaTensor, vCache: CudaTensor, kvLen: int, scale: float,
+                        mask: Optional[CudaTensor] = None) -> CudaTensor:
+        """softmax(q k^T * scale + mask) v for one query token per sequence (model.ts:292-312): q [B, H, 1, D]
+        (or [B, H, D]), caches [B, kvH, capacity, D]; returns [B, 1, H * D], the layout o_proj reads."""
+        b, h, d = q.shape[0], q.shape[1], q.shape[-1]
+        kvh, cap = kCache.shape[1], kCache.shape[2]
+        out = self.empty([b, 1, h * d], q.dtype)
+        B.check(self._b._ctx, self._b._lib.tl_decode_attention(self._b._ctx, q.buffer, kCache.buffer, vCache.buffer, out.buffer, B.DTYPE_ID[q.dtype], b, h,
+                                                               kvh, d, kvLen, cap, float(scale), mask.buffer if mask is not None else None))
+        return out
+
+    def kvAppend(self, cache: CudaTensor, new: CudaTensor, position: int):
+        """cache[:, :, position, :] = new ([B, kvH, 1, D] or [B, kvH, D]): one strided copy (model.ts:240-262)."""
+        b, kvh, cap, d = cache.shape
+        esz = np.dtype(_NP_OF[cache.dtype]).itemsize
+        B.check(self._b._ctx, self._b._lib.tl_copy2d(self._b._ctx, cache.buffer + position * d * esz, cap * d * esz, new.buffer, d * esz, d * esz, b * kvh))
 
     def matmul(self, a: CudaTensor, b: CudaTensor, options: Optional[dict] = None) -> CudaTensor:
         """Backend matmul; the storage-format seam (matmul-ops.ts:42-59)."""

@@ -546,6 +546,26 @@ FN(BinaryOp) {
 /* transpose2d(ctx, in, out, batch, rows, cols, elemBytes) */
 FN(Transpose2d) { ARGS(7); CTX(0); return check(env, c, tl_transpose2d(c, dptr(env, argv[1]), dptr(env, argv[2]), i64(env, argv[3]), i64(env, argv[4]), i64(env, argv[5]), i32(env, argv[6]))); }
 
+/* rmsnorm(ctx, x, xDtype, weight, weightDtype, out, outDtype, rows, cols, eps) */
+FN(Rmsnorm) {
+  ARGS(10); CTX(0);
+  return check(env, c, tl_rmsnorm(c, dptr(env, argv[1]), i32(env, argv[2]), dptr(env, argv[3]), i32(env, argv[4]), dptr(env, argv[5]), i32(env, argv[6]),
+                                  i64(env, argv[7]), i64(env, argv[8]), (float)f64(env, argv[9])));
+}
+/* rope(ctx, qk, dtype, cos, sin, out, outer, seqLen, headDim, sinScale, cosOffset, sinOffset) */
+FN(Rope) {
+  ARGS(12); CTX(0);
+  return check(env, c, tl_rope(c, dptr(env, argv[1]), i32(env, argv[2]), (const float*)dptr(env, argv[3]), (const float*)dptr(env, argv[4]), dptr(env, argv[5]),
+                               i64(env, argv[6]), i64(env, argv[7]), i64(env, argv[8]), (float)f64(env, argv[9]), i64(env, argv[10]), i64(env, argv[11])));
+}
+/* decodeAttention(ctx, q, kCache, vCache, out, dtype, batch, heads, kvHeads, headDim, kvLen, kvCapacity, scale, mask | null) */
+FN(DecodeAttention) {
+  ARGS(14); CTX(0);
+  return check(env, c, tl_decode_attention(c, dptr(env, argv[1]), dptr(env, argv[2]), dptr(env, argv[3]), dptr(env, argv[4]), i32(env, argv[5]), i64(env, argv[6]),
+                                           i64(env, argv[7]), i64(env, argv[8]), i64(env, argv[9]), i64(env, argv[10]), i64(env, argv[11]),
+                                           (float)f64(env, argv[12]), (const float*)dptr(env, argv[13])));
+}
+
 /* ---- dense matmul ---------------------------------------------------------------
  * matmul(ctx, a, b, out, m, n, k, batch, strideA, strideB, strideC, transA, transB, alpha, dtypeA, dtypeB, outDtype,
  *        castA, castB, epilogue?, planOnly) -> undefined, or the receipt (Int32Array) when planOnly */
@@ -692,6 +712,7 @@ napi_value napi_register_module_v1(napi_env env, napi_value exports) {
       EXPORT("qgemvNtStaticScratch", QgemvNtStaticScratch), EXPORT("qgemmNt", QgemmNt), EXPORT("qmatmulNt", QmatmulNt),
       EXPORT("dequantInt8", DequantInt8), EXPORT("unpackInt8", UnpackInt8), EXPORT("quantizeLinearWeightInt4", QuantizeLinearWeightInt4),
       EXPORT("dequantInt4", DequantInt4), EXPORT("unpackInt4", UnpackInt4), EXPORT("matmul", Matmul),
+      EXPORT("rmsnorm", Rmsnorm), EXPORT("rope", Rope), EXPORT("decodeAttention", DecodeAttention),
       EXPORT("unaryOp", UnaryOp), EXPORT("binaryOp", BinaryOp), EXPORT("transpose2d", Transpose2d),
       EXPORT("planQmatmul", PlanQmatmul), EXPORT("variantName", VariantName), EXPORT("forceVariant", ForceVariant),
       EXPORT("classifyShape", ClassifyShape), EXPORT("shapeClassName", ShapeClassName),

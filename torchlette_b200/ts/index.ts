@@ -171,6 +171,34 @@ export function contiguous(t: CudaTensor): CudaTensor {
   return out;
 }
 
+// ---- the other ops of a decode step (packages/qwen3-browser/src/model.ts:220-420) ------------
+/** rmsnorm (src/frontend/tensor.ts:363-367): x * rsqrt(mean(x^2) + eps) * weight over the last dim. */
+export function rmsnorm(x: CudaTensor, weight: CudaTensor, eps = 1e-5): CudaTensor {
+  const cols = x.shape[x.shape.length - 1];
+  const out = empty(x.shape, x.dtype as string);
+  addon.rmsnorm(need(), x.buffer, DTYPE_ID[x.dtype as string], weight.buffer, DTYPE_ID[weight.dtype as string], out.buffer,
+                DTYPE_ID[out.dtype as string], numel(x.shape) / cols, cols, eps);
+  return out;
+}
+/** fusedRoPE (src/backend/types.ts:593-598; kernel semantics src/backend/webgpu/rope-kernel.ts:1-93). */
+export function fusedRoPE(qk: CudaTensor, cos: CudaTensor, sin: CudaTensor,
+                          config: { seqLen: number; headDim: number; sinScale?: number; cosOffset?: number; sinOffset?: number }): CudaTensor {
+  const out = empty(qk.shape, qk.dtype as string);
+  addon.rope(need(), qk.buffer, DTYPE_ID[qk.dtype as string], cos.buffer, sin.buffer, out.buffer,
+             numel(qk.shape) / (config.seqLen * config.headDim), config.seqLen, config.headDim, config.sinScale ?? 1, config.cosOffset ?? 0,
+             config.sinOffset ?? 0);
+  return out;
+}
+/** One query token per sequence against a KV cache (model.ts:292-312): q [B,H,1,D], caches [B,kvH,cap,D]. */
+export function decodeAttention(q: CudaTensor, kCache: CudaTensor, vCache: CudaTensor, kvLen: number, scale: number,
+                                mask?: CudaTensor): CudaTensor {
+  const [b, h] = q.shape, d = q.shape[q.shape.length - 1];
+  const out = empty([b, 1, h * d], q.dtype as string);
+  addon.decodeAttention(need(), q.buffer, kCache.buffer, vCache.buffer, out.buffer, DTYPE_ID[q.dtype as string], b, h, kCache.shape[1], d, kvLen,
+                        kCache.shape[2], scale, mask ? mask.buffer : null);
+  return out;
+}
+
 /** createQuantizedWeight (engine.ts:2041-2149): validate, upload, attach format + scales. */
 export function createQuantizedWeight(packed: Uint32Array, scalesBits: Uint16Array | Float32Array, n: number, k: number,
                                       format: StorageFormat & { scaleConvention?: "snorm127" | "direct" }): CudaTensor {
@@ -383,6 +411,8 @@ const ops: Partial<BackendOps> = {
   tanh: ((t: BackendTensor) => tanh(t as CudaTensor)) as any,
   gelu: ((t: BackendTensor, o?: any) => gelu(t as CudaTensor, o)) as any,
   cast: ((t: BackendTensor, dtype: string) => cast(t as CudaTensor, dtype)) as any,
+  fusedRoPE: ((qk: BackendTensor, cos: BackendTensor, sin: BackendTensor, config: any) =>
+    fusedRoPE(qk as CudaTensor, cos as CudaTensor, sin as CudaTensor, config)) as any,
   // the storage-format seam (matmul-ops.ts:42-59): a packed B goes to the fused-dequant kernels
   matmul: ((a: BackendTensor, b: BackendTensor, options?: { outBuffer?: any }) =>
     dispatchMatmul(a as CudaTensor, b as CudaTensor, false, false, options?.outBuffer)) as any,
