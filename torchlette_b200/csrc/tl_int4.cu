@@ -216,26 +216,45 @@ void launch_int4_m(tl_ctx* ctx, Int4Args p, const EpiParams& epi, int m) {
 // Tensor-core form (f16 / bf16 activations, K % 128 == 0, group % 128 == 0): CTA per 16 weight rows,
 // warps interleaved over 128-wide k blocks.  Lane (g, t) loads 16 bytes = 32 nibbles of rows g and
 // g + 8 and the matching 32 activations of batch row g.  (w ^ 0x88888888) turns every nibble into
-// q + 8; ((u >> 4x) & 0x000F000F) | magic is the pair (q_x + 8, q_{x+4} + 8) as 16-bit floats
-// 1024 + . (f16) or 128 + . (bf16), one subtraction gives (q_x, q_{x+4}) exactly.  A word of eight
+// q + 8; a mask and a magic exponent make the pair (q_x + 8, q_{x+4} + 8) 16-bit floats 1024 + .
+// (f16) or 128 + . (bf16), and one subtraction -- or, for the nibbles taken at bits 4-7, one fused
+// multiply-add -- gives (q_x, q_{x+4}) exactly (Nib::quad).  A word of eight
 // nibbles feeds two mma.sync.m16n8k16; the activations are paired the same way with two byte
 // permutes per MMA.  One group per k block: the block's accumulators are folded into the totals
 // with the rows' scales (per-channel scales once at the end).
 // ---------------------------------------------------------------------------
+// quad(u, v): the four MMA operand registers of one word u (nibbles already q + 8):
+//   v[0] = (q0, q4), v[1] = (q1, q5), v[2] = (q2, q6), v[3] = (q3, q7)
 template <typename AT> struct Nib;
 template <> struct Nib<__half> {
-  __device__ static uint32_t pair(uint32_t u, int x) {
-    const uint32_t v = ((u >> (4 * x)) & 0x000F000Fu) | 0x64006400u;
-    const __half2 r = __hsub2(*reinterpret_cast<const __half2*>(&v), __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408)));
-    return *reinterpret_cast<const uint32_t*>(&r);
+  // ONE shift per word: nibbles at bits 0-3 give 1024 + n, nibbles at bits 4-7 give 1024 + 16 n, which
+  // one fused multiply-add turns into n - 8 exactly ((1024 + 16 n) / 16 - 72); the upper half of the
+  // word goes through the same two masks after a shift by 8.
+  __device__ static void quad(uint32_t u, uint32_t (&v)[4]) {
+    const __half2 k1032 = __halves2half2(__ushort_as_half(0x6408), __ushort_as_half(0x6408));
+    const __half2 k16th = __halves2half2(__ushort_as_half(0x2C00), __ushort_as_half(0x2C00));   // 1/16
+    const __half2 km72 = __halves2half2(__ushort_as_half(0xD480), __ushort_as_half(0xD480));    // -72
+    const uint32_t u8 = u >> 8;
+    const uint32_t a = (u & 0x000F000Fu) | 0x64006400u, b = (u & 0x00F000F0u) | 0x64006400u;
+    const uint32_t c = (u8 & 0x000F000Fu) | 0x64006400u, d = (u8 & 0x00F000F0u) | 0x64006400u;
+    const __half2 r0 = __hsub2(*reinterpret_cast<const __half2*>(&a), k1032);
+    const __half2 r1 = __hfma2(*reinterpret_cast<const __half2*>(&b), k16th, km72);
+    const __half2 r2 = __hsub2(*reinterpret_cast<const __half2*>(&c), k1032);
+    const __half2 r3 = __hfma2(*reinterpret_cast<const __half2*>(&d), k16th, km72);
+    v[0] = *reinterpret_cast<const uint32_t*>(&r0); v[1] = *reinterpret_cast<const uint32_t*>(&r1);
+    v[2] = *reinterpret_cast<const uint32_t*>(&r2); v[3] = *reinterpret_cast<const uint32_t*>(&r3);
   }
 };
 template <> struct Nib<__nv_bfloat16> {
-  __device__ static uint32_t pair(uint32_t u, int x) {
-    const uint32_t v = ((u >> (4 * x)) & 0x000F000Fu) | 0x43004300u;
+  // seven mantissa bits hold 128 + n only for a nibble at bits 0-3: one shift per pair
+  __device__ static void quad(uint32_t u, uint32_t (&v)[4]) {
     const uint32_t m = 0x43084308u;  // 136 | 136
-    const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&m));
-    return *reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const uint32_t w = ((u >> (4 * x)) & 0x000F000Fu) | 0x43004300u;
+      const __nv_bfloat162 r = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&w), *reinterpret_cast<const __nv_bfloat162*>(&m));
+      v[x] = *reinterpret_cast<const uint32_t*>(&r);
+    }
   }
 };
 
@@ -261,7 +280,7 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
     for (int i = 0; i < 4; ++i) total[nt][i] = 0.f;
   const int kblocks = p.k >> 7;
   // one 128-wide k block: 8 MMAs per batch tile, on two accumulators so that only four are dependent
-  auto block = [&](const uint4& wl4, const uint4& wh4, int kb) {
+  auto block = [&](const uint4& wl4, const uint4& wh4, float s_lo, float s_hi, int kb) {
     const uint32_t wl[4] = {wl4.x ^ 0x88888888u, wl4.y ^ 0x88888888u, wl4.z ^ 0x88888888u, wl4.w ^ 0x88888888u};
     const uint32_t wh[4] = {wh4.x ^ 0x88888888u, wh4.y ^ 0x88888888u, wh4.z ^ 0x88888888u, wh4.w ^ 0x88888888u};
     float c[NT][4], d[NT][4];
@@ -271,8 +290,11 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
       for (int i = 0; i < 4; ++i) { c[nt][i] = GROUPED ? 0.f : total[nt][i]; d[nt][i] = 0.f; }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t a00 = Nib<AT>::pair(wl[j], 0), a01 = Nib<AT>::pair(wh[j], 0), a02 = Nib<AT>::pair(wl[j], 1), a03 = Nib<AT>::pair(wh[j], 1);
-      const uint32_t a10 = Nib<AT>::pair(wl[j], 2), a11 = Nib<AT>::pair(wh[j], 2), a12 = Nib<AT>::pair(wl[j], 3), a13 = Nib<AT>::pair(wh[j], 3);
+      uint32_t lo[4], hi[4];
+      Nib<AT>::quad(wl[j], lo);
+      Nib<AT>::quad(wh[j], hi);
+      const uint32_t a00 = lo[0], a01 = hi[0], a02 = lo[1], a03 = hi[1];
+      const uint32_t a10 = lo[2], a11 = hi[2], a12 = lo[3], a13 = hi[3];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const uint4 xv = __ldg(reinterpret_cast<const uint4*>(x_row[nt] + int64_t(kb) * 128) + j);  // x0..x7 of this word
@@ -281,9 +303,6 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
       }
     }
     if (GROUPED) {
-      const int grp = (kb * 128) / p.group;
-      const float s_lo = tl_load_scale(p.scales, p.scales_dtype, r_lo * p.groups_per_row + grp);
-      const float s_hi = tl_load_scale(p.scales, p.scales_dtype, r_hi * p.groups_per_row + grp);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         total[nt][0] = fmaf(s_lo, c[nt][0] + d[nt][0], total[nt][0]); total[nt][1] = fmaf(s_lo, c[nt][1] + d[nt][1], total[nt][1]);
@@ -296,21 +315,51 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
         for (int i = 0; i < 4; ++i) total[nt][i] = c[nt][i] + d[nt][i];
     }
   };
-  // two blocks' weights are requested before the first is used: with 16 warps a 4096-wide row is
-  // exactly two blocks per warp, so all of a CTA's weight bytes are in flight at once
+  // Two blocks' weights (and their scales) are always in flight.  (Programmatic dependent launch with
+  // the first loads ahead of griddepcontrol.wait measured slightly slower here, 17.8 against 16.6 us.)
+  // the rows' group scales of a block travel with its weights (loaded in the loop they cost an
+  // exposed L2 / DRAM round trip per block: the scale array is read once, like the weights)
+  const int shift = 31 - __clz(p.group >> 7);  // group = 128 << shift when GROUPED takes this kernel's power-of-two path
+  const bool pow2 = (p.group & (p.group - 1)) == 0;
+  auto scale_of = [&](int64_t row, int kblk) -> float {
+    if (!GROUPED) return 1.f;
+    const int grp = pow2 ? (kblk >> shift) : (kblk * 128) / p.group;
+    return tl_load_scale(p.scales, p.scales_dtype, row * p.groups_per_row + grp);
+  };
   int kb = warp;
-  for (; kb + warps < kblocks; kb += 2 * warps) {
-    const uint4 l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
-    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
-    const uint4 l1 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb + warps) * 64));
-    const uint4 h1 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb + warps) * 64));
-    block(l0, h0, kb);
-    block(l1, h1, kb + warps);
+  bool have0 = kb < kblocks, have1 = kb + warps < kblocks;
+  uint4 l0 = make_uint4(0, 0, 0, 0), h0 = l0, l1 = l0, h1 = l0;
+  float sl0 = 0.f, sh0 = 0.f, sl1 = 0.f, sh1 = 0.f;
+  if (have0) {
+    l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
+    h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+    sl0 = scale_of(r_lo, kb); sh0 = scale_of(r_hi, kb);
   }
-  if (kb < kblocks) {
-    const uint4 l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
-    const uint4 h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
-    block(l0, h0, kb);
+  if (have1) {
+    l1 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb + warps) * 64));
+    h1 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb + warps) * 64));
+    sl1 = scale_of(r_lo, kb + warps); sh1 = scale_of(r_hi, kb + warps);
+  }
+  while (have0) {
+    const uint4 cl0 = l0, ch0 = h0, cl1 = l1, ch1 = h1;
+    const float csl0 = sl0, csh0 = sh0, csl1 = sl1, csh1 = sh1;
+    const int kb0 = kb;
+    const bool run1 = have1;
+    kb += 2 * warps;
+    have0 = kb < kblocks;
+    have1 = kb + warps < kblocks;
+    if (have0) {
+      l0 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb) * 64));
+      h0 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb) * 64));
+      sl0 = scale_of(r_lo, kb); sh0 = scale_of(r_hi, kb);
+    }
+    if (have1) {
+      l1 = __ldg(reinterpret_cast<const uint4*>(w_lo + int64_t(kb + warps) * 64));
+      h1 = __ldg(reinterpret_cast<const uint4*>(w_hi + int64_t(kb + warps) * 64));
+      sl1 = scale_of(r_lo, kb + warps); sh1 = scale_of(r_hi, kb + warps);
+    }
+    block(cl0, ch0, csl0, csh0, kb0);
+    if (run1) block(cl1, ch1, csl1, csh1, kb0 + warps);
   }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
@@ -335,7 +384,11 @@ __global__ void __launch_bounds__(512) qgemv_int4_mma_kernel(Int4Args p, EpiPara
 template <typename AT>
 void launch_int4_mma(tl_ctx* ctx, const Int4Args& p, const EpiParams& e, bool grouped) {
   const int kblocks = p.k >> 7;
-  const int warps = kblocks >= 16 ? 16 : kblocks >= 8 ? 8 : kblocks >= 4 ? 4 : kblocks >= 2 ? 2 : 1;
+  int warps = kblocks >= 8 ? 8 : kblocks >= 4 ? 4 : kblocks >= 2 ? 2 : 1;  // 8 measured best or equal at m = 1, 8, 16
+  // A/B hook: {TL_FAMILY_QGEMV, 9, warps} forces the CTA width
+  if (ctx->has_forced && ctx->forced.family == TL_FAMILY_QGEMV && ctx->forced.kernel == 9 && ctx->forced.p0 >= 1 && ctx->forced.p0 <= 16 &&
+      (ctx->forced.p0 & (ctx->forced.p0 - 1)) == 0)
+    warps = ctx->forced.p0;
   const int grid = (p.n + 15) / 16, nt = p.m > 8 ? 2 : 1;
   const size_t smem = size_t(warps) * nt * 128 * sizeof(float);
   if (nt == 2) {
