@@ -216,6 +216,28 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
     B.check(ctx, lib.tl_event_create(ctx, C.byref(ev0)))
     B.check(ctx, lib.tl_event_create(ctx, C.byref(ev1)))
     torch.cuda.synchronize(dev)
+
+    def time_sweep(sweep_fn, n_copies, reps=20):
+        """One sweep over the weight copies captured as a graph and replayed: the launches arrive back
+        to back however slow the host's call path is.  Returns microseconds per launch."""
+        sweep_fn(2)
+        be.sync()
+        B.check(ctx, lib.tl_graph_begin(ctx))
+        sweep_fn(1)
+        gh = C.c_void_p()
+        B.check(ctx, lib.tl_graph_end(ctx, C.byref(gh)))
+        for _ in range(3):
+            B.check(ctx, lib.tl_graph_launch(ctx, gh))
+        be.sync()
+        B.check(ctx, lib.tl_event_record(ctx, ev0))
+        for _ in range(reps):
+            B.check(ctx, lib.tl_graph_launch(ctx, gh))
+        B.check(ctx, lib.tl_event_record(ctx, ev1))
+        ms = C.c_float()
+        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+        B.check(ctx, lib.tl_graph_destroy(ctx, gh))
+        return ms.value * 1e3 / (reps * n_copies)
+
     for m in (1, 16):
         x = torch.randn(m, k, device=dev).to(torch.float16)
         y = torch.empty(m, n, dtype=torch.float16, device=dev)
@@ -226,26 +248,7 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                 for c in range(copies):
                     B.check(ctx, lib.tl_qgemv_nt(ctx, x.data_ptr(), B.TL_F16, w[c].data_ptr(), s[c].data_ptr(),
                                                  y.data_ptr(), B.TL_F16, m, n, k, C.byref(q), 1.0, C.byref(e)))
-        sweep(3)
-        be.sync()
-        # one sweep over the weight copies captured as a graph and replayed: the launches arrive
-        # back to back however slow the host's call path is
-        B.check(ctx, lib.tl_graph_begin(ctx))
-        sweep(1)
-        gh = C.c_void_p()
-        B.check(ctx, lib.tl_graph_end(ctx, C.byref(gh)))
-        for _ in range(3):
-            B.check(ctx, lib.tl_graph_launch(ctx, gh))
-        be.sync()
-        reps = 20
-        B.check(ctx, lib.tl_event_record(ctx, ev0))
-        for _ in range(reps):
-            B.check(ctx, lib.tl_graph_launch(ctx, gh))
-        B.check(ctx, lib.tl_event_record(ctx, ev1))
-        ms = C.c_float()
-        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-        B.check(ctx, lib.tl_graph_destroy(ctx, gh))
-        us = ms.value * 1e3 / (reps * copies)
+        us = time_sweep(sweep, copies)
         nbytes = n * k + n * 4 + n * 4 + m * k * 2 + m * n * 2
         gbs = nbytes / us / 1e3
         out[f"gemv_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": gbs,
@@ -266,15 +269,7 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                 for c in range(copies):
                     B.check(ctx, lib.tl_matmul(ctx, x.data_ptr(), wd[c].data_ptr(), y.data_ptr(), m, n, k, 1, 0, 0, m * n, 0, 1,
                                                1.0, B.TL_F16, B.TL_F16, B.TL_F16, -1, -1, C.byref(e), None))
-        sweep_dense(3)
-        be.sync()
-        reps = 20
-        B.check(ctx, lib.tl_event_record(ctx, ev0))
-        sweep_dense(reps)
-        B.check(ctx, lib.tl_event_record(ctx, ev1))
-        ms = C.c_float()
-        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-        us = ms.value * 1e3 / (reps * copies)
+        us = time_sweep(sweep_dense, copies)
         nbytes = 2 * n * k + n * 4 + m * k * 2 + m * n * 2
         out[f"dense_gemv_f16_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": nbytes / us / 1e3,
                                                  "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
@@ -294,15 +289,7 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
                 for c in range(copies4):
                     B.check(ctx, lib.tl_qmatmul_nt(ctx, x.data_ptr(), B.TL_F16, w4[c].data_ptr(), s4.data_ptr(), y.data_ptr(), B.TL_F16,
                                                    m, n, k, C.byref(q4), 1.0, C.byref(e)))
-        sweep4(2)
-        be.sync()
-        reps = 10
-        B.check(ctx, lib.tl_event_record(ctx, ev0))
-        sweep4(reps)
-        B.check(ctx, lib.tl_event_record(ctx, ev1))
-        ms = C.c_float()
-        B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
-        us = ms.value * 1e3 / (reps * copies4)
+        us = time_sweep(sweep4, copies4, reps=10)
         nbytes = n * k // 2 + n * (k // 128) * 2 + n * 4 + m * k * 2 + m * n * 2
         out[f"int4_gemv_g128_4096x14336_m{m}"] = {"us_per_launch": us, "algorithmic_bytes": nbytes, "GBps": nbytes / us / 1e3,
                                                   "frac_of_hbm_peak": nbytes / us / 1e3 / hbm_peak, "epilogue": "bias+gelu, f16 out",
