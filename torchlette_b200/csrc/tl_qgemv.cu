@@ -580,6 +580,8 @@ template <int N> __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+__device__ __forceinline__ void prefetch_l1(const void* p) { asm volatile("prefetch.global.L1 [%0];" ::"l"(p)); }
+
 // Arguments of the fused row-parallel GEMV + all-reduce (see qgemv_ring_allreduce_kernel).
 struct PushArgs {
   uint8_t* base[tl_ctx::kMaxPeers];  // every rank's exchange buffer as mapped on this GPU (own = local)
@@ -797,6 +799,13 @@ __device__ __forceinline__ void ring_tile(const GemvArgs& p, const EpiParams& ep
       cp_async16(ring_base + (2 * s + 1) * slot_bytes, w_hi + int64_t(s) * kstride);
     }
     cp_async_commit();
+  }
+  // The tile's per-channel scales and bias entries are read in the epilogue, at the very end of a
+  // one-wave launch: a cold line there is an exposed DRAM round trip on every launch.  Ask for the
+  // lines now (scales and bias are inputs, never a predecessor's output); no register stays live.
+  if (tid == 0) {
+    if (!GROUPED) prefetch_l1(reinterpret_cast<const uint8_t*>(p.scales) + size_t(tile_row) * (p.scales_dtype == TL_F32 ? 4 : 2));
+    if (epi.fast_bias) prefetch_l1(epi.fast_bias + tile_row);
   }
   // weights never depend on the previous kernel; activations (its output) and our own stores do
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1032,6 +1041,10 @@ __device__ __forceinline__ void ring_tile2(const GemvArgs& p, const EpiParams& e
       for (int r = 0; r < 4; ++r) cp_async16(ring_base + (4 * s + r) * slot_bytes, wp[r] + int64_t(s) * kstride);
     }
     cp_async_commit();
+  }
+  if (tid == 0) {  // the epilogue's scales and bias entries: see ring_tile
+    if (!GROUPED) prefetch_l1(reinterpret_cast<const uint8_t*>(p.scales) + size_t(tile_row) * (p.scales_dtype == TL_F32 ? 4 : 2));
+    if (epi.fast_bias) prefetch_l1(epi.fast_bias + tile_row);
   }
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
