@@ -295,6 +295,15 @@ TL_API int32_t tl_rmsnorm(tl_ctx* ctx, const void* x, int32_t x_dtype, const voi
 TL_API int32_t tl_rope(tl_ctx* ctx, const void* qk, int32_t dtype, const float* cos_table, const float* sin_table,
                        void* out, int64_t outer, int64_t seq_len, int64_t head_dim, float sin_scale,
                        int64_t cos_offset, int64_t sin_offset);
+/* tl_attention: the same for q_len query positions per sequence: q [batch, n_heads, q_len, head_dim],
+ * out [batch, q_len, n_heads, head_dim] (the permute in front of o_proj, model.ts:314-318, is folded
+ * into the store).  causal != 0: query s sees the keys up to position kv_len - q_len + s (the triu mask
+ * of model.ts:300-307; prefill is kv_len == q_len).  mask, if given, is f32 [q_len, kv_len], added to
+ * the scores.  tl_decode_attention is q_len = 1. */
+TL_API int32_t tl_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out,
+                            int32_t dtype, int64_t batch, int64_t n_heads, int64_t n_kv_heads, int64_t q_len,
+                            int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,
+                            const float* mask, int32_t causal);
 TL_API int32_t tl_decode_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out,
                                    int32_t dtype, int64_t batch, int64_t n_heads, int64_t n_kv_heads,
                                    int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,

@@ -182,3 +182,37 @@ def test_one_decoder_layer_step_end_to_end(backend):
     np.testing.assert_allclose(ops.read(kc)[:, :, pos], rk, rtol=1e-4, atol=1e-4)
     np.testing.assert_allclose(ops.read(vc)[:, :, pos], rv, rtol=1e-4, atol=1e-4)
     assert be.getGpuUncapturedErrorCount() == 0
+
+
+def np_causal_attention(q, k, v, scale):
+    """q [B,H,S,D]; k, v [B,kvH,L,D], L >= S; query s sees keys <= L - S + s.  Returns [B,S,H,D]."""
+    b, h, s, d = q.shape
+    length = k.shape[2]
+    rep = h // k.shape[1]
+    ke, ve = np.repeat(k.astype(np.float64), rep, axis=1), np.repeat(v.astype(np.float64), rep, axis=1)
+    sc = np.einsum("bhsd,bhld->bhsl", q.astype(np.float64), ke) * scale
+    vis = np.arange(length)[None, :] <= (length - s + np.arange(s))[:, None]
+    sc = np.where(vis[None, None], sc, -np.inf)
+    sc = sc - sc.max(-1, keepdims=True)
+    p = np.exp(sc)
+    p /= p.sum(-1, keepdims=True)
+    return np.einsum("bhsl,bhld->bshd", p, ve)
+
+
+@pytest.mark.parametrize("s_q,kv_len", [(7, 7), (5, 12), (1, 9), (33, 33)])
+def test_causal_attention_prefill_and_multi_token_with_cache(backend, s_q, kv_len):
+    be = backend
+    b, h, kvh, d, cap = 2, 6, 3, 32, 40
+    rng = np.random.default_rng(s_q * 100 + kv_len)
+    q = rng.standard_normal((b, h, s_q, d)).astype(np.float32)
+    k = rng.standard_normal((b, kvh, cap, d)).astype(np.float32)
+    v = rng.standard_normal((b, kvh, cap, d)).astype(np.float32)
+    qt, kt, vt = _f32(be, q), _f32(be, k), _f32(be, v)
+    out = be.ops.attention(qt, kt, vt, kv_len, 1.0 / np.sqrt(d), causal=True)
+    assert out.shape == [b, s_q, h * d]
+    ref = np_causal_attention(q, k[:, :, :kv_len], v[:, :, :kv_len], 1.0 / np.sqrt(d))
+    np.testing.assert_allclose(np.asarray(be.ops.read(out), np.float64).reshape(b, s_q, h, d), ref, rtol=2e-5, atol=2e-5)
+    with pytest.raises(tb.TlError):
+        be.ops.attention(qt, kt, vt, s_q - 1 if s_q > 1 else 0, 1.0, causal=True)  # fewer keys than queries
+    for t in (qt, kt, vt, out):
+        t.destroy()

@@ -295,6 +295,18 @@ class CudaOps:
                                                                kvh, d, kvLen, cap, float(scale), mask.buffer if mask is not None else None))
         return out
 
+    def attention(self, q: CudaTensor, kCache: CudaTensor, vCache: CudaTensor, kvLen: int, scale: float, causal: bool = True,
+                  mask: Optional[CudaTensor] = None) -> CudaTensor:
+        """scaledDotProductAttention over (a prefix of) a KV cache for S query positions (model.ts:284-318):
+        q [B, H, S, D], caches [B, kvH, capacity, D]; returns [B, S, H * D].  With ``causal`` query s sees
+        keys up to kvLen - S + s (prefill: kvLen == S)."""
+        b, h, sq, d = q.shape
+        out = self.empty([b, sq, h * d], q.dtype)
+        B.check(self._b._ctx, self._b._lib.tl_attention(self._b._ctx, q.buffer, kCache.buffer, vCache.buffer, out.buffer, B.DTYPE_ID[q.dtype], b, h,
+                                                        kCache.shape[1], sq, d, kvLen, kCache.shape[2], float(scale),
+                                                        mask.buffer if mask is not None else None, 1 if causal else 0))
+        return out
+
     def kvAppend(self, cache: CudaTensor, new: CudaTensor, position: int):
         """cache[:, :, position, :] = new ([B, kvH, 1, D] or [B, kvH, D]): one strided copy (model.ts:240-262)."""
         b, kvh, cap, d = cache.shape

@@ -117,6 +117,7 @@ SIGNATURES = {
     "tl_transpose2d": (_I32, [_P, _P, _P, _I64, _I64, _I64, _I32]),
     "tl_rmsnorm": (_I32, [_P, _P, _I32, _P, _I32, _P, _I32, _I64, _I64, _F]),
     "tl_rope": (_I32, [_P, _P, _I32, _P, _P, _P, _I64, _I64, _I64, _F, _I64, _I64]),
+    "tl_attention": (_I32, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P, _I32]),
     "tl_decode_attention": (_I32, [_P, _P, _P, _P, _P, _I32, _I64, _I64, _I64, _I64, _I64, _I64, _F, _P]),
     "tl_dequant_int8": (_I32, [_P, _P, _P, _P, _I32, _I64, _I64, C.POINTER(QuantDesc)]),
     "tl_unpack_int8": (_I32, [_P, _P, _P, _I64, _I64]),

@@ -566,6 +566,14 @@ FN(DecodeAttention) {
                                            (float)f64(env, argv[12]), (const float*)dptr(env, argv[13])));
 }
 
+/* attention(ctx, q, kCache, vCache, out, dtype, batch, heads, kvHeads, qLen, headDim, kvLen, kvCapacity, scale, mask | null, causal) */
+FN(Attention) {
+  ARGS(16); CTX(0);
+  return check(env, c, tl_attention(c, dptr(env, argv[1]), dptr(env, argv[2]), dptr(env, argv[3]), dptr(env, argv[4]), i32(env, argv[5]), i64(env, argv[6]),
+                                    i64(env, argv[7]), i64(env, argv[8]), i64(env, argv[9]), i64(env, argv[10]), i64(env, argv[11]), i64(env, argv[12]),
+                                    (float)f64(env, argv[13]), (const float*)dptr(env, argv[14]), i32(env, argv[15])));
+}
+
 /* ---- dense matmul ---------------------------------------------------------------
  * matmul(ctx, a, b, out, m, n, k, batch, strideA, strideB, strideC, transA, transB, alpha, dtypeA, dtypeB, outDtype,
  *        castA, castB, epilogue?, planOnly) -> undefined, or the receipt (Int32Array) when planOnly */
@@ -712,7 +720,7 @@ napi_value napi_register_module_v1(napi_env env, napi_value exports) {
       EXPORT("qgemvNtStaticScratch", QgemvNtStaticScratch), EXPORT("qgemmNt", QgemmNt), EXPORT("qmatmulNt", QmatmulNt),
       EXPORT("dequantInt8", DequantInt8), EXPORT("unpackInt8", UnpackInt8), EXPORT("quantizeLinearWeightInt4", QuantizeLinearWeightInt4),
       EXPORT("dequantInt4", DequantInt4), EXPORT("unpackInt4", UnpackInt4), EXPORT("matmul", Matmul),
-      EXPORT("rmsnorm", Rmsnorm), EXPORT("rope", Rope), EXPORT("decodeAttention", DecodeAttention),
+      EXPORT("rmsnorm", Rmsnorm), EXPORT("rope", Rope), EXPORT("decodeAttention", DecodeAttention), EXPORT("attention", Attention),
       EXPORT("unaryOp", UnaryOp), EXPORT("binaryOp", BinaryOp), EXPORT("transpose2d", Transpose2d),
       EXPORT("planQmatmul", PlanQmatmul), EXPORT("variantName", VariantName), EXPORT("forceVariant", ForceVariant),
       EXPORT("classifyShape", ClassifyShape), EXPORT("shapeClassName", ShapeClassName),

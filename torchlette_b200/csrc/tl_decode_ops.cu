@@ -7,7 +7,8 @@
 //
 //   rmsnorm    y = x * rsqrt(mean(x^2) + eps) * w            src/ops/semantic/composite.ts:156-170
 //   rope       half-split (GPT-NeoX / Llama) rotation         src/backend/webgpu/rope-kernel.ts:1-93
-//   attention  softmax(q k^T * scale + mask) v, S = 1         model.ts:292-312 (the decomposed decode path)
+//   attention  softmax(q k^T * scale + mask) v over a KV cache   model.ts:284-318 (decode, S = 1; and the causal
+//              form for several query positions, prefill or multi-token with a cache)
 #include <algorithm>
 #include <cfloat>
 
@@ -72,23 +73,30 @@ __global__ void __launch_bounds__(256) rope_kernel(const void* qk, int dtype, co
   }
 }
 
-// one CTA per (batch, query head); 4 warps; scores for the kv_len positions live in shared memory
-__global__ void __launch_bounds__(128) decode_attention_kernel(const void* q, const void* kc, const void* vc, void* out, int dtype,
-                                                               int n_heads, int n_kv_heads, int head_dim, int kv_len,
-                                                               int64_t kv_capacity, float scale, const float* mask) {
+// one CTA per (batch, query head, query position); 4 warps; scores for the visible positions live in
+// shared memory.  q is [B, H, S, D]; the output is written as [B, S, H, D] (the permute that o_proj's
+// input needs, model.ts:314-318, folded into the store).  With `causal`, query s sees the keys up to
+// position kv_len - q_len + s (the mask the reference builds with triu, model.ts:300-307).
+__global__ void __launch_bounds__(128) attention_kernel(const void* q, const void* kc, const void* vc, void* out, int dtype,
+                                                        int n_heads, int n_kv_heads, int q_len, int head_dim, int kv_len_total,
+                                                        int64_t kv_capacity, float scale, const float* mask, int causal) {
   extern __shared__ float scores[];  // [kv_len]
   __shared__ float red[4];
-  const int b = blockIdx.x / n_heads, h = blockIdx.x - b * n_heads;
+  const int sq = blockIdx.x % q_len;
+  const int bh = blockIdx.x / q_len;
+  const int b = bh / n_heads, h = bh - b * n_heads;
   const int kvh = h / (n_heads / n_kv_heads);  // repeat_kv order: head h reads kv head h / n_rep
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int64_t q_base = (int64_t(b) * n_heads + h) * head_dim;
+  const int kv_len = causal ? kv_len_total - q_len + sq + 1 : kv_len_total;
+  const int64_t q_base = ((int64_t(b) * n_heads + h) * q_len + sq) * head_dim;
+  const int64_t o_base = ((int64_t(b) * q_len + sq) * n_heads + h) * head_dim;
   const int64_t kv_base = (int64_t(b) * n_kv_heads + kvh) * kv_capacity * head_dim;
   // scores: a warp per key position, lanes over the head dimension
   float wmax = -FLT_MAX;
   for (int j = warp; j < kv_len; j += 4) {
     float dot = 0.f;
     for (int d = lane; d < head_dim; d += 32) dot = fmaf(ld_f32(q, dtype, q_base + d), ld_f32(kc, dtype, kv_base + int64_t(j) * head_dim + d), dot);
-    dot = warp_sum(dot) * scale + (mask ? mask[j] : 0.f);
+    dot = warp_sum(dot) * scale + (mask ? mask[int64_t(sq) * kv_len_total + j] : 0.f);
     if (lane == 0) scores[j] = dot;
     wmax = fmaxf(wmax, dot);
   }
@@ -110,7 +118,7 @@ __global__ void __launch_bounds__(128) decode_attention_kernel(const void* q, co
   for (int d = threadIdx.x; d < head_dim; d += 128) {
     float acc = 0.f;
     for (int j = 0; j < kv_len; ++j) acc = fmaf(scores[j], ld_f32(vc, dtype, kv_base + int64_t(j) * head_dim + d), acc);
-    tl_store_out(out, dtype, q_base + d, acc * inv);
+    tl_store_out(out, dtype, o_base + d, acc * inv);
   }
 }
 
@@ -154,27 +162,36 @@ int32_t tl_rope(tl_ctx* ctx, const void* qk, int32_t dtype, const float* cos_tab
   return TL_OK;
 }
 
-int32_t tl_decode_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out, int32_t dtype, int64_t batch,
-                            int64_t n_heads, int64_t n_kv_heads, int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,
-                            const float* mask) {
+int32_t tl_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out, int32_t dtype, int64_t batch,
+                     int64_t n_heads, int64_t n_kv_heads, int64_t q_len, int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,
+                     const float* mask, int32_t causal) {
   TL_CHECK_CTX(ctx);
-  if (batch < 0 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || head_dim < 1 || kv_len < 1 || kv_capacity < kv_len)
-    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_decode_attention: bad shape (heads %lld, kv heads %lld, kv_len %lld, capacity %lld)",
-                        (long long)n_heads, (long long)n_kv_heads, (long long)kv_len, (long long)kv_capacity);
-  if (!tl_dtype_valid(dtype)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_decode_attention: unknown dtype");
+  if (batch < 0 || n_heads < 1 || n_kv_heads < 1 || n_heads % n_kv_heads != 0 || head_dim < 1 || q_len < 1 || kv_len < q_len ||
+      kv_capacity < kv_len)
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG,
+                        "tl_attention: bad shape (heads %lld, kv heads %lld, q_len %lld, kv_len %lld, capacity %lld)", (long long)n_heads,
+                        (long long)n_kv_heads, (long long)q_len, (long long)kv_len, (long long)kv_capacity);
+  if (!tl_dtype_valid(dtype)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_attention: unknown dtype");
   if (batch == 0) return TL_OK;
-  if (!q || !k_cache || !v_cache || !out) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_decode_attention: null pointer");
+  if (!q || !k_cache || !v_cache || !out) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_attention: null pointer");
   const size_t smem = size_t(kv_len) * sizeof(float);
-  if (smem > 200 * 1024 || batch * n_heads > INT32_MAX || head_dim > 1024)
-    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_decode_attention: kv_len %lld exceeds the %d positions one launch keeps in shared memory",
+  if (smem > 200 * 1024 || batch * n_heads * q_len > INT32_MAX || head_dim > 1024)
+    return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "tl_attention: kv_len %lld exceeds the %d positions one launch keeps in shared memory",
                         (long long)kv_len, 200 * 1024 / 4);
   DeviceGuard guard(ctx->device);
-  if (smem > 48 * 1024) cudaFuncSetAttribute(decode_attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-  decode_attention_kernel<<<unsigned(batch * n_heads), 128, smem, ctx->stream>>>(q, k_cache, v_cache, out, dtype, int(n_heads), int(n_kv_heads),
-                                                                                 int(head_dim), int(kv_len), kv_capacity, scale, mask);
+  if (smem > 48 * 1024) cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  attention_kernel<<<unsigned(batch * n_heads * q_len), 128, smem, ctx->stream>>>(q, k_cache, v_cache, out, dtype, int(n_heads), int(n_kv_heads),
+                                                                                  int(q_len), int(head_dim), int(kv_len), kv_capacity, scale, mask,
+                                                                                  causal ? 1 : 0);
   TL_CUDA(ctx, cudaGetLastError());
   ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
   return TL_OK;
+}
+
+int32_t tl_decode_attention(tl_ctx* ctx, const void* q, const void* k_cache, const void* v_cache, void* out, int32_t dtype, int64_t batch,
+                            int64_t n_heads, int64_t n_kv_heads, int64_t head_dim, int64_t kv_len, int64_t kv_capacity, float scale,
+                            const float* mask) {
+  return tl_attention(ctx, q, k_cache, v_cache, out, dtype, batch, n_heads, n_kv_heads, 1, head_dim, kv_len, kv_capacity, scale, mask, 0);
 }
 
 }  // extern "C"

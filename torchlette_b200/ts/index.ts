@@ -199,6 +199,16 @@ export function decodeAttention(q: CudaTensor, kCache: CudaTensor, vCache: CudaT
   return out;
 }
 
+/** S query positions against (a prefix of) a KV cache, causal (model.ts:284-318): q [B,H,S,D] -> [B,S,H*D]. */
+export function attention(q: CudaTensor, kCache: CudaTensor, vCache: CudaTensor, kvLen: number, scale: number, causal = true,
+                          mask?: CudaTensor): CudaTensor {
+  const [b, h, s, d] = q.shape;
+  const out = empty([b, s, h * d], q.dtype as string);
+  addon.attention(need(), q.buffer, kCache.buffer, vCache.buffer, out.buffer, DTYPE_ID[q.dtype as string], b, h, kCache.shape[1], s, d, kvLen,
+                  kCache.shape[2], scale, mask ? mask.buffer : null, causal ? 1 : 0);
+  return out;
+}
+
 /** createQuantizedWeight (engine.ts:2041-2149): validate, upload, attach format + scales. */
 export function createQuantizedWeight(packed: Uint32Array, scalesBits: Uint16Array | Float32Array, n: number, k: number,
                                       format: StorageFormat & { scaleConvention?: "snorm127" | "direct" }): CudaTensor {
