@@ -104,6 +104,13 @@ typedef struct tl_epilogue {
 /* initWebGPU / destroyWebGPU / syncWebGPU / getWebGPUInitError /
  * getGpuUncapturedErrorCount (src/backend/webgpu/index.ts:39-70,
  * src/backend/webgpu/gpu-context.ts:386-405). */
+/* Read from the environment at tl_ctx_create (the reference's ENV, src/core/env.ts:14-26):
+ *   TORCHLETTE_CUDA_VARIANT=family,kernel[,p0,p1,p2,p3]  start with that variant forced (tl_force_variant)
+ *   TORCHLETTE_CUDA_PROFILE=1   CUDA events around every tl_qgemv_nt / tl_qgemm_nt / tl_qmatmul_nt / tl_matmul
+ *                               call, one "[tl profile] label m n k: us" line per call on stderr (the
+ *                               analogue of TORCHLETTE_PROFILE=1, src/backend/webgpu/profiler.ts); it
+ *                               synchronises after each call and is silent during graph capture
+ * and, where they are used: TORCHLETTE_GEMV=0, TORCHLETTE_AUTOTUNE=1, TORCHLETTE_DEBUG_AUTOTUNE=1, TL_NCCL_LIB. */
 TL_API int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx);
 TL_API int32_t tl_ctx_destroy(tl_ctx* ctx);
 TL_API int32_t tl_sync(tl_ctx* ctx);

@@ -71,6 +71,22 @@ int32_t tl_ensure_zeroed_scratch(tl_ctx* ctx, size_t bytes, void** out) {
   return TL_OK;
 }
 
+TlProfileScope::TlProfileScope(tl_ctx* c, const char* l, int64_t m_, int64_t n_, int64_t k_)
+    : ctx(c), label(l), m(m_), n(n_), k(k_), on(false) {
+  if (!c || !c->profile || c->capturing) return;
+  DeviceGuard guard(c->device);
+  if (!c->prof_e0 && (cudaEventCreate(&c->prof_e0) != cudaSuccess || cudaEventCreate(&c->prof_e1) != cudaSuccess)) return;
+  on = cudaEventRecord(c->prof_e0, c->stream) == cudaSuccess;
+}
+TlProfileScope::~TlProfileScope() {
+  if (!on) return;
+  DeviceGuard guard(ctx->device);
+  float ms = 0.f;
+  if (cudaEventRecord(ctx->prof_e1, ctx->stream) == cudaSuccess && cudaEventSynchronize(ctx->prof_e1) == cudaSuccess &&
+      cudaEventElapsedTime(&ms, ctx->prof_e0, ctx->prof_e1) == cudaSuccess)
+    fprintf(stderr, "[tl profile] %s m=%lld n=%lld k=%lld: %.2f us\n", label, (long long)m, (long long)n, (long long)k, ms * 1e3);
+}
+
 extern "C" {
 
 int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx) {
@@ -115,6 +131,20 @@ int32_t tl_ctx_create(int32_t device_ordinal, tl_ctx** out_ctx) {
     return tl_set_error(nullptr, TL_ERR_OOM, "tl_ctx_create: cannot allocate the device status word");
   }
   ctx->pf_flags = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(ctx->dev_status) + 64);
+  // environment knobs, read once per context like the reference's ENV (src/core/env.ts:14-26):
+  //   TORCHLETTE_CUDA_VARIANT=family,kernel,p0,p1,p2,p3   force one kernel variant (A/B runs without code)
+  //   TORCHLETTE_CUDA_PROFILE=1                           per-call event timing on stderr
+  if (const char* ev = getenv("TORCHLETTE_CUDA_VARIANT")) {
+    tl_variant v{};
+    if (sscanf(ev, "%d,%d,%d,%d,%d,%d", &v.family, &v.kernel, &v.p0, &v.p1, &v.p2, &v.p3) >= 2 &&
+        (v.family == TL_FAMILY_QGEMV || v.family == TL_FAMILY_QGEMM || v.family == TL_FAMILY_MATMUL)) {
+      ctx->forced = v;
+      ctx->has_forced = true;
+    } else {
+      fprintf(stderr, "[tlcuda] TORCHLETTE_CUDA_VARIANT='%s' ignored: expected family,kernel[,p0,p1,p2,p3] with family 1..3\n", ev);
+    }
+  }
+  if (const char* ev = getenv("TORCHLETTE_CUDA_PROFILE")) ctx->profile = ev[0] == '1';
   *out_ctx = ctx;
   return TL_OK;
 }
@@ -129,6 +159,7 @@ int32_t tl_ctx_destroy(tl_ctx* ctx) {
   for (auto& p : ctx->retired_scratch) cudaFree(p.first);
   if (ctx->dev_status) cudaFree(ctx->dev_status);
   if (ctx->stream_scratch) cudaFree(ctx->stream_scratch);
+  if (ctx->prof_e0) { cudaEventDestroy(ctx->prof_e0); cudaEventDestroy(ctx->prof_e1); }
   for (int r = 0; r < tl_ctx::kMaxPeers; ++r)
     if (ctx->p2p_peer[r] && ctx->p2p_peer[r] != ctx->p2p_local) cudaIpcCloseMemHandle(ctx->p2p_peer[r]);
   if (ctx->p2p_local) cudaFree(ctx->p2p_local);
@@ -658,6 +689,7 @@ extern "C" {
 int32_t tl_qgemv_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed, const void* scales,
                     void* out, int32_t out_dtype, int32_t m, int64_t n, int64_t k,
                     const tl_quant_desc* qdesc, float alpha, const tl_epilogue* epilogue) {
+  TlProfileScope prof(ctx, "matmul_gemv_q8", m, n, k);  // the reference's label for this route (matmul/dispatch.ts:928)
   return qmatmul_impl(ctx, "tl_qgemv_nt", 1, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc,
                       alpha, epilogue, nullptr);
 }
@@ -665,6 +697,7 @@ int32_t tl_qgemv_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* pac
 int32_t tl_qgemm_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed, const void* scales,
                     void* out, int32_t out_dtype, int64_t m, int64_t n, int64_t k,
                     const tl_quant_desc* qdesc, float alpha, const tl_epilogue* epilogue) {
+  TlProfileScope prof(ctx, "matmul_gemm_q8", m, n, k);
   return qmatmul_impl(ctx, "tl_qgemm_nt", 2, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc,
                       alpha, epilogue, nullptr);
 }
@@ -672,6 +705,7 @@ int32_t tl_qgemm_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* pac
 int32_t tl_qmatmul_nt(tl_ctx* ctx, const void* a, int32_t a_dtype, const void* packed, const void* scales,
                       void* out, int32_t out_dtype, int64_t m, int64_t n, int64_t k,
                       const tl_quant_desc* qdesc, float alpha, const tl_epilogue* epilogue) {
+  TlProfileScope prof(ctx, m <= 16 ? "matmul_gemv_q8" : "matmul_gemm_q8", m, n, k);
   return qmatmul_impl(ctx, "tl_qmatmul_nt", 0, a, a_dtype, packed, scales, out, out_dtype, m, n, k, qdesc,
                       alpha, epilogue, nullptr);
 }

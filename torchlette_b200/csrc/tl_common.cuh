@@ -77,6 +77,9 @@ struct tl_ctx {
   std::map<TuneKey, tl_variant> class_tuned;
   std::map<int, int> ring_occupancy;  // resident CTAs per SM of each ring kernel shape (queried once)
   bool capturing = false;
+  // TORCHLETTE_CUDA_PROFILE=1: CUDA events around every product call, one line per call on stderr
+  bool profile = false;
+  cudaEvent_t prof_e0 = nullptr, prof_e1 = nullptr;
   // multi-GPU
   void* nccl_comm = nullptr;
   int rank = 0, world = 1;
@@ -113,6 +116,20 @@ int32_t tl_ensure_zeroed_scratch(tl_ctx* ctx, size_t bytes, void** out);
   } while (0)
 
 // Sets the calling thread's current device to the context's for one scope.
+// Per-call timing behind TORCHLETTE_CUDA_PROFILE=1 (the reference's TORCHLETTE_PROFILE=1 timestamp pairs per
+// compute pass, src/backend/webgpu/profiler.ts, webgpu/dispatch.ts:80-84): two events around the call's
+// launches on the context's stream, a synchronize, and one line "[tl profile] <label> m n k: us" on stderr.
+// It serialises the stream, so it is for reading kernel times, not for running a benchmark; it does nothing
+// while a graph is being captured.
+struct TlProfileScope {
+  tl_ctx* ctx;
+  const char* label;
+  int64_t m, n, k;
+  bool on;
+  TlProfileScope(tl_ctx* c, const char* l, int64_t m_, int64_t n_, int64_t k_);
+  ~TlProfileScope();
+};
+
 struct DeviceGuard {
   int prev = -1;
   explicit DeviceGuard(int dev) {

@@ -190,6 +190,7 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
                              int32_t dtype_a, int32_t dtype_b, int32_t out_dtype, int32_t cast_a, int32_t cast_b,
                              const tl_epilogue* epilogue, tl_plan_receipt* receipt_only) {
   TL_CHECK_CTX(ctx);
+  TlProfileScope prof(receipt_only ? nullptr : ctx, "matmul", m, n, k);
   if (!receipt_only && (!a || !b || !out)) return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: null pointer");
   if (m < 0 || n < 0 || k < 0 || batch < 1)
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: bad shape m=%lld n=%lld k=%lld batch=%lld", (long long)m, (long long)n,
