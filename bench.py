@@ -154,12 +154,18 @@ class CpuArm:
                           f"rows, batch {self.batch}, extrapolated to a full step; f32 weights dequantized once, untimed"}
 
 
-def cpu_sample(batch: int):
+def cpu_sample(batch: int, seconds: float = 10.0):
+    """About `seconds` of CPU work on all host threads: the sample is repeated and the median kept."""
     arm = CpuArm(batch)
     arm.step_seconds()
-    d = arm.describe(batch / arm.step_seconds())
+    t0 = time.perf_counter()
+    vals = []
+    while len(vals) < 3 or time.perf_counter() - t0 < seconds:
+        vals.append(arm.step_seconds())
+    d = arm.describe(batch / statistics.median(vals))
+    d["sample"] += f"; {len(vals)} repetitions in {time.perf_counter() - t0:.1f} s, median"
     # the reference's JavaScript CPU backend is single-threaded: the faithful figure beside the all-core one
-    d["value_1_thread"] = batch / arm.step_seconds(threads=1)
+    d["value_1_thread"] = batch / statistics.median([arm.step_seconds(threads=1) for _ in range(3)])
     return d
 
 
