@@ -12,6 +12,7 @@ import pytest
 
 from oracle import oracle as orc
 from torchlette_b200 import backend as tb
+from torchlette_b200 import binding as B
 
 pytestmark = pytest.mark.gpu
 
@@ -346,4 +347,78 @@ def test_dense_tensor_core_batched(backend):
     for i in range(bs):
         assert _rel(g[i], _ref(a_v[i], b_v[i])) <= 1e-3
     for t in (a, b, y):
+        t.destroy()
+
+
+# every tile shape of the tensor-core kernel, forced: (BN, MH) with MH row halves of 128 per tile
+_TC_TILES = [(256, 1), (224, 1), (192, 1), (160, 1), (128, 1), (256, 2), (240, 2), (224, 2), (208, 2), (192, 2), (176, 2), (160, 2)]
+
+
+@pytest.mark.parametrize("bn,mh", _TC_TILES)
+def test_dense_tensor_core_every_tile_shape_ragged(backend, bn, mh):
+    """m, n and k off every tile boundary (the second row half of the last tile is partly out of range,
+    the last column tile is ragged, k ends inside a 64-k stage), bias + gelu, f16 in and out."""
+    be = backend
+    m, k, n = 300, 200, 2 * bn + 40
+    rng = np.random.default_rng(bn + mh)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "f16")
+    w, w_v = _to_dev(be, (rng.uniform(-1, 1, n * k) * 0.2).astype(np.float32), [n, k], "f16")
+    bias_v = rng.uniform(-1, 1, n).astype(np.float32)
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    plan = tb.detectMatmulEpilogue([("add", bias_t), ("gelu", None), ("cast", "f16")])
+    be.forceVariant((B.TL_FAMILY_MATMUL, 2, bn, 0, mh, 0))
+    try:
+        receipt = be.planMatmul(m, n, k, "f16", "f16", transB=True)
+        assert receipt["variant"].startswith("matmul.tc") and receipt["choice"][2] == bn and receipt["choice"][4] == mh
+        y = be.ops.matmul(x, be.ops.transpose(w), {"epilogue": plan[0], "epilogueInputs": plan[1]})
+        assert _rel(_read_f32(be, y), _ref(x_v, w_v.T, bias_v, "gelu")) <= 1e-2
+        # exactly representable inputs: bit-equal to the oracle, f32 out (the un-approximated path)
+        xp, xp_v = _to_dev(be, _pattern(m * k, 0), [m, k], "f16")
+        wp, wp_v = _to_dev(be, _pattern(n * k, 3), [n, k], "f16")
+        yp = be.ops.matmul(xp, be.ops.transpose(wp))
+        np.testing.assert_array_equal(_read_f32(be, yp), _ref(xp_v, wp_v.T))
+    finally:
+        be.forceVariant(None)
+    for t in (x, w, bias_t, y, xp, wp, yp):
+        t.destroy()
+
+
+@pytest.mark.parametrize("bn,mh", [(160, 2), (256, 2), (128, 1)])
+def test_dense_tensor_core_several_tiles_per_cta(backend, bn, mh):
+    """More tiles than SMs: every CTA walks several tiles, so the accumulators in TMEM are handed back
+    and forth between the MMA warp and the epilogue warps (one set when MH = 2, two when MH = 1)."""
+    be = backend
+    m, k, n = 2048, 192, 20 * bn
+    rng = np.random.default_rng(5)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "bf16")
+    w, w_v = _to_dev(be, rng.uniform(-1, 1, n * k).astype(np.float32), [n, k], "bf16")
+    be.forceVariant((B.TL_FAMILY_MATMUL, 2, bn, 0, mh, 0))
+    try:
+        y = be.ops.matmul(x, be.ops.transpose(w))
+        assert _rel(_read_f32(be, y), _ref(x_v, w_v.T)) <= 1e-3
+    finally:
+        be.forceVariant(None)
+    for t in (x, w, y):
+        t.destroy()
+
+
+@pytest.mark.parametrize("out_dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("act", ["relu", "silu", "gelu", "gelu_erf", "sigmoid", "tanh"])
+def test_dense_tensor_core_unary_modes_on_two_half_tiles(backend, out_dtype, act):
+    be = backend
+    m, k, n = 260, 128, 330
+    rng = np.random.default_rng(9)
+    x, x_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "bf16")
+    w, w_v = _to_dev(be, (rng.uniform(-1, 1, n * k) * 0.2).astype(np.float32), [n, k], "bf16")
+    chain = [("gelu", {"approximate": "none"}) if act == "gelu_erf" else (act, None)]
+    if out_dtype != "f32":
+        chain.append(("cast", out_dtype))
+    plan = tb.detectMatmulEpilogue(chain)
+    be.forceVariant((B.TL_FAMILY_MATMUL, 2, 160, 0, 2, 0))
+    try:
+        y = be.ops.matmul(x, be.ops.transpose(w), {"epilogue": plan[0], "epilogueInputs": plan[1]})
+        assert _rel(_read_f32(be, y), _ref(x_v, w_v.T, None, act)) <= (1e-3 if out_dtype == "f32" else 1e-2)
+    finally:
+        be.forceVariant(None)
+    for t in (x, w, y):
         t.destroy()

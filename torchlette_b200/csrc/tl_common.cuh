@@ -228,7 +228,8 @@ int32_t tl_int4_matmul(tl_ctx* ctx, const char* who, int route, const void* a, i
                        const tl_epilogue* epilogue, tl_plan_receipt* receipt_only);
 // Dense tensor-core matmul (tl_matmul_tc.cu): NT layout, both operands f16 or both bf16.
 bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, int64_t k, int32_t dtype_a, int32_t dtype_b);
-void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid);
+void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int* bn, int* mh, int* stages,
+                       int* grid);
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const struct EpiParams& epi);
 bool tl_qgemv_stream_applicable(const tl_variant& v, int64_t m, int64_t k, int32_t a_dtype, const tl_quant_desc& q);

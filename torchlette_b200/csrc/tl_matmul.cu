@@ -248,11 +248,12 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     receipt_only->grid[2] = use_gemv ? 1 : int32_t(batch);
     receipt_only->block = use_gemv ? warps * 32 : 256;
     if (use_tc) {
-      int bn, stages, grid;
-      tl_dense_tc_shape(m, n, ctx->sm_count, &bn, &stages, &grid);
-      receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages;
+      int bn, mh, stages, grid;
+      const bool f = forced_tc && ctx->forced.p0 > 0;
+      tl_dense_tc_shape(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid);
+      receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages; receipt_only->choice.p2 = mh;
       receipt_only->grid[0] = grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
-      receipt_only->block = 320;
+      receipt_only->block = 576;
     }
     receipt_only->split_k = 1;
     receipt_only->from_tuning_cache = 0;

@@ -5,11 +5,20 @@
 // tiled matmul body + epilogue (src/schedule/matmul-skeleton.ts:738-966) for the NT layout that
 // `linear` produces (other layouts are brought to it by one transposition pass, see tl_matmul).
 //
-//   tile: 128 rows of A (tokens, = TMEM lanes) x BN rows of B (output columns, = TMEM columns; BN is 128,
-//         160, 192, 224 or 256, whichever leaves the fewest idle SMs in the last wave),
-//         64 k per pipeline stage (one 128-byte swizzled row per operand row), 4 MMAs of K = 16 per stage;
+//   tile: 128 x MH rows of A (tokens, = TMEM lanes; MH = 1 or 2 row halves) x BN rows of B (output columns,
+//         = TMEM columns; BN a multiple of 16 up to 256), 64 k per pipeline stage (one 128-byte swizzled row
+//         per operand row), 4 MMAs of K = 16 per stage and row half;
+//   MH = 1: two accumulators of BN columns, so the epilogue of tile i overlaps the main loop of tile i+1.
+//   MH = 2: both row halves multiply the SAME B tile in shared memory, which halves the B bytes an SM pulls
+//         from L2 per flop -- with 128-row tiles the SM's L2 ingest (about 64 bytes per clock), not the tensor
+//         pipe, sets the pace: (128 + 224) x 128 bytes per 448 MMA clocks is 100 bytes per clock, (256 + 208)
+//         x 128 per 832 is 71.  The two halves fill TMEM (2 x BN columns), so the epilogue (one warp per lane
+//         quarter and half) does not overlap the next tile; it is a few percent when K is in the thousands.
+//         The host picks MH and BN from a per-tile time model times the number of waves (tl_dense_tc_shape);
 //   warp 0: TMA producer (one elected lane); warp 1: TMEM allocation + MMA issue (one elected lane);
-//   warps 2..9: epilogue, two warps per TMEM lane quarter, each taking half of the tile's columns;
+//   warps 2..17: epilogue, four warps per TMEM lane quarter (MH = 1: each takes a quarter of the columns;
+//         MH = 2: a row half and half of the columns) -- the epilogue is a latency-bound instruction
+//         stream, and with K in the low thousands it, not the MMA, paced the tile until it had 16 warps;
 //   persistent: one CTA per SM walks the tiles round-robin, row tiles fastest so that CTAs running
 //   side by side read the same B rows through L2.
 // Ragged edges: TMA zero-fills out-of-range rows and k, stores are masked.
@@ -24,7 +33,8 @@
 
 namespace {
 
-constexpr int kBM = 128, kBK = 64;
+constexpr int kDenseThreads = 32 * (2 + 16);  // TMA warp, MMA warp, 16 epilogue warps
+constexpr int kBM = 128, kBK = 64;  // kBM: rows per MMA (TMEM lanes); a tile has kBM * MH rows
 
 struct DenseTcArgs {
   void* out;
@@ -38,13 +48,21 @@ template <typename T> struct OperandFmt;
 template <> struct OperandFmt<__half> { static constexpr uint32_t kFmt = 0; };
 template <> struct OperandFmt<__nv_bfloat16> { static constexpr uint32_t kFmt = 1; };
 
-template <typename AT, int BN, int STAGES>
-__global__ void __launch_bounds__(320, 1)
+// The precise unary ops and the general op chain, out of line (one call per element).
+__device__ __noinline__ float dense_unary_outlined(int op, bool approx, float x) { return approx ? tl_unary_approx(op, x) : tl_unary(op, x); }
+__device__ __noinline__ float dense_epilogue_outlined(const EpiParams& e, float v, int64_t row, int64_t col, int64_t n) {
+  return tl_apply_epilogue(e, v, row, col, n);
+}
+
+template <typename AT, int BN, int STAGES, int MH>
+__global__ void __launch_bounds__(kDenseThreads, 1)
 dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, DenseTcArgs p, EpiParams epi) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
-  constexpr int kABytes = kBM * 128, kBBytes = BN * 128, kStageBytes = kABytes + kBBytes;
+  static_assert(MH == 1 || MH == 2, "row halves");
+  constexpr int kTileM = kBM * MH, kAcc = MH == 1 ? 2 : 1;  // accumulator sets in TMEM (each MH x BN columns)
+  constexpr int kABytes = kTileM * 128, kBBytes = BN * 128, kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
-  constexpr int kEpiWarp0 = 2, kEpiWarps = 8;
+  constexpr int kEpiWarp0 = 2, kEpiWarps = 16;
   constexpr uint32_t kIdesc = (1u << 4) | (OperandFmt<AT>::kFmt << 7) | (OperandFmt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
                               (uint32_t(kBM >> 4) << 24);
 
@@ -93,7 +111,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           }
           uint8_t* st = stages + size_t(s) * kStageBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
-          tma_load_2d(st, &amap, ks * kBK, m_tile * kBM, &full_bar[s]);
+          tma_load_2d(st, &amap, ks * kBK, m_tile * kTileM, &full_bar[s]);
           tma_load_2d(st + kABytes, &bmap, ks * kBK, n_tile * BN, &full_bar[s]);
         }
       }
@@ -103,13 +121,13 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     if (lane == 0) {
       int it = 0, tl = 0;
       for (int t = blockIdx.x; t < tiles && !abort_flag; t += gridDim.x, ++tl) {
-        const int acc = tl & 1;
-        if (tl >= 2 && !mbar_wait(&tempty_bar[acc], ((tl >> 1) - 1) & 1, &abort_flag)) {
+        const int acc = tl % kAcc, use = tl / kAcc;
+        if (use >= 1 && !mbar_wait(&tempty_bar[acc], (use - 1) & 1, &abort_flag)) {
           if (!abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
           break;
         }
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + uint32_t(acc * BN);
+        const uint32_t d_tmem = tmem_base + uint32_t(acc * MH * BN);
         bool ok = true;
         for (int ks = 0; ks < p.ksteps; ++ks, ++it) {
           const int s = it % STAGES;
@@ -122,8 +140,11 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const uint32_t a_base = smem_u32(stages + size_t(s) * kStageBytes);
           const uint32_t b_base = a_base + kABytes;
 #pragma unroll
-          for (int kk = 0; kk < kBK / 16; ++kk)
-            tc_mma_ss(d_tmem, make_b_desc(a_base + kk * 32), make_b_desc(b_base + kk * 32), kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+          for (int h = 0; h < MH; ++h)
+#pragma unroll
+            for (int kk = 0; kk < kBK / 16; ++kk)
+              tc_mma_ss(d_tmem + uint32_t(h * BN), make_b_desc(a_base + h * (kBM * 128) + kk * 32), make_b_desc(b_base + kk * 32),
+                        kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
         if (!ok) break;
@@ -132,47 +153,77 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     }
   } else {
     // ------------------------------ epilogue ------------------------------
-    const int quad = warp & 3, ehalf = (warp - kEpiWarp0) >> 2;
+    // Four warps per TMEM lane quarter.  Everything per chunk stays in registers: the loops are fully
+    // unrolled, the op chain is decoded once per kernel into `mode`, and the general chain is an
+    // out-of-line call per element (it is the rare case; inlined 16 times it would evict the hot loop).
+    constexpr int kColParts = (kEpiWarps / 4) / MH;
+    const int quad = warp & 3, part = (warp - kEpiWarp0) >> 2;
+    const int ehalf = MH == 2 ? part / kColParts : 0, cpart = MH == 2 ? part % kColParts : part;
     const uint32_t lane_addr = uint32_t(quad * 32) << 16;
     constexpr int kChunksN = BN / 16;
-    const int cbeg = ehalf == 0 ? 0 : (kChunksN + 1) / 2, cend = ehalf == 0 ? (kChunksN + 1) / 2 : kChunksN;
-    const bool fast = epi.fast != 0, approx = p.out_dtype != TL_F32;
+    const int cbeg = cpart * kChunksN / kColParts, cend = (cpart + 1) * kChunksN / kColParts;
+    const bool approx = p.out_dtype != TL_F32;
+    enum { kPlain, kGelu, kRelu, kSilu, kUnary, kGeneric };
+    const int fu = epi.fast_unary;
+    const int mode = !epi.fast ? kGeneric
+                   : fu == 0 ? kPlain
+                   : (approx && fu == TL_UNARY_GELU_TANH) ? kGelu
+                   : fu == TL_UNARY_RELU ? kRelu
+                   : (approx && fu == TL_UNARY_SILU) ? kSilu : kUnary;
+    const float* bias = epi.fast ? epi.fast_bias : nullptr;
+    const float alpha = epi.alpha;
     const int esz = p.out_dtype == TL_F32 ? 4 : 2;
     const bool vec_ok = (p.n * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
     int tl = 0;
     for (int t = blockIdx.x; t < tiles; t += gridDim.x, ++tl) {
-      const int acc = tl & 1;
+      const int acc = tl % kAcc;
       const int n_tile = t / p.m_tiles, m_tile = t - n_tile * p.m_tiles;
-      const int64_t row = int64_t(m_tile) * kBM + quad * 32 + lane;  // this thread's output row
+      const int64_t row = int64_t(m_tile) * kTileM + ehalf * kBM + quad * 32 + lane;  // this thread's output row
       const bool row_ok = row < p.m;
-      if (!mbar_wait(&tfull_bar[acc], (tl >> 1) & 1, &abort_flag)) {
+      const uint32_t acc_col = uint32_t(acc * MH * BN + ehalf * BN);
+      if (!mbar_wait(&tfull_bar[acc], (tl / kAcc) & 1, &abort_flag)) {
         if (lane == 0 && !abort_flag) { abort_flag = 1; atomicExch(p.status, TL_DEV_TIMEOUT_TMEM); }
         break;
       }
       tc_fence_after();
       uint32_t vn[16];
-      if (cbeg < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + cbeg * 16), vn);
+      if (cbeg < cend) tmem_ld16(tmem_base + lane_addr + acc_col + uint32_t(cbeg * 16), vn);
 #pragma unroll 1
       for (int ch = cbeg; ch < cend; ++ch) {
         const int64_t col0 = int64_t(n_tile) * BN + ch * 16;
-        uint32_t v[16];
+        float o[16];
         tmem_ld_wait();
 #pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = vn[j];
-        if (ch + 1 < cend) tmem_ld16(tmem_base + lane_addr + uint32_t(acc * BN + (ch + 1) * 16), vn);  // next chunk in flight
+        for (int j = 0; j < 16; ++j) o[j] = __uint_as_float(vn[j]);
+        if (ch + 1 < cend) tmem_ld16(tmem_base + lane_addr + acc_col + uint32_t((ch + 1) * 16), vn);  // next chunk in flight
         if (!row_ok || col0 >= p.n) continue;
-        float o[16];
         const int jmax = int(min(int64_t(16), p.n - col0));
-        if (fast) {
+        if (mode != kGeneric) {
+          if (bias) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float b = (epi.fast_bias && j < jmax) ? __ldg(epi.fast_bias + col0 + j) : 0.f;
-            o[j] = fmaf(__uint_as_float(v[j]), epi.alpha, b);
-            if (epi.fast_unary) o[j] = approx ? tl_unary_approx(epi.fast_unary, o[j]) : tl_unary(epi.fast_unary, o[j]);
+            for (int j = 0; j < 16; ++j) o[j] = fmaf(o[j], alpha, j < jmax ? __ldg(bias + col0 + j) : 0.f);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] *= alpha;
+          }
+          if (mode == kGelu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              o[j] = (0.5f * o[j]) * (1.f + tl_tanh_approx(0.7978845608f * (o[j] + 0.044715f * (o[j] * (o[j] * o[j])))));
+          } else if (mode == kRelu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = fmaxf(o[j], 0.f);
+          } else if (mode == kSilu) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = __fdividef(o[j], 1.f + __expf(-o[j]));
+          } else if (mode == kUnary) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) o[j] = dense_unary_outlined(fu, approx, o[j]);
           }
         } else {
-#pragma unroll 1
-          for (int j = 0; j < jmax; ++j) o[j] = tl_apply_epilogue(epi, __uint_as_float(v[j]), row, col0 + j, p.n);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < jmax) o[j] = dense_epilogue_outlined(epi, o[j], row, col0 + j, p.n);
         }
         uint8_t* optr = reinterpret_cast<uint8_t*>(p.out) + (row * p.n + col0) * esz;
         if (jmax == 16 && vec_ok) {
@@ -196,8 +247,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             reinterpret_cast<uint4*>(optr)[1] = make_uint4(w[4], w[5], w[6], w[7]);
           }
         } else {
-#pragma unroll 1
-          for (int j = 0; j < jmax; ++j) tl_store_out(p.out, p.out_dtype, row * p.n + col0 + j, o[j]);
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            if (j < jmax) tl_store_out(p.out, p.out_dtype, row * p.n + col0 + j, o[j]);
         }
       }
       tc_fence_before();
@@ -214,13 +266,14 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   }
 }
 
-template <typename AT, int BN, int STAGES>
+template <typename AT, int BN, int STAGES, int MH>
 cudaError_t launch_dense(int grid, cudaStream_t s, const CUtensorMap& amap, const CUtensorMap& bmap, const DenseTcArgs& p,
                          const EpiParams& e) {
-  constexpr size_t smem = size_t(STAGES) * (kBM * 128 + BN * 128) + 1024;
-  auto kern = dense_tc_kernel<AT, BN, STAGES>;
+  constexpr size_t smem = size_t(STAGES) * (kBM * MH * 128 + BN * 128) + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory per CTA");
+  auto kern = dense_tc_kernel<AT, BN, STAGES, MH>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-  kern<<<grid, 320, smem, s>>>(amap, bmap, p, e);
+  kern<<<grid, kDenseThreads, smem, s>>>(amap, bmap, p, e);
   return cudaGetLastError();
 }
 
@@ -234,50 +287,80 @@ bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, 
   return true;
 }
 
-// p0 of the receipt: BN (columns per tile); p1: stages.  A tile's time grows with BN (the MMA is the
-// long pole), so the cost of a choice is waves x BN with waves = ceil(tiles / SMs): e.g. n = 14336,
-// m = 2048 on 148 SMs is 7 waves at BN = 256 but also 7 waves at BN = 224 (6.92 full), 12 % less work.
-void tl_dense_tc_shape(int64_t m, int64_t n, int sms, int* bn, int* stages, int* grid) {
-  const int64_t m_tiles = (m + kBM - 1) / kBM;
-  int64_t best_cost = INT64_MAX;
-  int best = 128;
-  for (int b : {256, 224, 192, 160, 128}) {
-    if (b > 128 && n < b) continue;
-    const int64_t t = m_tiles * ((n + b - 1) / b);
-    const int64_t cost = ((t + sms - 1) / sms) * b;
-    if (cost < best_cost) { best_cost = cost; best = b; }
+// p0 of the receipt: BN (columns per tile); p1: stages; p2: MH (row halves per tile).  The choice minimises
+// waves x tile time, waves = ceil(tiles / SMs), with the tile time taken from measurements on B200 (bf16,
+// shapes from 1024^3 to 8192^3): a 64-k step costs `step_us` whatever the shape -- it follows the bytes the
+// SM pulls from L2 per step (86 to 117 GB/s per SM), not the MMA's clocks, which is why 256-row tiles win on
+// large shapes (0.742 us for 256 x 256 against 2 x 0.424 for 128 x 256) and why four stages (BN <= 192 at
+// MH = 2) beat three.  With MH = 1 the epilogue hides behind the next tile unless K is short; with MH = 2
+// it adds to every tile.  E.g. m = 2048, n = 14336, k = 4096 on 148 SMs: 128 x 224 tiles run 7 waves of
+// 27 us, 256 x 208 tiles 4 waves of 46 us.
+namespace {
+struct DenseCfg { int mh, bn, stages; float step_us; };
+constexpr DenseCfg kDenseCfgs[] = {{1, 256, 4, 0.424f}, {1, 224, 5, 0.410f}, {1, 192, 5, 0.373f}, {1, 160, 6, 0.358f},
+                                   {1, 128, 6, 0.348f}, {2, 256, 3, 0.742f}, {2, 240, 3, 0.734f}, {2, 224, 3, 0.700f},
+                                   {2, 208, 3, 0.684f}, {2, 192, 4, 0.580f}, {2, 176, 4, 0.586f}, {2, 160, 4, 0.583f}};
+}  // namespace
+
+void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int* bn, int* mh, int* stages,
+                       int* grid) {
+  const int64_t ksteps = (k + kBK - 1) / kBK;
+  double best_cost = 1e300;
+  DenseCfg best = kDenseCfgs[4];
+  for (const DenseCfg& c : kDenseCfgs) {
+    if (forced_bn > 0) {
+      if (c.bn != forced_bn || c.mh != (forced_mh == 2 ? 2 : 1)) continue;
+    } else {
+      if (c.bn > 128 && n < c.bn) continue;
+      if (c.mh == 2 && m <= kBM) continue;
+    }
+    const int64_t t = ((m + kBM * c.mh - 1) / (kBM * c.mh)) * ((n + c.bn - 1) / c.bn);
+    const double main_us = double(ksteps) * c.step_us;
+    const double tile = c.mh == 1 ? std::max(main_us, 0.012 * c.bn + 0.5) + 0.3 : main_us + 0.0094 * c.bn + 0.5;
+    const double cost = double((t + sms - 1) / sms) * tile;
+    if (cost < best_cost) { best_cost = cost; best = c; }
   }
-  *bn = best;
-  *stages = best == 256 ? 4 : best >= 192 ? 5 : 6;
-  const int64_t t = m_tiles * ((n + best - 1) / best);
+  *bn = best.bn; *mh = best.mh; *stages = best.stages;
+  const int64_t t = ((m + kBM * best.mh - 1) / (kBM * best.mh)) * ((n + best.bn - 1) / best.bn);
   *grid = int(std::min<int64_t>(sms, t));
 }
 
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const EpiParams& epi) {
-  int bn, stages, grid;
-  tl_dense_tc_shape(m, n, ctx->sm_count, &bn, &stages, &grid);
+  int bn, mh, stages, grid;
+  const bool forced = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == 2 && ctx->forced.p0 > 0;
+  tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid);
+  if (forced && (bn != ctx->forced.p0 || mh != (ctx->forced.p2 == 2 ? 2 : 1)))
+    return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: no tensor-core tile with BN=%d MH=%d", ctx->forced.p0, ctx->forced.p2);
+  const int tile_m = kBM * mh;
   DenseTcArgs p{};
   p.out = out; p.m = m; p.n = n; p.k = k; p.out_dtype = out_dtype;
-  p.m_tiles = int32_t((m + kBM - 1) / kBM);
+  p.m_tiles = int32_t((m + tile_m - 1) / tile_m);
   p.n_tiles = int32_t((n + bn - 1) / bn);
   p.ksteps = int32_t((k + kBK - 1) / kBK);
   p.status = ctx->dev_status;
   CUtensorMap amap, bmap;
-  if (!tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, kBM, 3) ||
+  if (!tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, uint32_t(tile_m), 3) ||
       !tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3))
     return tl_set_error(ctx, TL_ERR_CUDA, "tl_matmul: cuTensorMapEncodeTiled failed (m=%lld n=%lld k=%lld)", (long long)m,
                         (long long)n, (long long)k);
   cudaError_t e = cudaErrorInvalidValue;
-#define TL_DENSE_CASE(BN_, ST_)                                                                              \
-  if (bn == BN_)                                                                                             \
-    e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_>(grid, ctx->stream, amap, bmap, p, epi)              \
-                        : launch_dense<__nv_bfloat16, BN_, ST_>(grid, ctx->stream, amap, bmap, p, epi);
-  TL_DENSE_CASE(256, 4)
-  TL_DENSE_CASE(224, 5)
-  TL_DENSE_CASE(192, 5)
-  TL_DENSE_CASE(160, 6)
-  TL_DENSE_CASE(128, 6)
+#define TL_DENSE_CASE(MH_, BN_, ST_)                                                                          \
+  if (mh == MH_ && bn == BN_)                                                                                \
+    e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi)         \
+                        : launch_dense<__nv_bfloat16, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi);
+  TL_DENSE_CASE(1, 256, 4)
+  TL_DENSE_CASE(1, 224, 5)
+  TL_DENSE_CASE(1, 192, 5)
+  TL_DENSE_CASE(1, 160, 6)
+  TL_DENSE_CASE(1, 128, 6)
+  TL_DENSE_CASE(2, 256, 3)
+  TL_DENSE_CASE(2, 240, 3)
+  TL_DENSE_CASE(2, 224, 3)
+  TL_DENSE_CASE(2, 208, 3)
+  TL_DENSE_CASE(2, 192, 4)
+  TL_DENSE_CASE(2, 176, 4)
+  TL_DENSE_CASE(2, 160, 4)
 #undef TL_DENSE_CASE
   if (e != cudaSuccess) {
     ctx->async_errors++;
