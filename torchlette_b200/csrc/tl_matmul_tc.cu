@@ -9,11 +9,15 @@
 //         = TMEM columns; BN a multiple of 16 up to 256), 64 k per pipeline stage (one 128-byte swizzled row
 //         per operand row), 4 MMAs of K = 16 per stage and row half;
 //   MH = 1: two accumulators of BN columns, so the epilogue of tile i overlaps the main loop of tile i+1.
-//   MH = 2: both row halves multiply the SAME B tile in shared memory, which halves the B bytes an SM pulls
-//         from L2 per flop -- with 128-row tiles the SM's L2 ingest (about 64 bytes per clock), not the tensor
-//         pipe, sets the pace: (128 + 224) x 128 bytes per 448 MMA clocks is 100 bytes per clock, (256 + 208)
-//         x 128 per 832 is 71.  The two halves fill TMEM (2 x BN columns), so the epilogue (one warp per lane
-//         quarter and half) does not overlap the next tile; it is a few percent when K is in the thousands.
+//   MH = 2: both row halves multiply the SAME B tile in shared memory.  What paces this kernel is the
+//         SM's shared-memory bandwidth (128 bytes per clock), not the tensor pipe: every operand byte is
+//         written once by TMA and read once per MMA that uses it, so a 64-k step of a 128 x 256 tile moves
+//         2 x (16 + 32) KB = 96 KB = 750 clocks for 512 clocks of MMA (measured 0.424 us per step), and a
+//         256 x 256 tile (32 + 32) KB of writes + (32 + 2 x 32) KB of reads = 160 KB for twice the flops
+//         (0.742 us) -- 17 % fewer bytes per flop.  (Sharing B between two SMs with cta_group::2 is the
+//         step that would take the reads down further; this kernel stays within one CTA.)  The two halves
+//         fill TMEM (2 x BN columns), so the epilogue (one warp per lane quarter, half and column half)
+//         does not overlap the next tile; it is a few percent when K is in the thousands.
 //         The host picks MH and BN from a per-tile time model times the number of waves (tl_dense_tc_shape);
 //   warp 0: TMA producer (one elected lane); warp 1: TMEM allocation + MMA issue (one elected lane);
 //   warps 2..17: epilogue, four warps per TMEM lane quarter (MH = 1: each takes a quarter of the columns;
@@ -290,8 +294,9 @@ bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, 
 // p0 of the receipt: BN (columns per tile); p1: stages; p2: MH (row halves per tile).  The choice minimises
 // waves x tile time, waves = ceil(tiles / SMs), with the tile time taken from measurements on B200 (bf16,
 // shapes from 1024^3 to 8192^3): a 64-k step costs `step_us` whatever the shape -- it follows the bytes the
-// SM pulls from L2 per step (86 to 117 GB/s per SM), not the MMA's clocks, which is why 256-row tiles win on
-// large shapes (0.742 us for 256 x 256 against 2 x 0.424 for 128 x 256) and why four stages (BN <= 192 at
+// step moves through shared memory (TMA writes + MMA reads, at about 226 KB per us), not the MMA's clocks,
+// which is why 256-row tiles win on large shapes (0.742 us for 256 x 256 against 2 x 0.424 for 128 x 256);
+// the three-stage tiles run a little under that rate, which is why four stages (BN <= 192 at
 // MH = 2) beat three.  With MH = 1 the epilogue hides behind the next tile unless K is short; with MH = 2
 // it adds to every tile.  E.g. m = 2048, n = 14336, k = 4096 on 148 SMs: 128 x 224 tiles run 7 waves of
 // 27 us, 256 x 208 tiles 4 waves of 46 us.
