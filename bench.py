@@ -366,8 +366,27 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
         ms = C.c_float()
         B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
         tf = 2.0 * m * nn * kk / (ms.value / reps * 1e-3) / 1e12
+        rcpt = B.PlanReceipt()
+        B.check(ctx, lib.tl_plan_qmatmul(ctx, m, nn, kk, B.TL_BF16, B.TL_BF16, C.byref(q), C.byref(e2), C.byref(rcpt)))
         out[f"qgemm_{m}x{kk}x{nn}"] = {"ms": ms.value / reps, "TFLOPs": tf, "frac_of_bf16_peak": tf / tf_peak,
-                                       "epilogue": "gelu, bf16 out"}
+                                       "epilogue": "gelu, bf16 out",
+                                       "variant": lib.tl_variant_name(C.byref(rcpt.choice)).decode()}
+        # both int8 routes on every shape, forced: converting on the operand path (tcgen05, A from TMEM)
+        # against writing the weight out as bf16 once and running the dense kernel
+        for label, forced in (("fused", (B.TL_FAMILY_QGEMM, 0, 192, 128, 3, 8)), ("dequant_dense", (B.TL_FAMILY_QGEMM, 2, 0, 0, 0, 0))):
+            be.forceVariant(forced)
+            try:
+                for _ in range(3):
+                    run()
+                be.sync()
+                B.check(ctx, lib.tl_event_record(ctx, ev0))
+                for _ in range(reps):
+                    run()
+                B.check(ctx, lib.tl_event_record(ctx, ev1))
+                B.check(ctx, lib.tl_event_elapsed_ms(ctx, ev0, ev1, C.byref(ms)))
+                out[f"qgemm_{m}x{kk}x{nn}"][label + "_ms"] = ms.value / reps
+            finally:
+                be.forceVariant(None)
         del w, s, x, y
     # the two small configurations: a 2048 x 2048 f32 GEMV, and the seven 0.6B-shaped decode
     # projections (q, k, v, gate, up on K=1024; o on K=2048; down on K=3072) replayed as ONE

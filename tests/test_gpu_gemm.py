@@ -185,3 +185,89 @@ def test_qgemm_graph_replay(backend):
     be.destroyGraph(graph)
     for t in (out, x, w.scales, w):
         t.destroy()
+
+
+# ---------------------------------------------------------------------------
+# "dequant+dense": the weight written once as a 16-bit matrix into library scratch, then the dense
+# tensor-core kernel with the per-channel scales applied per output column (the reference's own
+# structure for m > 1, matmul-ops.ts:163-181; here the default when tokens per weight byte are many)
+# ---------------------------------------------------------------------------
+DEQUANT_DENSE = (2, 2, 0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("act_dtype", ["bf16", "f16"])
+@pytest.mark.parametrize("m,n,k", [(200, 300, 448), (33, 64, 64), (300, 1000, 2048)])
+def test_qgemm_dequant_dense_per_channel(backend, act_dtype, m, n, k):
+    got, ref = _gemm_case(backend, m, n, k, act_dtype, "f32", DEQUANT_DENSE, bias=True, act="gelu", seed=5)
+    assert cases.rel_err(got, ref) <= 1e-3  # q enters the tensor core exactly, the scale meets the f32 accumulator
+    got, ref = _gemm_case(backend, m, n, k, act_dtype, act_dtype, DEQUANT_DENSE, seed=6)
+    assert cases.rel_err(got, ref) <= 1e-2
+    assert backend.getGpuUncapturedErrorCount() == 0
+
+
+@pytest.mark.parametrize("group", [64, 128])
+@pytest.mark.parametrize("act_dtype", ["f16", "bf16"])
+def test_qgemm_dequant_dense_grouped_matches_the_fused_kernel(backend, group, act_dtype):
+    be = backend
+    m, n, k = 96, 260, 512
+    rng = np.random.default_rng(group + 1)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x = rng.standard_normal((m, k)).astype(np.float32)
+    xb = x.astype(np.float16) if act_dtype == "f16" else orc.bf16_bits_rne(x)
+    xv = xb.astype(np.float32) if act_dtype == "f16" else orc.bf16_bits_to_f32(xb)
+    packed, scales = be.quantizeLinearWeight(w, group)
+    wt = be.createQuantizedWeight(packed, scales, n, k, tb.resolveWeightFormat(f"int8-{group}", act_dtype))
+    xt = be.ops.tensorFromArray(xb, [m, k], act_dtype)
+    outs = []
+    for variant in (DEQUANT_DENSE, None):
+        be.forceVariant(variant)
+        try:
+            y = be.linear(xt, wt)
+        finally:
+            be.forceVariant(None)
+        outs.append(np.asarray(be.ops.read(y), dtype=np.float32))
+        y.destroy()
+    w32 = orc.dequantize_to_f32(packed, scales, k, group)
+    w16 = w32.astype(np.float16).astype(np.float32) if act_dtype == "f16" else orc.bf16_bits_to_f32(orc.bf16_bits_rne(w32))
+    assert cases.rel_err(outs[0], orc.matmul_nt(xv, w16)) <= 1e-2  # the fused kernel's own bound for grouped scales
+    assert cases.rel_err(outs[0], outs[1]) <= 1e-4                 # same operand arithmetic as the fused converters: only the summation order differs
+    for t in (xt, wt.scales, wt):
+        t.destroy()
+
+
+def test_qgemm_default_goes_dense_only_when_tokens_per_weight_are_many(backend):
+    be = backend
+    fmt = tb.perChannelFormat(14336).packing
+    assert ".dequant+dense" in be.planQuantizedMatmul(2048, 4096, 14336, "bf16", "bf16", fmt)["variant"]
+    fmt = tb.perChannelFormat(4096).packing
+    assert ".tcgen05" in be.planQuantizedMatmul(2048, 14336, 4096, "bf16", "bf16", fmt)["variant"]
+    assert ".tcgen05" in be.planQuantizedMatmul(512, 14336, 4096, "bf16", "bf16", fmt)["variant"]
+    assert ".dequant+dense" in be.planQuantizedMatmul(8192, 4096, 4096, "bf16", "bf16", fmt)["variant"]
+    g128 = tb.resolveWeightFormat("int8-128", "bf16").packing
+    assert ".dequant+dense" in be.planQuantizedMatmul(2048, 14336, 4096, "bf16", "bf16", g128)["variant"]
+    assert ".tcgen05" in be.planQuantizedMatmul(128, 14336, 4096, "bf16", "bf16", g128)["variant"]
+
+
+def test_qgemm_dequant_dense_graph_replay(backend):
+    be = backend
+    m, n, k = 256, 512, 512
+    cs = cases.per_channel_case(n, k, m, seed=9, act_dtype="bf16")
+    w = be.createQuantizedWeight(cs["packed"], cs["scales"], n, k, tb.perChannelFormat(k))
+    x = be.ops.tensorFromArray(cs["x_bits"], [m, k], "bf16")
+    out = be.ops.empty([m, n], "f32")
+    wT = be.ops.transpose(w)
+    be.forceVariant(DEQUANT_DENSE)
+    try:
+        be.ops.matmul(x, wT, {"outBuffer": out})  # sizes the scratch outside the capture
+        be.beginCapture()
+        be.ops.matmul(x, wT, {"outBuffer": out})
+        graph = be.endCapture()
+    finally:
+        be.forceVariant(None)
+    be._lib.tl_memset(be._ctx, out.buffer, 0, out.nbytes)
+    be.replay(graph)
+    ref = orc.matmul_nt(cs["x"], orc.dequantize_direct_f32(cs["packed"], cs["scales"], k, k))
+    assert cases.rel_err(be.ops.read(out), ref) <= 1e-3
+    be.destroyGraph(graph)
+    for t in (out, x, w.scales, w):
+        t.destroy()

@@ -46,6 +46,11 @@ struct DenseTcArgs {
   int32_t out_dtype;
   int32_t m_tiles, n_tiles, ksteps;
   int* status;
+  // optional factor per output column, applied to the accumulator before the op chain (the per-channel
+  // scales of a dequantized int8 weight whose 16-bit copy holds q itself): value = colscale[col] * colscale_mul
+  const void* colscale;
+  int32_t colscale_dtype;
+  float colscale_mul;
 };
 
 template <typename T> struct OperandFmt;
@@ -202,6 +207,10 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (ch + 1 < cend) tmem_ld16(tmem_base + lane_addr + acc_col + uint32_t((ch + 1) * 16), vn);  // next chunk in flight
         if (!row_ok || col0 >= p.n) continue;
         const int jmax = int(min(int64_t(16), p.n - col0));
+        if (p.colscale) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] *= j < jmax ? tl_load_scale(p.colscale, p.colscale_dtype, col0 + j) * p.colscale_mul : 0.f;
+        }
         if (mode != kGeneric) {
           if (bias) {
 #pragma unroll
@@ -330,8 +339,23 @@ void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, 
   *grid = int(std::min<int64_t>(sms, t));
 }
 
+// The modelled time of the launch tl_launch_dense_tc would make, in microseconds (selection between this
+// kernel and others is made on it).
+double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms) {
+  int bn, mh, stages, grid;
+  tl_dense_tc_shape(m, n, k, sms, 0, 0, &bn, &mh, &stages, &grid);
+  for (const DenseCfg& c : kDenseCfgs) {
+    if (c.bn != bn || c.mh != mh) continue;
+    const int64_t t = ((m + kBM * c.mh - 1) / (kBM * c.mh)) * ((n + c.bn - 1) / c.bn);
+    const double main_us = double((k + kBK - 1) / kBK) * c.step_us;
+    const double tile = c.mh == 1 ? std::max(main_us, 0.012 * c.bn + 0.5) + 0.3 : main_us + 0.0094 * c.bn + 0.5;
+    return double((t + sms - 1) / sms) * tile;
+  }
+  return 1e30;
+}
+
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
-                           int32_t out_dtype, const EpiParams& epi) {
+                           int32_t out_dtype, const EpiParams& epi, const void* colscale, int32_t colscale_dtype, float colscale_mul) {
   int bn, mh, stages, grid;
   const bool forced = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == 2 && ctx->forced.p0 > 0;
   tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid);
@@ -344,6 +368,7 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   p.n_tiles = int32_t((n + bn - 1) / bn);
   p.ksteps = int32_t((k + kBK - 1) / kBK);
   p.status = ctx->dev_status;
+  p.colscale = colscale; p.colscale_dtype = colscale_dtype; p.colscale_mul = colscale_mul;
   CUtensorMap amap, bmap;
   if (!tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, uint32_t(tile_m), 3) ||
       !tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3))

@@ -97,6 +97,49 @@ template <> struct Cvt<__nv_bfloat16> {
   }
 };
 
+// Sixteen int8 (one 16-byte chunk of a weight row) -> eight packed 16-bit pairs: q itself, exactly, or
+// q * sc in f32 with one rounding to the operand type (the oracle's dequantize-then-round).
+template <typename AT>
+__device__ __forceinline__ void cvt16(const uint4& raw, bool scaled, float sc, uint32_t (&v)[8]) {
+  const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
+  if (scaled) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t x = w4[j] ^ 0x80808080u;
+      const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
+      const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
+      const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
+      const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
+      v[2 * j] = Cvt<AT>::pack(f0, f1);
+      v[2 * j + 1] = Cvt<AT>::pack(f2, f3);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) Cvt<AT>::word(w4[j], v[2 * j], v[2 * j + 1]);
+  }
+}
+
+// The weight as a 16-bit [N, K] matrix in scratch, for the dense kernel (variant "dequant+dense"):
+// per-channel weights as q itself (the scale is applied per output column in that kernel's epilogue,
+// as the fused kernel does), grouped weights as round(q * scale), the fused converters' arithmetic.
+template <typename AT, bool GROUPED>
+__global__ void __launch_bounds__(256)
+dequant_int8_16_kernel(const uint4* __restrict__ packed, const void* __restrict__ scales, int scales_dtype, float wscale, int group,
+                       int groups_per_row, int64_t k, int64_t n_chunks, uint4* __restrict__ out) {
+  for (int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += int64_t(gridDim.x) * blockDim.x) {
+    const uint4 raw = __ldcs(packed + c);
+    float sc = 1.f;
+    if (GROUPED) {
+      const int64_t e = c * 16, row = e / k;
+      sc = tl_load_scale(scales, scales_dtype, row * groups_per_row + (e - row * k) / group) * wscale;
+    }
+    uint32_t v[8];
+    cvt16<AT>(raw, GROUPED, sc, v);
+    out[2 * c] = make_uint4(v[0], v[1], v[2], v[3]);
+    out[2 * c + 1] = make_uint4(v[4], v[5], v[6], v[7]);
+  }
+}
+
 // One unary op over sixteen accumulators.  The op and the precision are resolved once, so
 // each case is a straight run of sixteen independent chains.
 template <int OP, bool APPROX>
@@ -513,7 +556,7 @@ qgemm_tc_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant_
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-constexpr int kTc = 0, kSliced = 1;
+constexpr int kTc = 0, kSliced = 1, kDequantDense = 2;
 
 struct TcConfig { int bn, kstep, stages, ncw; };
 // the instantiated tile configurations (tl_variant p0..p3)
@@ -572,13 +615,15 @@ bool tl_qgemm_variant_applicable(const tl_variant& v, int64_t m, int64_t n, int6
   (void)n;
   if (v.family != TL_FAMILY_QGEMM || m < 1) return false;
   if (v.kernel == kSliced) return true;
+  if (v.kernel == kDequantDense)
+    return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0 &&
+           tl_dense_tc_applicable(nullptr, nullptr, m, n, k, a_dtype, a_dtype) && uint64_t(n) * uint64_t(k) * 2 <= (uint64_t(4) << 30);
   if (v.kernel != kTc) return false;
   return (a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0 && tc_config_known(v);
 }
 
 int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_t a_dtype,
                                  const tl_quant_desc& q, tl_variant* out) {
-  (void)ctx; (void)n;
   tl_variant v{};
   v.family = TL_FAMILY_QGEMM;
   if ((a_dtype == TL_F16 || a_dtype == TL_BF16) && k % 16 == 0 && q.group_size % 16 == 0) {
@@ -592,6 +637,22 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
       const int64_t pad192 = (m + 191) / 192 * 192, pad128 = (m + 127) / 128 * 128;
       if (pad192 * 3 <= pad128 * 4) { v.p0 = 192; v.p1 = 128; v.p2 = 3; v.p3 = 8; }
       else { v.p0 = 128; v.p1 = 128; v.p2 = 4; v.p3 = 8; }
+      // With many tokens per weight byte, writing the weight out once as a 16-bit matrix and running the
+      // dense kernel (whose operands both come from shared memory at its full tile sizes) beats converting
+      // on the operand path: compare the modelled times.  Fused: 0.87 us per 128-k step of a 128 x 192 tile
+      // (measured; 1.4 us with group scales), the last partial wave cut along K; dequantization: 3 bytes of
+      // HBM traffic per weight at the 4 TB/s that pass was measured at.  E.g. 2048 tokens: n = 4096,
+      // k = 14336 runs 200 us this way against 229 us fused, n = 14336, k = 4096 237 against 229 (stays fused),
+      // the same with groups of 128 218 against 368; 8192 tokens x 4096 x 4096: 231 against 284.
+      tl_variant dd{TL_FAMILY_QGEMM, kDequantDense, 0, 0, 0, 0};
+      if (v.p0 == 192 && tl_qgemm_variant_applicable(dd, m, n, k, a_dtype, q)) {
+        const int sms = ctx ? ctx->sm_count : 148;
+        const double tiles = double((n + kTileRows - 1) / kTileRows) * double((m + 191) / 192);
+        const double waves = std::max(1.0, std::ceil(tiles / sms * 4.0) / 4.0);
+        const double fused_us = waves * double((k + 127) / 128) * (q.group_size != k ? 1.4 : 0.87);  // group scales: an f32 multiply per weight
+        const double dense_us = tl_dense_tc_cost_us(m, n, k, sms) + double(n) * double(k) * 3.0 / 4.0e6 + 6.0;
+        if (dense_us < 0.92 * fused_us) v = dd;
+      }
     }
   } else {
     v.kernel = kSliced;  // f32 activations or odd K: sixteen-row slices through the small-batch kernels
@@ -606,7 +667,11 @@ int32_t tl_qgemm_candidates(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, int32_
   tl_qgemm_default_variant(ctx, m, n, k, a_dtype, q, &d);
   out->clear();
   out->push_back(d);
-  if (d.kernel != kTc) return TL_OK;
+  if (d.kernel == kSliced) return TL_OK;
+  {
+    tl_variant dd{TL_FAMILY_QGEMM, kDequantDense, 0, 0, 0, 0};
+    if (d.kernel != kDequantDense && m >= 256 && tl_qgemm_variant_applicable(dd, m, n, k, a_dtype, q)) out->push_back(dd);
+  }
   for (const auto& c : kTcConfigs) {
     if (c.bn < 64 && m > 4 * c.bn) continue;  // narrow token tiles re-stream the weight too often
     tl_variant v{TL_FAMILY_QGEMM, kTc, c.bn, c.kstep, c.stages, c.ncw};
@@ -624,6 +689,39 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
     return tl_set_error(ctx, TL_ERR_UNSUPPORTED, "qgemm: variant %s cannot run m=%lld n=%lld k=%lld G=%d %s",
                         tl_variant_name(&v), (long long)m, (long long)n, (long long)k, q.group_size,
                         tl_dtype_name(a_dtype));
+  if (v.kernel == kDequantDense) {
+    if (receipt) {
+      receipt->choice = v;
+      int bn, mh, stages, grid;
+      tl_dense_tc_shape(m, n, k, ctx->sm_count, 0, 0, &bn, &mh, &stages, &grid);
+      receipt->choice.p0 = bn; receipt->choice.p1 = stages; receipt->choice.p2 = mh;
+      receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
+      receipt->block = 576; receipt->split_k = 1;
+      return TL_OK;
+    }
+    if ((reinterpret_cast<uintptr_t>(packed) & 15) || (reinterpret_cast<uintptr_t>(a) & 15))
+      return tl_set_error(ctx, TL_ERR_INVALID_ARG, "qgemm: weight and activation pointers must be 16-byte aligned");
+    void* wbuf = nullptr;
+    int32_t rc = tl_ensure_scratch(ctx, size_t(n) * size_t(k) * 2, &wbuf);
+    if (rc != TL_OK) return rc;
+    const bool grouped = q.group_size != k;
+    const float wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
+    const int64_t n_chunks = n * k / 16;
+    const int grid = int(std::min<int64_t>((n_chunks + 255) / 256, int64_t(ctx->sm_count) * 8));
+    const uint4* pk = static_cast<const uint4*>(packed);
+    uint4* wo = static_cast<uint4*>(wbuf);
+    const int gpr = int(k / q.group_size);
+    if (a_dtype == TL_F16) {
+      if (grouped) dequant_int8_16_kernel<__half, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+      else dequant_int8_16_kernel<__half, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+    } else {
+      if (grouped) dequant_int8_16_kernel<__nv_bfloat16, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+      else dequant_int8_16_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+    }
+    TL_CUDA(ctx, cudaGetLastError());
+    ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
+    return tl_launch_dense_tc(ctx, a, wbuf, out, m, n, k, a_dtype, out_dtype, epi, grouped ? nullptr : scales, q.scales_dtype, wscale);
+  }
   if (v.kernel == kSliced) {
     if (receipt) {
       receipt->choice = v;
