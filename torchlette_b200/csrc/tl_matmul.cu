@@ -143,7 +143,9 @@ __global__ void __launch_bounds__(512) dense_gemv_kernel(MatmulArgs p, EpiParams
     for (int e = 0; e < 4; ++e) c[nt][e] = 0.f;
   const int kblocks = p.k >> 5;  // 32 k per block
   // (Requesting four blocks' weights before using the first measured SLOWER, 33.7 vs 29.3 us on
-  // 4096 x 14336: the extra registers cost a resident CTA.)
+  // 4096 x 14336: the extra registers cost a resident CTA.  So did a per-thread cp.async ring of 8
+  // slots: 28.9 us at m = 1, 46-49 us at m = 8 and 16, where the activation loads then wait behind
+  // the ring's wait_group.)
   for (int kb = warp; kb < kblocks; kb += warps) {
     const uint4 wl = __ldg(reinterpret_cast<const uint4*>(w_lo + kb * 32));
     const uint4 wh = __ldg(reinterpret_cast<const uint4*>(w_hi + kb * 32));
@@ -230,6 +232,11 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
   if (use_gemv) {
     const int kblocks = int(k / 32);
     warps = kblocks >= 16 ? 16 : kblocks >= 8 ? 8 : kblocks >= 4 ? 4 : kblocks >= 2 ? 2 : 1;
+    if (m > 8 && warps > 4) warps = 4;  // two batch tiles: 31.7 us against 36.2 with 16 warps on 4096 x 14336
+    // A/B hook: {TL_FAMILY_MATMUL, 1, warps} forces the CTA width
+    if (ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == kGemv && ctx->forced.p0 >= 1 &&
+        ctx->forced.p0 <= 16 && (ctx->forced.p0 & (ctx->forced.p0 - 1)) == 0)
+      warps = ctx->forced.p0;
   }
   const bool forced_tc = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == kTc;
   const size_t esz_ab = 2;
