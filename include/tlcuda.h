@@ -319,7 +319,17 @@ TL_API int32_t tl_decode_attention(tl_ctx* ctx, const void* q, const void* k_cac
 /* ---- selection: planTiledMatmul / selectMatmulChoice / SelectionReceipt
  * (src/backend/webgpu/matmul/dispatch.ts:171-192, 1130-1329;
  *  src/backend/webgpu/matmul/variants.ts:54-260) ------------------------------ */
-enum { TL_FAMILY_QGEMV = 1, TL_FAMILY_QGEMM = 2, TL_FAMILY_MATMUL = 3 /* dense: 0 tiled, 1 gemv */ };
+/* Kernel ids and parameters by family (tl_variant_name prints them):
+ *   TL_FAMILY_QGEMV  (m <= 16): 0 scalar, 1 simt, 2 mma, 3 sk, 4 ring (default; p0 warps, p1 k blocks in flight,
+ *                    p2 = 2: 32-row tiles), 5 tma, 6 bulk, 7 chain, 8 stream, 9 int4
+ *   TL_FAMILY_QGEMM  (m > 16): 0 tcgen05 with the int8 -> 16-bit conversion on the operand path (p0 token tile,
+ *                    p1 k per stage, p2 stages, p3 converter warps); 1 sliced (sixteen-row slices through the
+ *                    small-batch kernels: f32 activations, odd K); 2 dequant+dense (the weight written once as a
+ *                    16-bit matrix into scratch, then the dense tcgen05 kernel; receipt: p0 BN, p1 stages, p2 MH)
+ *   TL_FAMILY_MATMUL (dense): 0 tiled (CUDA cores, always applicable), 1 gemv (m <= 16 NT; p0 warps),
+ *                    2 tc (tcgen05, both operands from shared memory; p0 BN columns per tile, p1 stages,
+ *                    p2 MH = row halves of 128 per tile; forcing with p0 = 0 leaves the tile to the library) */
+enum { TL_FAMILY_QGEMV = 1, TL_FAMILY_QGEMM = 2, TL_FAMILY_MATMUL = 3 };
 typedef struct tl_variant {
   int32_t family;   /* TL_FAMILY_* */
   int32_t kernel;   /* family-specific kernel id (see tl_variant_name) */

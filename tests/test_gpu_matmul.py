@@ -422,3 +422,24 @@ def test_dense_tensor_core_unary_modes_on_two_half_tiles(backend, out_dtype, act
         be.forceVariant(None)
     for t in (x, w, y):
         t.destroy()
+
+
+def test_dense_tensor_core_full_size_sampled_rows(backend):
+    """The benchmark's dense shape (2048 x 4096 -> 14336, bf16, gelu, bf16 out) with the tile the library picks
+    for it; the oracle runs on token rows that cover every 128- and 256-row tile edge, over all N."""
+    be = backend
+    m, k, n = 2048, 4096, 14336
+    rng = np.random.default_rng(17)
+    x, x_v = _to_dev(be, rng.standard_normal(m * k, dtype=np.float32), [m, k], "bf16")
+    w, w_v = _to_dev(be, rng.standard_normal(n * k, dtype=np.float32) * np.float32(0.02), [n, k], "bf16")
+    plan = tb.detectMatmulEpilogue([("gelu", None), ("cast", "bf16")])
+    receipt = be.planMatmul(m, n, k, "bf16", "bf16", transB=True)
+    assert receipt["variant"].startswith("matmul.tc")
+    y = be.ops.matmul(x, be.ops.transpose(w), {"epilogue": plan[0], "epilogueInputs": plan[1]})
+    got = _read_f32(be, y)
+    rows = sorted({0, 1, 127, 128, 129, 255, 256, 257, 1023, 1024, 1919, 1920, 2046, 2047} |
+                  set(rng.integers(0, m, 10).tolist()))
+    ref = _ref(x_v[rows], w_v.T, None, "gelu")
+    assert _rel(got[rows], ref) <= 1e-2
+    for t in (x, w, y):
+        t.destroy()
