@@ -97,46 +97,46 @@ template <> struct Cvt<__nv_bfloat16> {
   }
 };
 
-// Sixteen int8 (one 16-byte chunk of a weight row) -> eight packed 16-bit pairs: q itself, exactly, or
-// q * sc in f32 with one rounding to the operand type (the oracle's dequantize-then-round).
-template <typename AT>
-__device__ __forceinline__ void cvt16(const uint4& raw, bool scaled, float sc, uint32_t (&v)[8]) {
-  const uint32_t w4[4] = {raw.x, raw.y, raw.z, raw.w};
-  if (scaled) {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t x = w4[j] ^ 0x80808080u;
-      const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
-      const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
-      const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
-      const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
-      v[2 * j] = Cvt<AT>::pack(f0, f1);
-      v[2 * j + 1] = Cvt<AT>::pack(f2, f3);
-    }
-  } else {
-#pragma unroll
-    for (int j = 0; j < 4; ++j) Cvt<AT>::word(w4[j], v[2 * j], v[2 * j + 1]);
-  }
-}
-
 // The weight as a 16-bit [N, K] matrix in scratch, for the dense kernel (variant "dequant+dense"):
 // per-channel weights as q itself (the scale is applied per output column in that kernel's epilogue,
 // as the fused kernel does), grouped weights as round(q * scale), the fused converters' arithmetic.
 template <typename AT, bool GROUPED>
 __global__ void __launch_bounds__(256)
-dequant_int8_16_kernel(const uint4* __restrict__ packed, const void* __restrict__ scales, int scales_dtype, float wscale, int group,
-                       int groups_per_row, int64_t k, int64_t n_chunks, uint4* __restrict__ out) {
-  for (int64_t c = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; c < n_chunks; c += int64_t(gridDim.x) * blockDim.x) {
-    const uint4 raw = __ldcs(packed + c);
-    float sc = 1.f;
-    if (GROUPED) {
-      const int64_t e = c * 16, row = e / k;
-      sc = tl_load_scale(scales, scales_dtype, row * groups_per_row + (e - row * k) / group) * wscale;
+dequant_int8_16_kernel(const uint2* __restrict__ packed, const void* __restrict__ scales, int scales_dtype, float wscale, int group,
+                       int groups_per_row, int64_t k, int64_t n_oct, uint4* __restrict__ out) {
+  // One octet (8 weights: 8 bytes in, 16 bytes out) per thread and step, so that a warp's loads AND its
+  // stores are each one contiguous run; four independent steps in flight.
+  const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+  for (int64_t o0 = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; o0 < n_oct; o0 += 4 * stride) {
+    uint2 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u)
+      if (o0 + u * stride < n_oct) raw[u] = __ldcs(packed + o0 + u * stride);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int64_t o = o0 + u * stride;
+      if (o >= n_oct) break;
+      uint32_t v[4];
+      if (GROUPED) {
+        const int64_t e = o * 8, row = e / k;
+        const float sc = tl_load_scale(scales, scales_dtype, row * groups_per_row + (e - row * k) / group) * wscale;
+        const uint32_t w2[2] = {raw[u].x, raw[u].y};
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint32_t x = w2[j] ^ 0x80808080u;
+          const float f0 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7650)) - 8388736.f) * sc;
+          const float f1 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7651)) - 8388736.f) * sc;
+          const float f2 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7652)) - 8388736.f) * sc;
+          const float f3 = (__uint_as_float(__byte_perm(x, 0x4B000000u, 0x7653)) - 8388736.f) * sc;
+          v[2 * j] = Cvt<AT>::pack(f0, f1);
+          v[2 * j + 1] = Cvt<AT>::pack(f2, f3);
+        }
+      } else {
+        Cvt<AT>::word(raw[u].x, v[0], v[1]);
+        Cvt<AT>::word(raw[u].y, v[2], v[3]);
+      }
+      out[o] = make_uint4(v[0], v[1], v[2], v[3]);
     }
-    uint32_t v[8];
-    cvt16<AT>(raw, GROUPED, sc, v);
-    out[2 * c] = make_uint4(v[0], v[1], v[2], v[3]);
-    out[2 * c + 1] = make_uint4(v[4], v[5], v[6], v[7]);
   }
 }
 
@@ -641,8 +641,8 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
       // dense kernel (whose operands both come from shared memory at its full tile sizes) beats converting
       // on the operand path: compare the modelled times.  Fused: 0.87 us per 128-k step of a 128 x 192 tile
       // (measured; 1.4 us with group scales), the last partial wave cut along K; dequantization: 3 bytes of
-      // HBM traffic per weight at the 4 TB/s that pass was measured at.  E.g. 2048 tokens: n = 4096,
-      // k = 14336 runs 200 us this way against 229 us fused, n = 14336, k = 4096 237 against 229 (stays fused),
+      // HBM traffic per weight at the 4.4 TB/s that pass was measured at (40 us for 14336 x 4096; the model keeps 4).  E.g. 2048 tokens: n = 4096,
+      // k = 14336 runs 200 us this way against 229 us fused, n = 14336, k = 4096 228 against 229 (stays fused),
       // the same with groups of 128 218 against 368; 8192 tokens x 4096 x 4096: 231 against 284.
       tl_variant dd{TL_FAMILY_QGEMM, kDequantDense, 0, 0, 0, 0};
       if (v.p0 == 192 && tl_qgemm_variant_applicable(dd, m, n, k, a_dtype, q)) {
@@ -706,17 +706,17 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
     if (rc != TL_OK) return rc;
     const bool grouped = q.group_size != k;
     const float wscale = q.scale_convention == TL_SCALE_SNORM127 ? 1.0f / 127.0f : 1.0f;
-    const int64_t n_chunks = n * k / 16;
-    const int grid = int(std::min<int64_t>((n_chunks + 255) / 256, int64_t(ctx->sm_count) * 8));
-    const uint4* pk = static_cast<const uint4*>(packed);
+    const int64_t n_oct = n * k / 8;
+    const int grid = int(std::min<int64_t>((n_oct + 1023) / 1024, int64_t(ctx->sm_count) * 8));
+    const uint2* pk = static_cast<const uint2*>(packed);
     uint4* wo = static_cast<uint4*>(wbuf);
     const int gpr = int(k / q.group_size);
     if (a_dtype == TL_F16) {
-      if (grouped) dequant_int8_16_kernel<__half, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
-      else dequant_int8_16_kernel<__half, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+      if (grouped) dequant_int8_16_kernel<__half, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_oct, wo);
+      else dequant_int8_16_kernel<__half, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_oct, wo);
     } else {
-      if (grouped) dequant_int8_16_kernel<__nv_bfloat16, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
-      else dequant_int8_16_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_chunks, wo);
+      if (grouped) dequant_int8_16_kernel<__nv_bfloat16, true><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_oct, wo);
+      else dequant_int8_16_kernel<__nv_bfloat16, false><<<grid, 256, 0, ctx->stream>>>(pk, scales, q.scales_dtype, wscale, q.group_size, gpr, k, n_oct, wo);
     }
     TL_CUDA(ctx, cudaGetLastError());
     ctx->counters[TL_COUNTER_KERNEL_LAUNCHES]++;
