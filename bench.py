@@ -329,7 +329,7 @@ def single_matrix_extras(be, hbm_peak, tf_peak):
     out["dense_tc_bf16_2048x4096x14336_nt_gelu"] = dict(time_dense(2048, 14336, 4096, True, B.TL_BF16, torch.bfloat16, C.byref(eg)),
                                                         kernel="tcgen05, A and B from shared memory")
     out["dense_tc_f16_2048x2048x2048_nn"] = dict(time_dense(2048, 2048, 2048, False, B.TL_F16, torch.float16, None),
-                                                 kernel="tcgen05 after one transposition pass over B")
+                                                 kernel="tcgen05, B stored [K, N] and multiplied MN-major as it lies (no transposed copy)")
     be.forceVariant((B.TL_FAMILY_MATMUL, 0, 0, 0, 0, 0))
     try:
         out["dense_tiled_f16_2048x2048x2048"] = dict(time_dense(2048, 2048, 2048, False, B.TL_F16, torch.float16, None, reps=3),

@@ -443,3 +443,47 @@ def test_dense_tensor_core_full_size_sampled_rows(backend):
     assert _rel(got[rows], ref) <= 1e-2
     for t in (x, w, y):
         t.destroy()
+
+
+@pytest.mark.parametrize("bn,mh", [(128, 1), (192, 1), (256, 1), (192, 2), (256, 2)])
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_dense_tensor_core_nn_layout_without_a_transposed_copy(backend, bn, mh, dtype):
+    """matmul(a, b) with b stored [K, N]: the tensor-core kernel stages and multiplies B MN-major (64-column
+    slabs), so nothing is transposed into scratch.  Ragged m, n, k; bias + gelu; bit-exact on representable inputs."""
+    be = backend
+    m, k, n = 300, 200, 1000
+    rng = np.random.default_rng(bn + mh)
+    a, a_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], dtype)
+    b, b_v = _to_dev(be, (rng.uniform(-1, 1, k * n) * 0.2).astype(np.float32), [k, n], dtype)
+    bias_v = rng.uniform(-1, 1, n).astype(np.float32)
+    bias_t = be.ops.tensorFromArray(bias_v, [n], "f32")
+    plan = tb.detectMatmulEpilogue([("add", bias_t), ("gelu", None)])
+    be.forceVariant((B.TL_FAMILY_MATMUL, 2, bn, 0, mh, 0))
+    try:
+        launches0 = be.getKernelLaunchCount()
+        y = be.ops.matmul(a, b, {"epilogue": plan[0], "epilogueInputs": plan[1]})
+        assert be.getKernelLaunchCount() == launches0 + 1  # one kernel: no transposition pass in front of it
+        assert _rel(_read_f32(be, y), _ref(a_v, b_v, bias_v, "gelu")) <= 1e-2
+        ap, ap_v = _to_dev(be, _pattern(m * k, 0), [m, k], dtype)
+        bp, bp_v = _to_dev(be, _pattern(k * n, 3), [k, n], dtype)
+        yp = be.ops.matmul(ap, bp)
+        np.testing.assert_array_equal(_read_f32(be, yp), _ref(ap_v, bp_v))
+    finally:
+        be.forceVariant(None)
+    for t in (a, b, bias_t, y, ap, bp, yp):
+        t.destroy()
+
+
+def test_dense_tensor_core_nn_layout_odd_n_takes_the_transposition_pass(backend):
+    be = backend
+    m, k, n = 160, 128, 1001  # a row pitch of 2002 bytes cannot be a TMA map
+    rng = np.random.default_rng(3)
+    a, a_v = _to_dev(be, rng.uniform(-1, 1, m * k).astype(np.float32), [m, k], "f16")
+    b, b_v = _to_dev(be, rng.uniform(-1, 1, k * n).astype(np.float32), [k, n], "f16")
+    assert be.planMatmul(m, n, k, "f16", "f16")["variant"].startswith("matmul.tc")
+    launches0 = be.getKernelLaunchCount()
+    y = be.ops.matmul(a, b)
+    assert be.getKernelLaunchCount() == launches0 + 2  # transposition, then the NT kernel
+    assert _rel(_read_f32(be, y), _ref(a_v, b_v)) <= 1e-3
+    for t in (a, b, y):
+        t.destroy()

@@ -257,7 +257,8 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     if (use_tc) {
       int bn, mh, stages, grid;
       const bool f = forced_tc && ctx->forced.p0 > 0;
-      tl_dense_tc_shape(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid);
+      tl_dense_tc_shape(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
+                        (!trans_b && n % 8 == 0 && n >= 128) ? 64 : 16);
       receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages; receipt_only->choice.p2 = mh;
       receipt_only->grid[0] = grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
       receipt_only->block = 576;
@@ -284,7 +285,9 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     if (has_ops) ctx->counters[TL_COUNTER_QGEMV_EPILOGUE]++;
   } else if (use_tc) {
     // bring the operands to the NT layout (A [M, K], B [N, K]) in scratch where they are stored transposed
-    const size_t a_elems = p.trans_a ? size_t(m) * k : 0, b_elems = p.trans_b ? 0 : size_t(n) * k;
+    // a B stored [K, N] is multiplied as it lies (MN-major tiles) when its row pitch allows a TMA map
+    const bool b_mn = !p.trans_b && n % 8 == 0 && n >= 128;
+    const size_t a_elems = p.trans_a ? size_t(m) * k : 0, b_elems = (p.trans_b || b_mn) ? 0 : size_t(n) * k;
     uint8_t* scratch = nullptr;
     if (a_elems + b_elems) {
       void* sp = nullptr;
@@ -301,11 +304,12 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
         if (rc != TL_OK) return rc;
       }
       uint8_t* bt = scratch + ((a_elems * 2 + 255) & ~size_t(255));
-      if (!p.trans_b && (bi == 0 || stride_b != 0)) {
+      if (!p.trans_b && !b_mn && (bi == 0 || stride_b != 0)) {
         rc = tl_transpose2d(ctx, bb, bt, 1, k, n, 2);       // stored [K, N] -> [N, K]
         if (rc != TL_OK) return rc;
       }
-      rc = tl_launch_dense_tc(ctx, p.trans_a ? scratch : ab, p.trans_b ? bb : bt, ob, m, n, k, dtype_a, out_dtype, epi);
+      rc = tl_launch_dense_tc(ctx, p.trans_a ? scratch : ab, (p.trans_b || b_mn) ? bb : bt, ob, m, n, k, dtype_a, out_dtype, epi, nullptr,
+                              0, 1.0f, b_mn);
       if (rc != TL_OK) return rc;
     }
     ctx->counters[TL_COUNTER_MATMUL]++;

@@ -3,7 +3,8 @@
 // tcgen05.mma through 128-byte-swizzle descriptors; f32 accumulators in TMEM, double buffered, the
 // epilogue written straight from TMEM.  The large-M kernel of tl_matmul; replaces the reference's
 // tiled matmul body + epilogue (src/schedule/matmul-skeleton.ts:738-966) for the NT layout that
-// `linear` produces (other layouts are brought to it by one transposition pass, see tl_matmul).
+// `linear` produces and for the NN layout (B stored [K, N], multiplied MN-major as it lies); an A stored
+// [K, M] is brought to [M, K] by one transposition pass, see tl_matmul.
 //
 //   tile: 128 x MH rows of A (tokens, = TMEM lanes; MH = 1 or 2 row halves) x BN rows of B (output columns,
 //         = TMEM columns; BN a multiple of 16 up to 256), 64 k per pipeline stage (one 128-byte swizzled row
@@ -65,7 +66,22 @@ __device__ __noinline__ float dense_epilogue_outlined(const EpiParams& e, float 
   return tl_apply_epilogue(e, v, row, col, n);
 }
 
-template <typename AT, int BN, int STAGES, int MH>
+// MN-major operand descriptor, 128-byte swizzle: the operand is stored [k][n] (n contiguous), staged as
+// 64-column slabs of [64 k x 128 bytes]; 8-k groups 1024 bytes apart (stride offset), slabs `slab_bytes`
+// apart (leading offset).
+__device__ __forceinline__ uint64_t dense_mn_desc(uint32_t smem_addr, uint32_t slab_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr >> 4) & 0x3fffu);
+  d |= uint64_t((slab_bytes >> 4) & 0x3fffu) << 16;
+  d |= uint64_t((1024 >> 4) & 0x3fff) << 32;
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;
+  return d;
+}
+
+// BMN = 1: B is stored [K, N] (the NN layout of matmul(a, b)); its tiles are staged and multiplied MN-major,
+// so no transposed copy of B is made.  BN must then be a multiple of 64.
+template <typename AT, int BN, int STAGES, int MH, int BMN>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, DenseTcArgs p, EpiParams epi) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
@@ -74,8 +90,10 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   constexpr int kABytes = kTileM * 128, kBBytes = BN * 128, kStageBytes = kABytes + kBBytes;
   constexpr uint32_t kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   constexpr int kEpiWarp0 = 2, kEpiWarps = 16;
-  constexpr uint32_t kIdesc = (1u << 4) | (OperandFmt<AT>::kFmt << 7) | (OperandFmt<AT>::kFmt << 10) | (uint32_t(BN >> 3) << 17) |
-                              (uint32_t(kBM >> 4) << 24);
+  static_assert(BMN == 0 || BN % 64 == 0, "MN-major B is staged in 64-column slabs");
+  constexpr uint32_t kIdesc = (1u << 4) | (OperandFmt<AT>::kFmt << 7) | (OperandFmt<AT>::kFmt << 10) | (uint32_t(BMN) << 16) |
+                              (uint32_t(BN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
+  constexpr int kSlabBytes = kBK * 128;  // one 64-column slab of an MN-major B stage
 
   extern __shared__ uint8_t dense_smem_raw[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tfull_bar[2], tempty_bar[2];
@@ -123,7 +141,13 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           uint8_t* st = stages + size_t(s) * kStageBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
           tma_load_2d(st, &amap, ks * kBK, m_tile * kTileM, &full_bar[s]);
-          tma_load_2d(st + kABytes, &bmap, ks * kBK, n_tile * BN, &full_bar[s]);
+          if (BMN) {
+#pragma unroll
+            for (int sl = 0; sl < BN / 64; ++sl)
+              tma_load_2d(st + kABytes + sl * kSlabBytes, &bmap, n_tile * BN + sl * 64, ks * kBK, &full_bar[s]);
+          } else {
+            tma_load_2d(st + kABytes, &bmap, ks * kBK, n_tile * BN, &full_bar[s]);
+          }
         }
       }
     }
@@ -154,8 +178,9 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           for (int h = 0; h < MH; ++h)
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk)
-              tc_mma_ss(d_tmem + uint32_t(h * BN), make_b_desc(a_base + h * (kBM * 128) + kk * 32), make_b_desc(b_base + kk * 32),
-                        kIdesc, (ks > 0 || kk > 0) ? 1u : 0u);
+              tc_mma_ss(d_tmem + uint32_t(h * BN), make_b_desc(a_base + h * (kBM * 128) + kk * 32),
+                        BMN ? dense_mn_desc(b_base + kk * 2048, kSlabBytes) : make_b_desc(b_base + kk * 32), kIdesc,
+                        (ks > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
         if (!ok) break;
@@ -281,12 +306,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   }
 }
 
-template <typename AT, int BN, int STAGES, int MH>
+template <typename AT, int BN, int STAGES, int MH, int BMN = 0>
 cudaError_t launch_dense(int grid, cudaStream_t s, const CUtensorMap& amap, const CUtensorMap& bmap, const DenseTcArgs& p,
                          const EpiParams& e) {
   constexpr size_t smem = size_t(STAGES) * (kBM * MH * 128 + BN * 128) + 1024;
   static_assert(smem <= 227 * 1024, "shared memory per CTA");
-  auto kern = dense_tc_kernel<AT, BN, STAGES, MH>;
+  auto kern = dense_tc_kernel<AT, BN, STAGES, MH, BMN>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   kern<<<grid, kDenseThreads, smem, s>>>(amap, bmap, p, e);
   return cudaGetLastError();
@@ -319,11 +344,12 @@ constexpr DenseCfg kDenseCfgs[] = {{1, 256, 4, 0.424f}, {1, 224, 5, 0.410f}, {1,
 }  // namespace
 
 void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int* bn, int* mh, int* stages,
-                       int* grid) {
+                       int* grid, int bn_multiple) {
   const int64_t ksteps = (k + kBK - 1) / kBK;
   double best_cost = 1e300;
   DenseCfg best = kDenseCfgs[4];
   for (const DenseCfg& c : kDenseCfgs) {
+    if (c.bn % bn_multiple != 0) continue;  // an MN-major B is staged in 64-column slabs
     if (forced_bn > 0) {
       if (c.bn != forced_bn || c.mh != (forced_mh == 2 ? 2 : 1)) continue;
     } else {
@@ -345,7 +371,7 @@ void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, 
 // kernel and others is made on it).
 double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms) {
   int bn, mh, stages, grid;
-  tl_dense_tc_shape(m, n, k, sms, 0, 0, &bn, &mh, &stages, &grid);
+  tl_dense_tc_shape(m, n, k, sms, 0, 0, &bn, &mh, &stages, &grid, 16);
   for (const DenseCfg& c : kDenseCfgs) {
     if (c.bn != bn || c.mh != mh) continue;
     const int64_t t = ((m + kBM * c.mh - 1) / (kBM * c.mh)) * ((n + c.bn - 1) / c.bn);
@@ -357,10 +383,12 @@ double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms) {
 }
 
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
-                           int32_t out_dtype, const EpiParams& epi, const void* colscale, int32_t colscale_dtype, float colscale_mul) {
+                           int32_t out_dtype, const EpiParams& epi, const void* colscale, int32_t colscale_dtype, float colscale_mul,
+                           bool b_mn) {
   int bn, mh, stages, grid;
   const bool forced = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == 2 && ctx->forced.p0 > 0;
-  tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid);
+  tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
+                    b_mn ? 64 : 16);
   if (forced && (bn != ctx->forced.p0 || mh != (ctx->forced.p2 == 2 ? 2 : 1)))
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: no tensor-core tile with BN=%d MH=%d", ctx->forced.p0, ctx->forced.p2);
   const int tile_m = kBM * mh;
@@ -373,7 +401,8 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   p.colscale = colscale; p.colscale_dtype = colscale_dtype; p.colscale_mul = colscale_mul;
   CUtensorMap amap, bmap;
   if (!tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, uint32_t(tile_m), 3) ||
-      !tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3))
+      !(b_mn ? tl_encode_tmap_2d(&bmap, 2, b, uint64_t(n), uint64_t(k), uint64_t(n) * 2, 64, kBK, 3)  // b stored [K, N]: 64 columns x 64 k per box
+             : tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3)))
     return tl_set_error(ctx, TL_ERR_CUDA, "tl_matmul: cuTensorMapEncodeTiled failed (m=%lld n=%lld k=%lld)", (long long)m,
                         (long long)n, (long long)k);
   cudaError_t e = cudaErrorInvalidValue;
@@ -381,6 +410,18 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   if (mh == MH_ && bn == BN_)                                                                                \
     e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi)         \
                         : launch_dense<__nv_bfloat16, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi);
+  if (b_mn) {
+#define TL_DENSE_MN_CASE(MH_, BN_, ST_)                                                                       \
+  if (mh == MH_ && bn == BN_)                                                                                \
+    e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_, 1>(grid, ctx->stream, amap, bmap, p, epi)      \
+                        : launch_dense<__nv_bfloat16, BN_, ST_, MH_, 1>(grid, ctx->stream, amap, bmap, p, epi);
+    TL_DENSE_MN_CASE(1, 256, 4)
+    TL_DENSE_MN_CASE(1, 192, 5)
+    TL_DENSE_MN_CASE(1, 128, 6)
+    TL_DENSE_MN_CASE(2, 256, 3)
+    TL_DENSE_MN_CASE(2, 192, 4)
+#undef TL_DENSE_MN_CASE
+  } else {
   TL_DENSE_CASE(1, 256, 4)
   TL_DENSE_CASE(1, 224, 5)
   TL_DENSE_CASE(1, 192, 5)
@@ -393,6 +434,7 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   TL_DENSE_CASE(2, 192, 4)
   TL_DENSE_CASE(2, 176, 4)
   TL_DENSE_CASE(2, 160, 4)
+  }
 #undef TL_DENSE_CASE
   if (e != cudaSuccess) {
     ctx->async_errors++;
