@@ -487,3 +487,28 @@ def test_dense_tensor_core_nn_layout_odd_n_takes_the_transposition_pass(backend)
     assert _rel(_read_f32(be, y), _ref(a_v, b_v)) <= 1e-3
     for t in (a, b, y):
         t.destroy()
+
+
+@pytest.mark.parametrize("bn,mh", [(128, 1), (256, 1), (192, 2), (256, 2)])
+@pytest.mark.parametrize("trans_b", [False, True])
+def test_dense_tensor_core_transposed_a_without_a_transposed_copy(backend, bn, mh, trans_b):
+    """matmul(transpose(a), b) with a stored [K, M]: A is staged and multiplied MN-major too (TN and TT)."""
+    be = backend
+    m, k, n = 296, 200, 1000
+    rng = np.random.default_rng(bn + mh + int(trans_b))
+    a, a_v = _to_dev(be, rng.uniform(-1, 1, k * m).astype(np.float32), [k, m], "bf16")
+    b, b_v = _to_dev(be, (rng.uniform(-1, 1, k * n) * 0.2).astype(np.float32), [n, k] if trans_b else [k, n], "bf16")
+    be.forceVariant((B.TL_FAMILY_MATMUL, 2, bn, 0, mh, 0))
+    try:
+        launches0 = be.getKernelLaunchCount()
+        y = be.ops.matmul(be.ops.transpose(a), be.ops.transpose(b) if trans_b else b)
+        assert be.getKernelLaunchCount() == launches0 + 1
+        assert _rel(_read_f32(be, y), _ref(a_v.T, b_v.T if trans_b else b_v)) <= 1e-3
+        ap, ap_v = _to_dev(be, _pattern(k * m, 1), [k, m], "bf16")
+        bp, bp_v = _to_dev(be, _pattern(k * n, 4), [n, k] if trans_b else [k, n], "bf16")
+        yp = be.ops.matmul(be.ops.transpose(ap), be.ops.transpose(bp) if trans_b else bp)
+        np.testing.assert_array_equal(_read_f32(be, yp), _ref(ap_v.T, bp_v.T if trans_b else bp_v))
+    finally:
+        be.forceVariant(None)
+    for t in (a, b, y, ap, bp, yp):
+        t.destroy()

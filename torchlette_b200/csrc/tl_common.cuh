@@ -233,7 +233,7 @@ void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, 
 double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms);
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const struct EpiParams& epi, const void* colscale = nullptr,
-                           int32_t colscale_dtype = 0, float colscale_mul = 1.0f, bool b_mn = false);
+                           int32_t colscale_dtype = 0, float colscale_mul = 1.0f, bool b_mn = false, bool a_mn = false);
 bool tl_qgemv_stream_applicable(const tl_variant& v, int64_t m, int64_t k, int32_t a_dtype, const tl_quant_desc& q);
 void tl_qgemv_stream_geometry(tl_ctx* ctx, const tl_variant& v, int32_t m, int64_t tiles, int64_t k, int* grid, int* block,
                               size_t* smem);

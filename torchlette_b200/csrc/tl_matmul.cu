@@ -258,7 +258,7 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
       int bn, mh, stages, grid;
       const bool f = forced_tc && ctx->forced.p0 > 0;
       tl_dense_tc_shape(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
-                        (!trans_b && n % 8 == 0 && n >= 128) ? 64 : 16);
+                        (((!trans_b && n % 8 == 0) || (trans_a && m % 8 == 0)) && n >= 128) ? 64 : 16);
       receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages; receipt_only->choice.p2 = mh;
       receipt_only->grid[0] = grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
       receipt_only->block = 576;
@@ -287,7 +287,8 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     // bring the operands to the NT layout (A [M, K], B [N, K]) in scratch where they are stored transposed
     // a B stored [K, N] is multiplied as it lies (MN-major tiles) when its row pitch allows a TMA map
     const bool b_mn = !p.trans_b && n % 8 == 0 && n >= 128;
-    const size_t a_elems = p.trans_a ? size_t(m) * k : 0, b_elems = (p.trans_b || b_mn) ? 0 : size_t(n) * k;
+    const bool a_mn = p.trans_a && m % 8 == 0 && n >= 128;  // likewise an A stored [K, M]
+    const size_t a_elems = (p.trans_a && !a_mn) ? size_t(m) * k : 0, b_elems = (p.trans_b || b_mn) ? 0 : size_t(n) * k;
     uint8_t* scratch = nullptr;
     if (a_elems + b_elems) {
       void* sp = nullptr;
@@ -299,7 +300,7 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
       const uint8_t* ab = static_cast<const uint8_t*>(a) + size_t(bi) * stride_a * 2;
       const uint8_t* bb = static_cast<const uint8_t*>(b) + size_t(bi) * stride_b * 2;
       uint8_t* ob = static_cast<uint8_t*>(out) + size_t(bi) * stride_c * tl_dtype_size(out_dtype);
-      if (p.trans_a && (bi == 0 || stride_a != 0)) {
+      if (p.trans_a && !a_mn && (bi == 0 || stride_a != 0)) {
         rc = tl_transpose2d(ctx, ab, scratch, 1, k, m, 2);  // stored [K, M] -> [M, K]
         if (rc != TL_OK) return rc;
       }
@@ -308,8 +309,8 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
         rc = tl_transpose2d(ctx, bb, bt, 1, k, n, 2);       // stored [K, N] -> [N, K]
         if (rc != TL_OK) return rc;
       }
-      rc = tl_launch_dense_tc(ctx, p.trans_a ? scratch : ab, (p.trans_b || b_mn) ? bb : bt, ob, m, n, k, dtype_a, out_dtype, epi, nullptr,
-                              0, 1.0f, b_mn);
+      rc = tl_launch_dense_tc(ctx, (p.trans_a && !a_mn) ? scratch : ab, (p.trans_b || b_mn) ? bb : bt, ob, m, n, k, dtype_a, out_dtype,
+                              epi, nullptr, 0, 1.0f, b_mn, a_mn);
       if (rc != TL_OK) return rc;
     }
     ctx->counters[TL_COUNTER_MATMUL]++;

@@ -3,8 +3,8 @@
 // tcgen05.mma through 128-byte-swizzle descriptors; f32 accumulators in TMEM, double buffered, the
 // epilogue written straight from TMEM.  The large-M kernel of tl_matmul; replaces the reference's
 // tiled matmul body + epilogue (src/schedule/matmul-skeleton.ts:738-966) for the NT layout that
-// `linear` produces and for the NN layout (B stored [K, N], multiplied MN-major as it lies); an A stored
-// [K, M] is brought to [M, K] by one transposition pass, see tl_matmul.
+// `linear` produces and for the other three (an operand stored with k as its slow dimension -- B [K, N],
+// A [K, M] -- is staged and multiplied MN-major as it lies, no transposed copy).
 //
 //   tile: 128 x MH rows of A (tokens, = TMEM lanes; MH = 1 or 2 row halves) x BN rows of B (output columns,
 //         = TMEM columns; BN a multiple of 16 up to 256), 64 k per pipeline stage (one 128-byte swizzled row
@@ -80,8 +80,9 @@ __device__ __forceinline__ uint64_t dense_mn_desc(uint32_t smem_addr, uint32_t s
 }
 
 // BMN = 1: B is stored [K, N] (the NN layout of matmul(a, b)); its tiles are staged and multiplied MN-major,
-// so no transposed copy of B is made.  BN must then be a multiple of 64.
-template <typename AT, int BN, int STAGES, int MH, int BMN>
+// so no transposed copy of B is made.  BN must then be a multiple of 64.  AMN = 1: the same for an A stored
+// [K, M] (a transposed view of the first operand).
+template <typename AT, int BN, int STAGES, int MH, int BMN, int AMN>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap, DenseTcArgs p, EpiParams epi) {
   static_assert(BN % 16 == 0 && BN >= 16 && BN <= 256, "MMA N");
@@ -91,7 +92,7 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   constexpr uint32_t kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
   constexpr int kEpiWarp0 = 2, kEpiWarps = 16;
   static_assert(BMN == 0 || BN % 64 == 0, "MN-major B is staged in 64-column slabs");
-  constexpr uint32_t kIdesc = (1u << 4) | (OperandFmt<AT>::kFmt << 7) | (OperandFmt<AT>::kFmt << 10) | (uint32_t(BMN) << 16) |
+  constexpr uint32_t kIdesc = (1u << 4) | (OperandFmt<AT>::kFmt << 7) | (OperandFmt<AT>::kFmt << 10) | (uint32_t(AMN) << 15) | (uint32_t(BMN) << 16) |
                               (uint32_t(BN >> 3) << 17) | (uint32_t(kBM >> 4) << 24);
   constexpr int kSlabBytes = kBK * 128;  // one 64-column slab of an MN-major B stage
 
@@ -140,7 +141,13 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           }
           uint8_t* st = stages + size_t(s) * kStageBytes;
           mbar_expect_tx(&full_bar[s], kStageBytes);
-          tma_load_2d(st, &amap, ks * kBK, m_tile * kTileM, &full_bar[s]);
+          if (AMN) {
+#pragma unroll
+            for (int sl = 0; sl < kTileM / 64; ++sl)
+              tma_load_2d(st + sl * kSlabBytes, &amap, m_tile * kTileM + sl * 64, ks * kBK, &full_bar[s]);
+          } else {
+            tma_load_2d(st, &amap, ks * kBK, m_tile * kTileM, &full_bar[s]);
+          }
           if (BMN) {
 #pragma unroll
             for (int sl = 0; sl < BN / 64; ++sl)
@@ -178,7 +185,8 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           for (int h = 0; h < MH; ++h)
 #pragma unroll
             for (int kk = 0; kk < kBK / 16; ++kk)
-              tc_mma_ss(d_tmem + uint32_t(h * BN), make_b_desc(a_base + h * (kBM * 128) + kk * 32),
+              tc_mma_ss(d_tmem + uint32_t(h * BN),
+                        AMN ? dense_mn_desc(a_base + h * (kBM * 128) + kk * 2048, kSlabBytes) : make_b_desc(a_base + h * (kBM * 128) + kk * 32),
                         BMN ? dense_mn_desc(b_base + kk * 2048, kSlabBytes) : make_b_desc(b_base + kk * 32), kIdesc,
                         (ks > 0 || kk > 0) ? 1u : 0u);
           tc_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
@@ -306,12 +314,12 @@ dense_tc_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   }
 }
 
-template <typename AT, int BN, int STAGES, int MH, int BMN = 0>
+template <typename AT, int BN, int STAGES, int MH, int BMN = 0, int AMN = 0>
 cudaError_t launch_dense(int grid, cudaStream_t s, const CUtensorMap& amap, const CUtensorMap& bmap, const DenseTcArgs& p,
                          const EpiParams& e) {
   constexpr size_t smem = size_t(STAGES) * (kBM * MH * 128 + BN * 128) + 1024;
   static_assert(smem <= 227 * 1024, "shared memory per CTA");
-  auto kern = dense_tc_kernel<AT, BN, STAGES, MH, BMN>;
+  auto kern = dense_tc_kernel<AT, BN, STAGES, MH, BMN, AMN>;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   kern<<<grid, kDenseThreads, smem, s>>>(amap, bmap, p, e);
   return cudaGetLastError();
@@ -384,11 +392,11 @@ double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms) {
 
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const EpiParams& epi, const void* colscale, int32_t colscale_dtype, float colscale_mul,
-                           bool b_mn) {
+                           bool b_mn, bool a_mn) {
   int bn, mh, stages, grid;
   const bool forced = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == 2 && ctx->forced.p0 > 0;
   tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
-                    b_mn ? 64 : 16);
+                    (b_mn || a_mn) ? 64 : 16);
   if (forced && (bn != ctx->forced.p0 || mh != (ctx->forced.p2 == 2 ? 2 : 1)))
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: no tensor-core tile with BN=%d MH=%d", ctx->forced.p0, ctx->forced.p2);
   const int tile_m = kBM * mh;
@@ -400,7 +408,8 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   p.status = ctx->dev_status;
   p.colscale = colscale; p.colscale_dtype = colscale_dtype; p.colscale_mul = colscale_mul;
   CUtensorMap amap, bmap;
-  if (!tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, uint32_t(tile_m), 3) ||
+  if (!(a_mn ? tl_encode_tmap_2d(&amap, 2, a, uint64_t(m), uint64_t(k), uint64_t(m) * 2, 64, kBK, 3)  // a stored [K, M]
+             : tl_encode_tmap_2d(&amap, 2, a, uint64_t(k), uint64_t(m), uint64_t(k) * 2, kBK, uint32_t(tile_m), 3)) ||
       !(b_mn ? tl_encode_tmap_2d(&bmap, 2, b, uint64_t(n), uint64_t(k), uint64_t(n) * 2, 64, kBK, 3)  // b stored [K, N]: 64 columns x 64 k per box
              : tl_encode_tmap_2d(&bmap, 2, b, uint64_t(k), uint64_t(n), uint64_t(k) * 2, kBK, uint32_t(bn), 3)))
     return tl_set_error(ctx, TL_ERR_CUDA, "tl_matmul: cuTensorMapEncodeTiled failed (m=%lld n=%lld k=%lld)", (long long)m,
@@ -410,11 +419,19 @@ int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out,
   if (mh == MH_ && bn == BN_)                                                                                \
     e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi)         \
                         : launch_dense<__nv_bfloat16, BN_, ST_, MH_>(grid, ctx->stream, amap, bmap, p, epi);
-  if (b_mn) {
-#define TL_DENSE_MN_CASE(MH_, BN_, ST_)                                                                       \
-  if (mh == MH_ && bn == BN_)                                                                                \
-    e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_, 1>(grid, ctx->stream, amap, bmap, p, epi)      \
-                        : launch_dense<__nv_bfloat16, BN_, ST_, MH_, 1>(grid, ctx->stream, amap, bmap, p, epi);
+  if (b_mn || a_mn) {
+#define TL_DENSE_MN_CASE(MH_, BN_, ST_)                                                                                  \
+  if (mh == MH_ && bn == BN_) {                                                                                         \
+    if (a_mn && b_mn)                                                                                                   \
+      e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_, 1, 1>(grid, ctx->stream, amap, bmap, p, epi)            \
+                          : launch_dense<__nv_bfloat16, BN_, ST_, MH_, 1, 1>(grid, ctx->stream, amap, bmap, p, epi);    \
+    else if (a_mn)                                                                                                      \
+      e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_, 0, 1>(grid, ctx->stream, amap, bmap, p, epi)            \
+                          : launch_dense<__nv_bfloat16, BN_, ST_, MH_, 0, 1>(grid, ctx->stream, amap, bmap, p, epi);    \
+    else                                                                                                                \
+      e = dtype == TL_F16 ? launch_dense<__half, BN_, ST_, MH_, 1, 0>(grid, ctx->stream, amap, bmap, p, epi)            \
+                          : launch_dense<__nv_bfloat16, BN_, ST_, MH_, 1, 0>(grid, ctx->stream, amap, bmap, p, epi);    \
+  }
     TL_DENSE_MN_CASE(1, 256, 4)
     TL_DENSE_MN_CASE(1, 192, 5)
     TL_DENSE_MN_CASE(1, 128, 6)
