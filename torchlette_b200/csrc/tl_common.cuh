@@ -228,9 +228,11 @@ int32_t tl_int4_matmul(tl_ctx* ctx, const char* who, int route, const void* a, i
                        const tl_epilogue* epilogue, tl_plan_receipt* receipt_only);
 // Dense tensor-core matmul (tl_matmul_tc.cu): NT layout, both operands f16 or both bf16.
 bool tl_dense_tc_applicable(const void* a, const void* b, int64_t m, int64_t n, int64_t k, int32_t dtype_a, int32_t dtype_b);
-void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int* bn, int* mh, int* stages,
-                       int* grid, int bn_multiple = 16);
-double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms);
+// The tile the dense tensor-core kernel would use and the modelled time of that launch: bn columns and
+// mh row halves of 128 per tile, ring stages, CTAs.  forced_bn > 0 pins the tile; bn_multiple = 64 when an
+// operand is multiplied MN-major.
+struct TlDenseTcChoice { int bn, mh, stages, grid; double cost_us; };
+TlDenseTcChoice tl_dense_tc_choose(int64_t m, int64_t n, int64_t k, int sms, int forced_bn = 0, int forced_mh = 0, int bn_multiple = 16);
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const struct EpiParams& epi, const void* colscale = nullptr,
                            int32_t colscale_dtype = 0, float colscale_mul = 1.0f, bool b_mn = false, bool a_mn = false);

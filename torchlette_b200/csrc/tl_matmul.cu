@@ -255,12 +255,11 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     receipt_only->grid[2] = use_gemv ? 1 : int32_t(batch);
     receipt_only->block = use_gemv ? warps * 32 : 256;
     if (use_tc) {
-      int bn, mh, stages, grid;
       const bool f = forced_tc && ctx->forced.p0 > 0;
-      tl_dense_tc_shape(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
-                        (((!trans_b && n % 8 == 0) || (trans_a && m % 8 == 0)) && n >= 128) ? 64 : 16);
-      receipt_only->choice.p0 = bn; receipt_only->choice.p1 = stages; receipt_only->choice.p2 = mh;
-      receipt_only->grid[0] = grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
+      const TlDenseTcChoice ch = tl_dense_tc_choose(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0,
+                                                    (((!trans_b && n % 8 == 0) || (trans_a && m % 8 == 0)) && n >= 128) ? 64 : 16);
+      receipt_only->choice.p0 = ch.bn; receipt_only->choice.p1 = ch.stages; receipt_only->choice.p2 = ch.mh;
+      receipt_only->grid[0] = ch.grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
       receipt_only->block = 576;
     }
     receipt_only->split_k = 1;

@@ -19,7 +19,7 @@
 //         step that would take the reads down further; this kernel stays within one CTA.)  The two halves
 //         fill TMEM (2 x BN columns), so the epilogue (one warp per lane quarter, half and column half)
 //         does not overlap the next tile; it is a few percent when K is in the thousands.
-//         The host picks MH and BN from a per-tile time model times the number of waves (tl_dense_tc_shape);
+//         The host picks MH and BN from a per-tile time model times the number of waves (tl_dense_tc_choose);
 //         (Stages of 32 k -- 64-byte-swizzle rows, seven deep in the same shared memory -- computed the same
 //         results 6 to 10 % slower at 256-row tiles.)
 //   warp 0: TMA producer (one elected lane); warp 1: TMEM allocation + MMA issue (one elected lane);
@@ -351,13 +351,11 @@ constexpr DenseCfg kDenseCfgs[] = {{1, 256, 4, 0.424f}, {1, 224, 5, 0.410f}, {1,
                                    {2, 208, 3, 0.684f}, {2, 192, 4, 0.580f}, {2, 176, 4, 0.586f}, {2, 160, 4, 0.583f}};
 }  // namespace
 
-void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int* bn, int* mh, int* stages,
-                       int* grid, int bn_multiple) {
+TlDenseTcChoice tl_dense_tc_choose(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, int forced_mh, int bn_multiple) {
   const int64_t ksteps = (k + kBK - 1) / kBK;
-  double best_cost = 1e300;
-  DenseCfg best = kDenseCfgs[4];
+  TlDenseTcChoice best{128, 1, 6, 1, 1e300};
   for (const DenseCfg& c : kDenseCfgs) {
-    if (c.bn % bn_multiple != 0) continue;  // an MN-major B is staged in 64-column slabs
+    if (c.bn % bn_multiple != 0) continue;  // an MN-major operand is staged in 64-column slabs
     if (forced_bn > 0) {
       if (c.bn != forced_bn || c.mh != (forced_mh == 2 ? 2 : 1)) continue;
     } else {
@@ -368,35 +366,18 @@ void tl_dense_tc_shape(int64_t m, int64_t n, int64_t k, int sms, int forced_bn, 
     const double main_us = double(ksteps) * c.step_us;
     const double tile = c.mh == 1 ? std::max(main_us, 0.012 * c.bn + 0.5) + 0.3 : main_us + 0.0094 * c.bn + 0.5;
     const double cost = double((t + sms - 1) / sms) * tile;
-    if (cost < best_cost) { best_cost = cost; best = c; }
+    if (cost < best.cost_us) best = TlDenseTcChoice{c.bn, c.mh, c.stages, int(std::min<int64_t>(sms, t)), cost};
   }
-  *bn = best.bn; *mh = best.mh; *stages = best.stages;
-  const int64_t t = ((m + kBM * best.mh - 1) / (kBM * best.mh)) * ((n + best.bn - 1) / best.bn);
-  *grid = int(std::min<int64_t>(sms, t));
-}
-
-// The modelled time of the launch tl_launch_dense_tc would make, in microseconds (selection between this
-// kernel and others is made on it).
-double tl_dense_tc_cost_us(int64_t m, int64_t n, int64_t k, int sms) {
-  int bn, mh, stages, grid;
-  tl_dense_tc_shape(m, n, k, sms, 0, 0, &bn, &mh, &stages, &grid, 16);
-  for (const DenseCfg& c : kDenseCfgs) {
-    if (c.bn != bn || c.mh != mh) continue;
-    const int64_t t = ((m + kBM * c.mh - 1) / (kBM * c.mh)) * ((n + c.bn - 1) / c.bn);
-    const double main_us = double((k + kBK - 1) / kBK) * c.step_us;
-    const double tile = c.mh == 1 ? std::max(main_us, 0.012 * c.bn + 0.5) + 0.3 : main_us + 0.0094 * c.bn + 0.5;
-    return double((t + sms - 1) / sms) * tile;
-  }
-  return 1e30;
+  return best;
 }
 
 int32_t tl_launch_dense_tc(tl_ctx* ctx, const void* a, const void* b, void* out, int64_t m, int64_t n, int64_t k, int32_t dtype,
                            int32_t out_dtype, const EpiParams& epi, const void* colscale, int32_t colscale_dtype, float colscale_mul,
                            bool b_mn, bool a_mn) {
-  int bn, mh, stages, grid;
   const bool forced = ctx->has_forced && ctx->forced.family == TL_FAMILY_MATMUL && ctx->forced.kernel == 2 && ctx->forced.p0 > 0;
-  tl_dense_tc_shape(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0, &bn, &mh, &stages, &grid,
-                    (b_mn || a_mn) ? 64 : 16);
+  const TlDenseTcChoice ch = tl_dense_tc_choose(m, n, k, ctx->sm_count, forced ? ctx->forced.p0 : 0, forced ? ctx->forced.p2 : 0,
+                                                (b_mn || a_mn) ? 64 : 16);
+  const int bn = ch.bn, mh = ch.mh, grid = ch.grid;
   if (forced && (bn != ctx->forced.p0 || mh != (ctx->forced.p2 == 2 ? 2 : 1)))
     return tl_set_error(ctx, TL_ERR_INVALID_ARG, "tl_matmul: no tensor-core tile with BN=%d MH=%d", ctx->forced.p0, ctx->forced.p2);
   const int tile_m = kBM * mh;

@@ -650,7 +650,7 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
         const double tiles = double((n + kTileRows - 1) / kTileRows) * double((m + 191) / 192);
         const double waves = std::max(1.0, std::ceil(tiles / sms * 4.0) / 4.0);
         const double fused_us = waves * double((k + 127) / 128) * (q.group_size != k ? 1.4 : 0.87);  // group scales: an f32 multiply per weight
-        const double dense_us = tl_dense_tc_cost_us(m, n, k, sms) + double(n) * double(k) * 3.0 / 4.0e6 + 6.0;
+        const double dense_us = tl_dense_tc_choose(m, n, k, sms).cost_us + double(n) * double(k) * 3.0 / 4.0e6 + 6.0;
         if (dense_us < 0.92 * fused_us) v = dd;
       }
     }
@@ -692,10 +692,9 @@ int32_t tl_launch_qgemm(tl_ctx* ctx, const tl_variant& v, const void* a, int32_t
   if (v.kernel == kDequantDense) {
     if (receipt) {
       receipt->choice = v;
-      int bn, mh, stages, grid;
-      tl_dense_tc_shape(m, n, k, ctx->sm_count, 0, 0, &bn, &mh, &stages, &grid);
-      receipt->choice.p0 = bn; receipt->choice.p1 = stages; receipt->choice.p2 = mh;
-      receipt->grid[0] = grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
+      const TlDenseTcChoice ch = tl_dense_tc_choose(m, n, k, ctx->sm_count);
+      receipt->choice.p0 = ch.bn; receipt->choice.p1 = ch.stages; receipt->choice.p2 = ch.mh;
+      receipt->grid[0] = ch.grid; receipt->grid[1] = 1; receipt->grid[2] = 1;
       receipt->block = 576; receipt->split_k = 1;
       return TL_OK;
     }
