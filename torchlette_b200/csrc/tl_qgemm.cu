@@ -641,7 +641,8 @@ int32_t tl_qgemm_default_variant(tl_ctx* ctx, int64_t m, int64_t n, int64_t k, i
       // dense kernel (whose operands both come from shared memory at its full tile sizes) beats converting
       // on the operand path: compare the modelled times.  Fused: 0.87 us per 128-k step of a 128 x 192 tile
       // (measured; 1.4 us with group scales), the last partial wave cut along K; dequantization: 3 bytes of
-      // HBM traffic per weight at the 4.4 TB/s that pass was measured at (40 us for 14336 x 4096; the model keeps 4).  E.g. 2048 tokens: n = 4096,
+      // HBM traffic per weight (the pass alone runs at the copy peak, 27 us for 14336 x 4096; the model charges 4 TB/s
+      // because the dense kernel that follows reads a freshly written operand and runs a little slower for it).  E.g. 2048 tokens: n = 4096,
       // k = 14336 runs 200 us this way against 229 us fused, n = 14336, k = 4096 228 against 229 (stays fused),
       // the same with groups of 128 218 against 368; 8192 tokens x 4096 x 4096: 231 against 284.
       tl_variant dd{TL_FAMILY_QGEMM, kDequantDense, 0, 0, 0, 0};
