@@ -174,6 +174,14 @@ __global__ void __launch_bounds__(512) dense_gemv_kernel(MatmulArgs p, EpiParams
   }
 }
 
+// Which operands the tensor-core kernel multiplies MN-major as they are stored (no transposed copy): a B
+// stored [K, N], an A stored [K, M], when the row pitch allows a TMA map (a multiple of 16 bytes) and the
+// 64-column tiles that form needs are not wasted on a narrow output.
+void dense_mn_operands(bool trans_a, bool trans_b, int64_t m, int64_t n, bool* a_mn, bool* b_mn) {
+  *b_mn = !trans_b && n % 8 == 0 && n >= 128;
+  *a_mn = trans_a && m % 8 == 0 && n >= 128;
+}
+
 bool gemv_applicable(const MatmulArgs& p, const EpiParams& epi) {
   // dense GEMV: m <= 16, one batch, B stored [N, K], same 2-byte operand type, no cast prologue,
   // epilogue of bias / unary ops only (gemv.ts:135-159), vector loads need k % 32 == 0 and alignment
@@ -256,8 +264,10 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
     receipt_only->block = use_gemv ? warps * 32 : 256;
     if (use_tc) {
       const bool f = forced_tc && ctx->forced.p0 > 0;
+      bool ra_mn, rb_mn;
+      dense_mn_operands(trans_a != 0, trans_b != 0, m, n, &ra_mn, &rb_mn);
       const TlDenseTcChoice ch = tl_dense_tc_choose(m, n, k, ctx->sm_count, f ? ctx->forced.p0 : 0, f ? ctx->forced.p2 : 0,
-                                                    (((!trans_b && n % 8 == 0) || (trans_a && m % 8 == 0)) && n >= 128) ? 64 : 16);
+                                                    (ra_mn || rb_mn) ? 64 : 16);
       receipt_only->choice.p0 = ch.bn; receipt_only->choice.p1 = ch.stages; receipt_only->choice.p2 = ch.mh;
       receipt_only->grid[0] = ch.grid; receipt_only->grid[1] = 1; receipt_only->grid[2] = 1;
       receipt_only->block = 576;
@@ -285,8 +295,8 @@ extern "C" int32_t tl_matmul(tl_ctx* ctx, const void* a, const void* b, void* ou
   } else if (use_tc) {
     // bring the operands to the NT layout (A [M, K], B [N, K]) in scratch where they are stored transposed
     // a B stored [K, N] is multiplied as it lies (MN-major tiles) when its row pitch allows a TMA map
-    const bool b_mn = !p.trans_b && n % 8 == 0 && n >= 128;
-    const bool a_mn = p.trans_a && m % 8 == 0 && n >= 128;  // likewise an A stored [K, M]
+    bool a_mn, b_mn;
+    dense_mn_operands(p.trans_a != 0, p.trans_b != 0, m, n, &a_mn, &b_mn);
     const size_t a_elems = (p.trans_a && !a_mn) ? size_t(m) * k : 0, b_elems = (p.trans_b || b_mn) ? 0 : size_t(n) * k;
     uint8_t* scratch = nullptr;
     if (a_elems + b_elems) {
